@@ -1,0 +1,142 @@
+/* t3.h: the C ABI of the B200-native EXL3 projection engine.
+ *
+ * A drop-in for the projection entry points of davidtai/turboexl3 (a Zig library over Metal/HIP kernels): every call
+ * below names the reference interface it replaces (file:line relative to the reference's root). Arguments are plain
+ * pointers and sizes; device pointers are CUDA device addresses of the current device; `stream` is a cudaStream_t passed
+ * as void*. No call allocates device memory except where it says so; scratch is a caller-provided workspace whose size
+ * the matching *_workspace_bytes call returns. Weights are read in the pack's own layout, never copied or repacked:
+ *   trellis  u16 [in/16, out/16, n]      (banks: [E, in/16, out/16, n]), n even in [16, 128], bits per weight = n/16
+ *   suh      f16 [in]   svh  f16 [out]   (banks: [E, in], [E, out])
+ * Every call validates before it launches anything and returns a t3_status; nothing is launched on a refusal
+ * (the reference's rule, docs/core/api.md:10-12). Calls are stream-ordered and never synchronise the device.
+ */
+#ifndef T3_H
+#define T3_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes. t3_status_name returns the reference's error names (src/root.zig:93-141, table/table.zig:591-593). */
+typedef enum {
+    T3_OK = 0,
+    T3_BAD_EXL3_SHAPE = 1,          /* "BadExl3Shape" */
+    T3_BAD_EXL3_DTYPE = 2,          /* "BadExl3Dtype" */
+    T3_ENGINE_NOT_IMPLEMENTED = 3,  /* "Exl3EngineNotImplemented" */
+    T3_ENGINE_CACHE_FULL = 4,       /* "Exl3EngineCacheFull" */
+    T3_GATE_UP_RATE_MISMATCH = 5,   /* "Exl3GateUpRateMismatch" */
+    T3_INVALID_CLAMP = 6,           /* "InvalidExl3Clamp" */
+    T3_INVALID_CONFIG = 7,          /* "InvalidTurboexl3Config" */
+    T3_KERNEL_CREATE_FAILED = 8,    /* "KernelCreateFailed" */
+    T3_CUDA_ERROR = 9,              /* "CudaError" (the reference's "MlxError") */
+    T3_TOPK_EXCEEDS_REDUCE_BANK = 10, /* "Exl3TopKExceedsReduceBank" (src/core/spec.zig:75-77) */
+    T3_WORKSPACE_TOO_SMALL = 11,    /* "WorkspaceTooSmall" (no counterpart: the reference allocates its scratch) */
+    T3_EXPERT_LAYOUT_UNSUPPORTED = 12, /* "ExpertLayoutUnsupported" (src/core/spec.zig:38-50) */
+    T3_WINDOW_UNSUPPORTED = 13,     /* "Exl3WindowUnsupported" (src/core/spec.zig:48) */
+    T3_NULL_POINTER = 14            /* "NullPointer" */
+} t3_status;
+
+const char* t3_status_name(int status);
+
+/* Activation dtypes, numbered as the reference's native kernels number them (src/kernels/hip/common.hpp:21). */
+typedef enum { T3_F32 = 0, T3_F16 = 1, T3_BF16 = 2 } t3_dtype;
+/* src/core/format.zig:18-21 */
+typedef enum { T3_MUL1 = 0, T3_MCG = 1 } t3_codebook;
+/* src/core/format.zig:83 */
+typedef enum { T3_CLAMP_GATE_IN = 0, T3_CLAMP_SILU_OUT = 1 } t3_clamp_at;
+
+/* How a pack's trellis decodes (format.Decode, src/core/format.zig:72-78): codebook and codeword width 8..16. */
+typedef struct {
+    int codebook;     /* t3_codebook */
+    int window_bits;  /* 16 unless the pack names a narrower search width */
+} t3_decode;
+
+/* One projection (root.Proj, src/root.zig:74): device pointers. */
+typedef struct {
+    const void* trellis;
+    const void* suh;
+    const void* svh;
+} t3_proj;
+
+/* A routed bank (root.Bank, src/root.zig:75) with the shapes the reference reads off its arrays
+ * (root.bankGeometry, src/root.zig:104-126). */
+typedef struct {
+    t3_proj gate, up, down;
+    int experts, hidden, inter;
+    int n_gate, n_up, n_down;  /* halfwords per tile of each projection's trellis */
+} t3_bank;
+
+/* Dispatch constants a host reads (root.kernels, src/root.zig:66-71; src/core/spec.zig:59-61). */
+#define T3_DECODE_ROWS_MAX 32   /* rows up to this take the in-register GEMV chain (the reference's is 16) */
+#define T3_REDUCE_MAX_TOPK 32
+int t3_uses_prefill_arm(size_t rows);                    /* spec.usesPrefillArm, src/core/spec.zig:63-65 */
+int t3_admit_topk(uint32_t topk);                        /* spec.admitTopK, src/core/spec.zig:75-77 */
+/* spec.trellisAdmitted, src/core/spec.zig:80-88: 1 when a stacked trellis shape fits the config */
+int t3_trellis_admitted(const int* shape, int ndim, uint32_t experts, uint32_t in_dim, uint32_t out_dim, uint32_t n);
+
+/* The pack's `expert_quant` block (spec.parseExpertQuant, src/core/spec.zig:38-50): n, codebook and window from the
+ * model config's JSON text. */
+typedef struct {
+    uint32_t n;
+    int codebook;
+    int window_bits;
+} t3_spec;
+int t3_parse_expert_quant(const char* json, size_t len, t3_spec* out);
+
+/* Process-wide configuration (core.config.Config / configure, src/core/config.zig:7-181), set before the first call.
+ * Only the knobs that mean something on this backend exist. */
+typedef struct {
+    int prefill;             /* 0: rows past T3_DECODE_ROWS_MAX refuse Exl3EngineNotImplemented (Config.prefill) */
+    uint32_t ring_bytes;     /* shared-memory bytes a GEMV CTA's code ring may take; 0 = default */
+    uint32_t dense_split;    /* K slices of a dense GEMV cluster (1, 2, 4, 8); 0 = choose from the shape */
+} t3_config;
+void t3_config_default(t3_config* out);
+int t3_configure(const t3_config* cfg);                  /* InvalidTurboexl3Config on a bad value */
+
+/* Bits a kernel sets when one of its bounded waits ran out (the context stays usable). Synchronises `stream`. */
+int t3_device_error(void* stream, uint32_t* bits_out, int clear);
+
+/* W_hat: the inner f16 weight [in, out] (format.reconstructInner, src/core/format.zig:276-291;
+ * Dense.dequantize, src/core/dense.zig:909-922). */
+int t3_dequant(const void* trellis, int in_dim, int out_dim, int n, t3_decode dec, void* w_hat, void* stream);
+
+/* Test hook, the reference's codebook kernel test (src/hip_tests.zig:24-57): all 65,536 codewords through the device
+ * decoders, out[cw] = f16 bits (device pointer to 65,536 uint16). */
+int t3_codebook_table(t3_decode dec, void* out, void* stream);
+
+/* root.linear (src/root.zig:309-351): y [rows, out] in x's dtype for x [rows, in]. `workspace` may be null when
+ * t3_linear_workspace_bytes returns 0 for the call. */
+size_t t3_linear_workspace_bytes(size_t rows, int in_dim, int out_dim, int n);
+int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, const void* suh, const void* svh,
+              int in_dim, int out_dim, int n, t3_decode dec, void* y, void* workspace, size_t workspace_bytes,
+              void* stream);
+
+/* root.moe (src/root.zig:822-825): routed SwiGLU experts. x [rows, hidden]; inds (int32/uint32) and scores
+ * [rows, topk]; y [rows, hidden] in x's dtype. scores_dtype is a t3_dtype. Gate, up and down must share a rate. */
+size_t t3_moe_workspace_bytes(size_t rows, int topk, const t3_bank* bank);
+int t3_moe(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds, const void* scores,
+           int scores_dtype, int topk, t3_decode dec, void* y, void* workspace, size_t workspace_bytes, void* stream);
+/* root.moeSwiglu (src/root.zig:831-833): t3_moe with the SwiGLU clamp `limit` (0 none) at `clamp_at`. */
+int t3_moe_swiglu(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds, const void* scores,
+                  int scores_dtype, int topk, t3_decode dec, uint32_t limit, int clamp_at, void* y, void* workspace,
+                  size_t workspace_bytes, void* stream);
+/* root.moeClamped (src/root.zig:1001-1004): limit in 1..128 at gate_in, else InvalidExl3Clamp. */
+int t3_moe_clamped(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds, const void* scores,
+                   int scores_dtype, int topk, t3_decode dec, int limit, void* y, void* workspace,
+                   size_t workspace_bytes, void* stream);
+/* root.moeWithShared (src/root.zig:976-984): t3_moe plus an already gated shared expert [rows, hidden] in x's dtype,
+ * added at the routed output's rounding point. */
+int t3_moe_with_shared(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds,
+                       const void* scores, int scores_dtype, int topk, t3_decode dec, const void* shared, void* y,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
+/* Kernels this library launched since the process started (for benches that must report their launch count). */
+uint64_t t3_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,136 @@
+"""The dense EXL3 linear against the oracle's format.project, at the shapes and row counts of the reference's own GPU
+tests (src/hip_tests.zig:294-347, src/core/gpu_test.zig:384-398) and of BASELINE configs 1 and 2.
+
+Bars (gpu_util.check): the reference's own `ref.compare` max|err|/rms <= 5e-3 for f32/f16 activations and <= 2.5e-2
+for bf16 (src/core/gpu_test.zig:46,438,446), plus compareRounded(half ulp of the output dtype) <= 3e-3."""
+import numpy as np
+import pytest
+import torch
+
+import turboexl3_b200 as t3
+from oracle import binding as ob
+from turboexl3_b200 import synth
+
+from gpu_util import bits16, check, dev, host_f32, x_as
+
+pytestmark = pytest.mark.gpu
+
+
+def run_case(in_dim, out_dim, n, codebook, window, dt, rows, seed, scaled=True):
+    trellis, suh, svh = synth.linear(seed, in_dim, out_dim, n, scaled=scaled)
+    x16 = synth.activations(seed + 1, rows, in_dim)
+    x = x_as(x16, dt)
+    dec = t3.Decode(codebook, window)
+    y = t3.linear(x, dev(trellis), dev(suh), dev(svh), dec)
+    assert y.shape == (rows, out_dim) and y.dtype == x.dtype
+    what = ob.reconstruct_inner(trellis, in_dim, out_dim, n, codebook, window)
+    ref = ob.linear_rows_what(host_f32(x), what, suh, svh, in_dim, out_dim)
+    assert np.all(np.isfinite(ref))
+    return host_f32(y), ref, y
+
+
+# (in, out, n, codebook, window, dtype): src/hip_tests.zig:294-347
+HIP_CASES = [
+    (512, 256, 64, t3.MCG, 16, "f32"), (512, 256, 64, t3.MUL1, 16, "f32"), (512, 384, 32, t3.MCG, 16, "f16"),
+    (512, 256, 48, t3.MUL1, 16, "f16"), (512, 256, 36, t3.MCG, 16, "f32"), (512, 256, 128, t3.MCG, 12, "f16"),
+    (2560, 640, 80, t3.MUL1, 16, "bf16"), (4096, 2048, 64, t3.MCG, 16, "bf16"),
+]
+
+
+@pytest.mark.parametrize("case", HIP_CASES)
+def test_reference_gemv_cases(case):
+    in_dim, out_dim, n, cb, w, dt = case
+    for rows in (1, 2, 3, 4, 5, 6, 7, 8, 9, 11, 16, 17, 31, 32):
+        got, ref, _ = run_case(in_dim, out_dim, n, cb, w, dt, rows, seed=in_dim + n + rows)
+        check(got, ref, dt, (case, rows))
+    assert t3.device_error() == 0
+
+
+def test_config1_single_linear():
+    """BASELINE config 1: 4096 x 4096, K = 4, seed 0, +-1 signs, one f16 row."""
+    got, ref, _ = run_case(4096, 4096, 64, t3.MUL1, 16, "f16", 1, seed=0, scaled=False)
+    check(got, ref, "f16", "config 1")
+
+
+@pytest.mark.parametrize("shape", [(2048, 2048), (2048, 6144), (6144, 2048)])
+@pytest.mark.parametrize("k", [1, 2, 3, 4, 5, 6, 8])
+def test_config2_sweep_decode_rows(shape, k):
+    """BASELINE config 2 at the in-register rows {1, 8, 17, 32}, +-1 signs."""
+    in_dim, out_dim = shape
+    for rows in (1, 8, 17, 32):
+        got, ref, _ = run_case(in_dim, out_dim, 16 * k, t3.MUL1, 16, "f16", rows, seed=7 * k + rows, scaled=False)
+        check(got, ref, "f16", (shape, k, rows))
+    assert t3.device_error() == 0
+
+
+def test_rows_past_the_register_path_still_match():
+    """rows > 32 run as chunks of 32; rows of the reference's wider cases (src/core/gpu_test.zig:396)."""
+    for rows in (33, 40, 129, 200):
+        got, ref, _ = run_case(512, 256, 64, t3.MUL1, 16, "f16", rows, seed=rows)
+        check(got, ref, "f16", rows)
+
+
+def test_a_row_alone_equals_the_row_in_a_batch():
+    """A row's bytes do not depend on its neighbours (src/hip_tests.zig:330-345, src/core/gpu_test.zig:708)."""
+    in_dim, out_dim, n = 2560, 640, 80
+    trellis, suh, svh = synth.linear(3, in_dim, out_dim, n, scaled=True)
+    t, a, b = dev(trellis), dev(suh), dev(svh)
+    for rows in (7, 16, 32):
+        x = dev(synth.activations(40 + rows, rows, in_dim))
+        full = bits16(t3.linear(x, t, a, b))
+        for r in (0, rows // 2, rows - 1):
+            alone = bits16(t3.linear(x[r:r + 1].contiguous(), t, a, b))
+            assert np.array_equal(alone[0], full[r]), (rows, r)
+
+
+def test_same_call_twice_same_bytes():
+    trellis, suh, svh = synth.linear(9, 2048, 2048, 48)
+    x = dev(synth.activations(10, 5, 2048))
+    t, a, b = dev(trellis), dev(suh), dev(svh)
+    assert np.array_equal(bits16(t3.linear(x, t, a, b)), bits16(t3.linear(x, t, a, b)))
+
+
+def test_leading_dims_are_rows():
+    trellis, suh, svh = synth.linear(12, 256, 128, 64)
+    x = dev(synth.activations(13, 6, 256))
+    t, a, b = dev(trellis), dev(suh), dev(svh)
+    y2 = t3.linear(x, t, a, b)
+    y3 = t3.linear(x.view(2, 3, 256), t, a, b)
+    assert y3.shape == (2, 3, 128)
+    assert np.array_equal(bits16(y2), bits16(y3).reshape(6, 128))
+
+
+def test_split_choices_agree_within_rounding():
+    """The cluster's K split only changes f32 summation order."""
+    trellis, suh, svh = synth.linear(21, 2048, 512, 64, scaled=True)
+    x = dev(synth.activations(22, 4, 2048))
+    t, a, b = dev(trellis), dev(suh), dev(svh)
+    outs = []
+    try:
+        for split in (1, 2, 4, 8):
+            t3.configure(dense_split=split)
+            outs.append(host_f32(t3.linear(x, t, a, b)))
+    finally:
+        t3.configure()
+    for o in outs[1:]:
+        assert ob.compare(o, outs[0], 2.0 ** -11)["max_ratio"] <= 3e-3
+
+
+def test_small_ring_recycles_stages():
+    """A ring far smaller than the slab forces every stage to be reused many times."""
+    trellis, suh, svh = synth.linear(31, 4096, 256, 128, scaled=True)
+    x = dev(synth.activations(32, 3, 4096))
+    t, a, b = dev(trellis), dev(suh), dev(svh)
+    base = bits16(t3.linear(x, t, a, b))
+    try:
+        t3.configure(ring_bytes=8192, dense_split=1)
+        small = host_f32(t3.linear(x, t, a, b))
+        t3.configure(ring_bytes=8192, dense_split=8)
+        small8 = bits16(t3.linear(x, t, a, b))
+    finally:
+        t3.configure()
+    assert np.array_equal(small8, base)
+    what = ob.reconstruct_inner(trellis, 4096, 256, 128, ob.MUL1)
+    ref = ob.linear_rows_what(host_f32(x), what, suh, svh, 4096, 256)
+    check(small, ref, "f16", "ring of one stage")
+    assert t3.device_error() == 0

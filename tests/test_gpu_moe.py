@@ -1,0 +1,179 @@
+"""The routed-expert chain at decode rows against the oracle's ref.moeRow, at the geometries of the reference's own GPU
+tests (src/hip_tests.zig:451-502, src/core/gpu_test.zig:33-44, src/core/topk_test.zig:33-45) and BASELINE config 3.
+
+Bars: `ref.compare` <= 5e-3 (f32/f16 activations) and <= 1.5e-2 (bf16), the reference's (src/core/gpu_test.zig:46,256),
+plus compareRounded(half ulp of the output dtype) <= 3e-3."""
+import numpy as np
+import pytest
+import torch
+
+import turboexl3_b200 as t3
+from oracle import binding as ob
+from turboexl3_b200 import synth
+
+from gpu_util import HALF_ULP_BF16, HALF_ULP_F16, TORCH_DT, bits16, dev, host_f32, x_as
+
+pytestmark = pytest.mark.gpu
+
+BAR = {"f32": 5e-3, "f16": 5e-3, "bf16": 1.5e-2}
+
+
+def make_bank(seed, experts, hidden, inter, n):
+    arrs = synth.bank(seed, experts, hidden, inter, n)
+    d = {k: dev(v) for k, v in arrs.items()}
+    bank = t3.Bank(t3.Proj(d["gate_t"], d["gate_suh"], d["gate_svh"]), t3.Proj(d["up_t"], d["up_suh"], d["up_svh"]),
+                   t3.Proj(d["down_t"], d["down_suh"], d["down_svh"]))
+    obank = ob.Bank(experts, hidden, inter, n, *[arrs[k] for k in (
+        "gate_t", "gate_suh", "gate_svh", "up_t", "up_suh", "up_svh", "down_t", "down_suh", "down_svh")])
+    return bank, obank
+
+
+def check_moe(got, ref, dt, what):
+    half = HALF_ULP_BF16 if dt == "bf16" else (HALF_ULP_F16 if dt == "f16" else 0.0)
+    assert np.all(np.isfinite(ref)) and np.all(np.isfinite(got)), what
+    c = ob.compare(got, ref)["max_ratio"]
+    r = ob.compare(got, ref, half)["max_ratio"]
+    assert c <= BAR[dt], (what, c, r)
+    assert r <= 3e-3, (what, c, r)
+
+
+def run(bank, obank, rows, topk, dt, dec, seed, limit=0, clamp_at=0, x_scale=1.0):
+    H, E = obank.hidden, obank.experts
+    inds, scores = synth.routing(seed, rows, E, topk)
+    x16 = (synth.activations(seed + 1, rows, H).astype(np.float32) * x_scale).astype(np.float16)
+    x = x_as(x16, dt).view(1, rows, H)
+    di, ds = dev(inds).view(1, rows, topk), dev(scores).view(1, rows, topk)
+    if limit:
+        y = t3.moe_swiglu(x, bank, di, ds, dec, limit, clamp_at)
+    else:
+        y = t3.moe(x, bank, di, ds, dec)
+    assert y.shape == x.shape and y.dtype == x.dtype
+    ref = ob.moe_rows(obank, host_f32(x).reshape(rows, H), inds, scores, dec.codebook, dec.window_bits, float(limit),
+                      clamp_at)
+    return host_f32(y).reshape(rows, H), ref
+
+
+# (hidden, inter, experts, topk, n, codebook, window, dtype): src/hip_tests.zig:451-502
+HIP_CASES = [
+    (512, 256, 12, 4, 64, t3.MCG, 16, "f32"), (512, 256, 12, 4, 64, t3.MUL1, 16, "f16"),
+    (512, 256, 12, 8, 36, t3.MCG, 16, "f32"), (512, 384, 12, 4, 128, t3.MUL1, 12, "f16"),
+    (2560, 640, 16, 10, 48, t3.MUL1, 16, "bf16"),
+]
+
+
+@pytest.mark.parametrize("case", HIP_CASES)
+def test_reference_routed_decode_cases(case):
+    H, I, E, topk, n, cb, w, dt = case
+    bank, obank = make_bank(H + n, E, H, I, n)
+    for rows in (1, 2, 3, 4, 5, 8, 16, 32):
+        got, ref = run(bank, obank, rows, topk, dt, t3.Decode(cb, w), seed=100 + rows)
+        check_moe(got, ref, dt, (case, rows))
+    assert t3.device_error() == 0
+
+
+@pytest.mark.parametrize("n", [32, 40, 48, 64, 80, 128])
+def test_rates_two_rows(n):  # src/core/gpu_test.zig:33-44
+    bank, obank = make_bank(n, 6, 512, 256, n)
+    dec = t3.Decode(t3.MCG, 12) if n in (48, 128) else t3.Decode.mul1
+    got, ref = run(bank, obank, 2, 4, "f16", dec, seed=n)
+    check_moe(got, ref, "f16", n)
+
+
+@pytest.mark.parametrize("topk,experts", [(1, 1), (2, 12), (3, 12)])
+def test_small_topk(topk, experts):  # src/core/topk_test.zig:33-45
+    bank, obank = make_bank(70 + topk, experts, 512, 256, 64)
+    for rows in (1, 3):
+        got, ref = run(bank, obank, rows, topk, "f16", t3.Decode.mul1, seed=rows)
+        check_moe(got, ref, "f16", (topk, experts, rows))
+
+
+def test_config3_hybrid_layer_with_shared_expert():
+    """BASELINE config 3: hidden 2048, 512 experts of width 512, top-10, K = 3, softmax routing renormalised, one shared
+    expert (a one-expert bank at top-1 whose score is the sigmoid gate), rows {1, 4, 16, 32}. The shared output is added at
+    the routed output's rounding point (root.moeWithShared)."""
+    H, I, E, topk, n = 2048, 512, 512, 10, 48
+    bank, obank = make_bank(3, E, H, I, n)
+    sbank, sobank = make_bank(4, 1, H, I, n)
+    dec = t3.Decode.mul1
+    for rows in (1, 4, 16, 32):
+        inds, scores = synth.routing(300 + rows, rows, E, topk)
+        x16 = synth.activations(301 + rows, rows, H)
+        x = dev(x16).view(1, rows, H)
+        gate_logit = np.random.default_rng(302 + rows).standard_normal(rows).astype(np.float32)
+        g = (1.0 / (1.0 + np.exp(-gate_logit))).astype(np.float32)
+        zeros = np.zeros((rows, 1), np.int32)
+        shared = t3.moe(x, sbank, dev(zeros).view(1, rows, 1), dev(g.reshape(rows, 1)).view(1, rows, 1), dec)
+        y = t3.moe_with_shared(x, bank, dev(inds).view(1, rows, topk), dev(scores).view(1, rows, topk), dec, shared)
+        xf = x16.astype(np.float32)
+        routed_ref = ob.moe_rows(obank, xf, inds, scores)
+        shared_ref = ob.moe_rows(sobank, xf, zeros, g.reshape(rows, 1))
+        to16 = lambda a: a.astype(np.float16).astype(np.float32)
+        ref = to16(routed_ref) + to16(shared_ref)
+        check_moe(host_f32(shared).reshape(rows, H), shared_ref, "f16", ("shared", rows))
+        check_moe(host_f32(y).reshape(rows, H), ref, "f16", ("layer", rows))
+    assert t3.device_error() == 0
+
+
+def test_rows_sharing_experts_and_row_alone_bytes():
+    """Few experts, many rows: most experts serve several rows from one decode. A row's bytes are the same alone and in
+    the batch (src/core/gpu_test.zig:1139, src/hip_tests.zig:489-500)."""
+    H, I, E, topk, n = 512, 256, 5, 4, 64
+    bank, obank = make_bank(17, E, H, I, n)
+    rows = 16
+    inds, scores = synth.routing(18, rows, E, topk)
+    x = dev(synth.activations(19, rows, H)).view(1, rows, H)
+    di, ds = dev(inds).view(1, rows, topk), dev(scores).view(1, rows, topk)
+    full = bits16(t3.moe(x, bank, di, ds)).reshape(rows, H)
+    ref = ob.moe_rows(obank, host_f32(x).reshape(rows, H), inds, scores)
+    check_moe(host_f32(t3.moe(x, bank, di, ds)).reshape(rows, H), ref, "f16", "shared experts")
+    for r in (0, 7, 15):
+        alone = bits16(t3.moe(x[:, r:r + 1].contiguous(), bank, di[:, r:r + 1].contiguous(),
+                              ds[:, r:r + 1].contiguous())).reshape(H)
+        assert np.array_equal(alone, full[r]), r
+
+
+def test_duplicate_expert_in_one_row():
+    """The same expert twice in a row's slots (more members than rows): both slots are computed and summed."""
+    H, I, E, n = 512, 256, 3, 64
+    bank, obank = make_bank(23, E, H, I, n)
+    inds = np.array([[1, 1, 2, 1]], np.int32)
+    scores = np.array([[0.4, 0.3, 0.2, 0.1]], np.float32)
+    x = dev(synth.activations(24, 1, H)).view(1, 1, H)
+    y = t3.moe(x, bank, dev(inds).view(1, 1, 4), dev(scores).view(1, 1, 4))
+    ref = ob.moe_rows(obank, host_f32(x).reshape(1, H), inds, scores)
+    check_moe(host_f32(y).reshape(1, H), ref, "f16", "duplicates")
+
+
+@pytest.mark.parametrize("clamp_at", [t3.CLAMP_GATE_IN, t3.CLAMP_SILU_OUT])
+def test_clamped_swiglu(clamp_at):
+    """root.moeClamped / moeLing's clamp (ref.moeRowClampedAt, src/core/ref.zig:154-190) with inputs scaled so a good share
+    of gates and ups clamp (the reference's clamped test does the same, src/models/deepseek_v41/clamped_test.zig:1-11)."""
+    H, I, E, topk, n = 512, 384, 8, 4, 48
+    bank, obank = make_bank(31, E, H, I, n)
+    for rows in (1, 4, 16):
+        got, ref = run(bank, obank, rows, topk, "f16", t3.Decode.mul1, seed=500 + rows, limit=1, clamp_at=clamp_at,
+                       x_scale=2.0)
+        check_moe(got, ref, "f16", (clamp_at, rows))
+        unclamped = ob.moe_rows(obank, host_f32(dev(
+            (synth.activations(501 + rows, rows, H).astype(np.float32) * 2.0).astype(np.float16))), *synth.routing(
+                500 + rows, rows, E, topk))
+        assert ob.compare(unclamped, ref)["max_ratio"] > 1e-2  # the clamp did something
+    with pytest.raises(t3.Exl3Error) as e:
+        x = dev(synth.activations(1, 1, H)).view(1, 1, H)
+        t3.moe_clamped(x, bank, dev(np.zeros((1, 1, 1), np.int32)), dev(np.ones((1, 1, 1), np.float32)), t3.Decode.mul1, 0)
+    assert e.value.name == "InvalidExl3Clamp"
+
+
+def test_score_and_index_dtypes():
+    H, I, E, topk, n = 512, 256, 6, 4, 64
+    bank, obank = make_bank(41, E, H, I, n)
+    rows = 3
+    inds, scores = synth.routing(42, rows, E, topk)
+    x = dev(synth.activations(43, rows, H)).view(1, rows, H)
+    base = bits16(t3.moe(x, bank, dev(inds).view(1, rows, topk), dev(scores).view(1, rows, topk)))
+    u32 = torch.from_numpy(inds.astype(np.uint32)).cuda().view(1, rows, topk)
+    assert np.array_equal(bits16(t3.moe(x, bank, u32, dev(scores).view(1, rows, topk))), base)
+    s16 = torch.from_numpy(scores).to(torch.float16)
+    y16 = t3.moe(x, bank, dev(inds).view(1, rows, topk), s16.cuda().view(1, rows, topk))
+    ref = ob.moe_rows(obank, host_f32(x).reshape(rows, H), inds, s16.float().numpy())
+    check_moe(host_f32(y16).reshape(rows, H), ref, "f16", "f16 scores")

@@ -1,0 +1,14 @@
+"""B200-native EXL3 projection engine: hand-written sm_100a kernels behind turboexl3's projection entry points.
+
+The product is libt3.so (C ABI: include/t3.h); this package is its Python host layer, mirroring the reference's module
+API (src/root.zig). Importing the package does not load the library; the first call does, and fails loudly if it has not
+been built (`python -m turboexl3_b200.build`).
+"""
+from .api import (CLAMP_GATE_IN, CLAMP_SILU_OUT, DECODE_ROWS_MAX, MCG, MUL1, REDUCE_MAX_TOPK, Bank, Decode, Exl3Error,
+                  Proj, codebook_table, configure, dequantize, device_error, launch_count, lib, linear, moe,
+                  moe_clamped, moe_swiglu, moe_with_shared, parse_expert_quant, status_name, trellis_admitted)
+
+__all__ = ["CLAMP_GATE_IN", "CLAMP_SILU_OUT", "DECODE_ROWS_MAX", "MCG", "MUL1", "REDUCE_MAX_TOPK", "Bank", "Decode",
+           "Exl3Error", "Proj", "codebook_table", "configure", "dequantize", "device_error", "launch_count", "lib",
+           "linear", "moe", "moe_clamped", "moe_swiglu", "moe_with_shared", "parse_expert_quant", "status_name",
+           "trellis_admitted"]

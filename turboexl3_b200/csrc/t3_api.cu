@@ -1,0 +1,471 @@
+// The C ABI (include/t3.h): admission, launch planning and dispatch. Every refusal happens before any launch, under the
+// reference's error names (turboexl3 src/root.zig:93-141, 322-351, 839-904).
+#include <atomic>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "../../include/t3.h"
+#include "t3_gemv.cuh"
+#include "t3_internal.h"
+
+namespace t3 {
+
+cudaError_t launch_dense_gemv_cb0(const DenseArgs&, cudaStream_t);
+cudaError_t launch_dense_gemv_cb1(const DenseArgs&, cudaStream_t);
+cudaError_t launch_moe_gate_up_cb0(const MoeArgs&, cudaStream_t);
+cudaError_t launch_moe_gate_up_cb1(const MoeArgs&, cudaStream_t);
+cudaError_t launch_moe_down_cb0(const MoeArgs&, cudaStream_t);
+cudaError_t launch_moe_down_cb1(const MoeArgs&, cudaStream_t);
+
+namespace {
+
+std::atomic<uint64_t> g_launches{0};
+
+__device__ uint32_t g_dev_error_word;
+
+std::mutex g_mu;
+t3_config g_cfg = {1, 0, 0};
+uint32_t* g_err_ptr[64] = {};
+
+constexpr uint32_t kSmemCap = 220u * 1024u;      // dynamic shared memory a GEMV CTA may ask for
+constexpr uint32_t kDefaultRing = 64u * 1024u;
+
+uint32_t* dev_error_ptr() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (!g_err_ptr[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_dev_error_word) != cudaSuccess) return nullptr;
+        g_err_ptr[dev] = static_cast<uint32_t*>(p);
+    }
+    return g_err_ptr[dev];
+}
+
+uint32_t pow2_at_most(uint32_t v, uint32_t cap) {
+    uint32_t s = 1;
+    while (s * 2u <= v && s * 2u <= cap) s *= 2u;
+    return s;
+}
+
+uint32_t largest_slice(uint32_t nb, uint32_t split) {
+    uint32_t mx = 0;
+    for (uint32_t r = 0; r < split; ++r) {
+        uint32_t b0, b1;
+        slice_blocks(nb, split, r, b0, b1);
+        mx = b1 - b0 > mx ? b1 - b0 : mx;
+    }
+    return mx * 128u;
+}
+
+// The ring of one GEMV CTA: stages of about 8 KB, as many as the slab needs or the budget holds.
+bool plan_ring(uint32_t row_cap, uint32_t slice_max, uint32_t n, RingPlan& ring) {
+    const uint32_t row_bytes = 16u * n, nrows = slice_max / 16u;
+    uint32_t stage_rows = 8192u / row_bytes;
+    stage_rows = stage_rows < 1u ? 1u : (stage_rows > 32u ? 32u : stage_rows);
+    stage_rows = stage_rows > nrows ? nrows : stage_rows;
+    const uint32_t stage_bytes = stage_rows * row_bytes;
+    const uint32_t need = (nrows + stage_rows - 1u) / stage_rows;
+    const uint32_t fixed = gemv_smem(row_cap, slice_max, stage_bytes, 0).total;
+    if (fixed + stage_bytes > kSmemCap) return false;
+    uint32_t budget = g_cfg.ring_bytes ? g_cfg.ring_bytes : kDefaultRing;
+    if (budget > kSmemCap - fixed) budget = kSmemCap - fixed;
+    uint32_t stages = budget / stage_bytes;
+    stages = stages < 1u ? 1u : stages;
+    stages = stages > need ? need : stages;
+    stages = stages > kMaxStages ? kMaxStages : stages;
+    ring.stage_rows = stage_rows;
+    ring.stages = stages;
+    return true;
+}
+
+bool dtype_ok(int dt) { return dt == T3_F32 || dt == T3_F16 || dt == T3_BF16; }
+size_t dtype_size(int dt) { return dt == T3_F32 ? 4 : 2; }
+
+int decode_mask(t3_decode dec, uint32_t& mask) {
+    if (dec.codebook != T3_MUL1 && dec.codebook != T3_MCG) return T3_ENGINE_NOT_IMPLEMENTED;
+    if (dec.window_bits < 8 || dec.window_bits > 16) return T3_WINDOW_UNSUPPORTED;
+    mask = (1u << dec.window_bits) - 1u;
+    return T3_OK;
+}
+
+bool rate_ok(int n) { return n >= 16 && n <= 128 && n % 2 == 0; }
+
+int cuda_status(cudaError_t rc) { return rc == cudaSuccess ? T3_OK : T3_CUDA_ERROR; }
+
+}  // namespace
+
+uint32_t row_cap_for(uint32_t rows) { return rows <= 8u ? 8u : (rows <= 16u ? 16u : 32u); }
+
+uint32_t gemv_smem_bytes(uint32_t row_cap, uint32_t slice_max, uint32_t n, RingPlan ring) {
+    return gemv_smem(row_cap, slice_max, ring.stage_rows * 16u * n, ring.stages).total;
+}
+
+cudaError_t launch_dense_gemv(const DenseArgs& a, int codebook, cudaStream_t stream) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return codebook == T3_MCG ? launch_dense_gemv_cb1(a, stream) : launch_dense_gemv_cb0(a, stream);
+}
+cudaError_t launch_moe_gate_up(const MoeArgs& a, int codebook, cudaStream_t stream) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return codebook == T3_MCG ? launch_moe_gate_up_cb1(a, stream) : launch_moe_gate_up_cb0(a, stream);
+}
+cudaError_t launch_moe_down(const MoeArgs& a, int codebook, cudaStream_t stream) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return codebook == T3_MCG ? launch_moe_down_cb1(a, stream) : launch_moe_down_cb0(a, stream);
+}
+
+}  // namespace t3
+
+using namespace t3;
+
+extern "C" {
+
+const char* t3_status_name(int status) {
+    switch (status) {
+        case T3_OK: return "Ok";
+        case T3_BAD_EXL3_SHAPE: return "BadExl3Shape";
+        case T3_BAD_EXL3_DTYPE: return "BadExl3Dtype";
+        case T3_ENGINE_NOT_IMPLEMENTED: return "Exl3EngineNotImplemented";
+        case T3_ENGINE_CACHE_FULL: return "Exl3EngineCacheFull";
+        case T3_GATE_UP_RATE_MISMATCH: return "Exl3GateUpRateMismatch";
+        case T3_INVALID_CLAMP: return "InvalidExl3Clamp";
+        case T3_INVALID_CONFIG: return "InvalidTurboexl3Config";
+        case T3_KERNEL_CREATE_FAILED: return "KernelCreateFailed";
+        case T3_CUDA_ERROR: return "CudaError";
+        case T3_TOPK_EXCEEDS_REDUCE_BANK: return "Exl3TopKExceedsReduceBank";
+        case T3_WORKSPACE_TOO_SMALL: return "WorkspaceTooSmall";
+        case T3_EXPERT_LAYOUT_UNSUPPORTED: return "ExpertLayoutUnsupported";
+        case T3_WINDOW_UNSUPPORTED: return "Exl3WindowUnsupported";
+        case T3_NULL_POINTER: return "NullPointer";
+        default: return "Unknown";
+    }
+}
+
+int t3_uses_prefill_arm(size_t rows) { return rows > T3_DECODE_ROWS_MAX; }
+
+int t3_admit_topk(uint32_t topk) { return topk > T3_REDUCE_MAX_TOPK ? T3_TOPK_EXCEEDS_REDUCE_BANK : T3_OK; }
+
+int t3_trellis_admitted(const int* shape, int ndim, uint32_t experts, uint32_t in_dim, uint32_t out_dim, uint32_t n) {
+    if (!shape || ndim != 4) return 0;
+    for (int i = 0; i < 4; ++i)
+        if (shape[i] <= 0) return 0;
+    if (in_dim % 16u != 0 || out_dim % 16u != 0) return 0;
+    if ((uint32_t)shape[0] != experts || (uint32_t)shape[1] != in_dim / 16u || (uint32_t)shape[2] != out_dim / 16u) return 0;
+    if (!rate_ok(shape[3])) return 0;
+    return (uint32_t)shape[3] <= n;
+}
+
+// ---- expert_quant ---------------------------------------------------------------------------------------------------
+
+namespace {
+
+// the value text of `"key":` inside [begin, end): a string's contents, or a bare number / literal
+bool json_value(const char* begin, const char* end, const char* key, std::string& out, bool& is_string) {
+    const std::string pat = std::string("\"") + key + "\"";
+    const char* p = begin;
+    while (p < end) {
+        const char* hit = static_cast<const char*>(memmem(p, (size_t)(end - p), pat.data(), pat.size()));
+        if (!hit) return false;
+        const char* q = hit + pat.size();
+        while (q < end && (*q == ' ' || *q == '\t' || *q == '\n' || *q == '\r')) ++q;
+        if (q < end && *q == ':') {
+            ++q;
+            while (q < end && (*q == ' ' || *q == '\t' || *q == '\n' || *q == '\r')) ++q;
+            if (q >= end) return false;
+            if (*q == '"') {
+                const char* r = ++q;
+                while (r < end && *r != '"') ++r;
+                if (r >= end) return false;
+                out.assign(q, r);
+                is_string = true;
+                return true;
+            }
+            const char* r = q;
+            while (r < end && *r != ',' && *r != '}' && *r != ' ' && *r != '\n' && *r != '\r' && *r != '\t') ++r;
+            out.assign(q, r);
+            is_string = false;
+            return !out.empty();
+        }
+        p = hit + 1;
+    }
+    return false;
+}
+
+}  // namespace
+
+int t3_parse_expert_quant(const char* json, size_t len, t3_spec* out) {
+    if (!json || !out) return T3_NULL_POINTER;
+    const char* end = json + len;
+    static const char kKey[] = "\"expert_quant\"";
+    const char* blk = static_cast<const char*>(memmem(json, len, kKey, sizeof kKey - 1));
+    if (!blk) return T3_EXPERT_LAYOUT_UNSUPPORTED;
+    const char* open = blk + sizeof kKey - 1;
+    while (open < end && *open != '{' && (*open == ':' || *open == ' ' || *open == '\n' || *open == '\t' || *open == '\r')) ++open;
+    if (open >= end || *open != '{') return T3_EXPERT_LAYOUT_UNSUPPORTED;
+    const char* close = open;
+    int depth = 0;
+    for (; close < end; ++close) {
+        if (*close == '{') ++depth;
+        if (*close == '}' && --depth == 0) break;
+    }
+    if (close >= end) return T3_EXPERT_LAYOUT_UNSUPPORTED;
+    std::string v;
+    bool is_str = false;
+    if (!json_value(open, close + 1, "format", v, is_str) || !is_str || v != "exl3") return T3_EXPERT_LAYOUT_UNSUPPORTED;
+    if (!json_value(open, close + 1, "k", v, is_str) || is_str) return T3_EXPERT_LAYOUT_UNSUPPORTED;
+    char* tail = nullptr;
+    const double k = strtod(v.c_str(), &tail);
+    if (tail == v.c_str() || *tail != '\0') return T3_EXPERT_LAYOUT_UNSUPPORTED;
+    const double scaled = k * 16.0, rounded = std::round(scaled);
+    if (std::fabs(scaled - rounded) > 1e-6 || rounded < 0 || rounded > 1024) return T3_EXPERT_LAYOUT_UNSUPPORTED;
+    if (!rate_ok((int)rounded)) return T3_EXPERT_LAYOUT_UNSUPPORTED;
+    if (!json_value(open, close + 1, "codebook", v, is_str) || !is_str) return T3_EXPERT_LAYOUT_UNSUPPORTED;
+    int cb;
+    if (v == "mul1") cb = T3_MUL1;
+    else if (v == "mcg") cb = T3_MCG;
+    else return T3_EXPERT_LAYOUT_UNSUPPORTED;
+    int window = 16;
+    if (json_value(open, close + 1, "window", v, is_str)) {
+        if (is_str) return T3_WINDOW_UNSUPPORTED;
+        char* t2 = nullptr;
+        const long w = strtol(v.c_str(), &t2, 10);
+        if (t2 == v.c_str() || *t2 != '\0' || w < 8 || w > 16) return T3_WINDOW_UNSUPPORTED;
+        window = (int)w;
+    }
+    out->n = (uint32_t)rounded;
+    out->codebook = cb;
+    out->window_bits = window;
+    return T3_OK;
+}
+
+// ---- configuration --------------------------------------------------------------------------------------------------
+
+void t3_config_default(t3_config* out) {
+    if (!out) return;
+    out->prefill = 1;
+    out->ring_bytes = 0;
+    out->dense_split = 0;
+}
+
+int t3_configure(const t3_config* cfg) {
+    if (!cfg) return T3_NULL_POINTER;
+    const uint32_t s = cfg->dense_split;
+    if (s != 0 && s != 1 && s != 2 && s != 4 && s != 8) return T3_INVALID_CONFIG;
+    if (cfg->ring_bytes != 0 && (cfg->ring_bytes < 4096u || cfg->ring_bytes > kSmemCap)) return T3_INVALID_CONFIG;
+    if (cfg->prefill != 0 && cfg->prefill != 1) return T3_INVALID_CONFIG;
+    std::lock_guard<std::mutex> lock(g_mu);
+    g_cfg = *cfg;
+    return T3_OK;
+}
+
+int t3_device_error(void* stream, uint32_t* bits_out, int clear) {
+    uint32_t* p = dev_error_ptr();
+    if (!p) return T3_CUDA_ERROR;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    uint32_t bits = 0;
+    if (cudaMemcpyAsync(&bits, p, sizeof bits, cudaMemcpyDeviceToHost, s) != cudaSuccess) return T3_CUDA_ERROR;
+    if (clear && cudaMemsetAsync(p, 0, sizeof bits, s) != cudaSuccess) return T3_CUDA_ERROR;
+    if (cudaStreamSynchronize(s) != cudaSuccess) return T3_CUDA_ERROR;
+    if (bits_out) *bits_out = bits;
+    return T3_OK;
+}
+
+uint64_t t3_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+// ---- W_hat ----------------------------------------------------------------------------------------------------------
+
+int t3_dequant(const void* trellis, int in_dim, int out_dim, int n, t3_decode dec, void* w_hat, void* stream) {
+    if (!trellis || !w_hat) return T3_NULL_POINTER;
+    if (in_dim <= 0 || out_dim <= 0 || in_dim % 128 != 0 || out_dim % 128 != 0 || !rate_ok(n)) return T3_BAD_EXL3_SHAPE;
+    uint32_t mask;
+    if (int rc = decode_mask(dec, mask)) return rc;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cuda_status(launch_dequant(static_cast<const uint8_t*>(trellis), (uint32_t)in_dim, (uint32_t)out_dim,
+                                      (uint32_t)n, mask, dec.codebook, w_hat, static_cast<cudaStream_t>(stream)));
+}
+
+int t3_codebook_table(t3_decode dec, void* out, void* stream) {
+    if (!out) return T3_NULL_POINTER;
+    uint32_t mask;
+    if (int rc = decode_mask(dec, mask)) return rc;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cuda_status(launch_codebook_table(dec.codebook, mask, static_cast<uint16_t*>(out), static_cast<cudaStream_t>(stream)));
+}
+
+// ---- dense linear ---------------------------------------------------------------------------------------------------
+
+size_t t3_linear_workspace_bytes(size_t rows, int in_dim, int out_dim, int n) {
+    (void)rows;
+    (void)in_dim;
+    (void)out_dim;
+    (void)n;
+    return 0;  // the decode-row kernel keeps everything on chip
+}
+
+int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, const void* suh, const void* svh,
+              int in_dim, int out_dim, int n, t3_decode dec, void* y, void* workspace, size_t workspace_bytes,
+              void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    if (!x || !trellis || !suh || !svh || !y) return T3_NULL_POINTER;
+    if (in_dim <= 0 || out_dim <= 0 || in_dim % 128 != 0 || out_dim % 128 != 0 || !rate_ok(n) || rows < 1 ||
+        rows > (size_t)1 << 30)
+        return T3_BAD_EXL3_SHAPE;
+    if (!dtype_ok(x_dtype)) return T3_BAD_EXL3_DTYPE;
+    uint32_t mask;
+    if (int rc = decode_mask(dec, mask)) return rc;
+    t3_config cfg;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        cfg = g_cfg;
+    }
+    if (rows > T3_DECODE_ROWS_MAX && !cfg.prefill) return T3_ENGINE_NOT_IMPLEMENTED;
+
+    DenseArgs a = {};
+    a.trellis = static_cast<const uint8_t*>(trellis);
+    a.suh = suh;
+    a.svh = svh;
+    a.in = (uint32_t)in_dim;
+    a.out = (uint32_t)out_dim;
+    a.n = (uint32_t)n;
+    a.mask = mask;
+    a.x_dt = x_dtype;
+    const uint32_t nb = a.in / 128u;
+    a.split = cfg.dense_split ? pow2_at_most(nb, cfg.dense_split) : pow2_at_most(nb, 8u);
+    a.slice_max = largest_slice(nb, a.split);
+    a.err = dev_error_ptr();
+    // rows past the in-register capacity run as chunks of it (each chunk decodes the matrix again)
+    const size_t cap = T3_DECODE_ROWS_MAX;
+    const size_t elt = dtype_size(x_dtype);
+    for (size_t r0 = 0; r0 < rows; r0 += cap) {
+        a.rows = (uint32_t)(rows - r0 < cap ? rows - r0 : cap);
+        if (!plan_ring(row_cap_for(a.rows), a.slice_max, a.n, a.ring)) return T3_ENGINE_NOT_IMPLEMENTED;
+        a.x = static_cast<const uint8_t*>(x) + r0 * a.in * elt;
+        a.y = static_cast<uint8_t*>(y) + r0 * a.out * elt;
+        if (int rc = cuda_status(launch_dense_gemv(a, dec.codebook, static_cast<cudaStream_t>(stream)))) return rc;
+    }
+    return T3_OK;
+}
+
+// ---- routed experts -------------------------------------------------------------------------------------------------
+
+namespace {
+
+int validate_bank(const t3_bank* b, int hidden_of_x) {
+    if (!b) return T3_NULL_POINTER;
+    const t3_proj* ps[3] = {&b->gate, &b->up, &b->down};
+    for (const t3_proj* p : ps)
+        if (!p->trellis || !p->suh || !p->svh) return T3_NULL_POINTER;
+    if (b->experts <= 0 || b->hidden <= 0 || b->inter <= 0 || b->hidden % 128 != 0 || b->inter % 128 != 0 ||
+        b->hidden != hidden_of_x || !rate_ok(b->n_gate) || !rate_ok(b->n_up) || !rate_ok(b->n_down))
+        return T3_BAD_EXL3_SHAPE;
+    if (b->n_gate != b->n_up) return T3_GATE_UP_RATE_MISMATCH;
+    if (b->n_gate != b->n_down) return T3_ENGINE_NOT_IMPLEMENTED;  // src/root.zig:841
+    return T3_OK;
+}
+
+size_t align256(size_t v) { return (v + 255u) & ~(size_t)255u; }
+
+int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds, const void* scores,
+             int scores_dtype, int topk, t3_decode dec, uint32_t limit, int clamp_at, const void* shared, void* y,
+             void* workspace, size_t workspace_bytes, void* stream) {
+    if (!x || !inds || !scores || !y) return T3_NULL_POINTER;
+    if (rows < 1 || rows > (size_t)1 << 30 || topk <= 0) return T3_BAD_EXL3_SHAPE;
+    if (topk > T3_REDUCE_MAX_TOPK) return T3_BAD_EXL3_SHAPE;  // validateCall, src/root.zig:131
+    if (int rc = validate_bank(bank, bank ? bank->hidden : 0)) return rc;
+    if (!dtype_ok(x_dtype) || !dtype_ok(scores_dtype)) return T3_BAD_EXL3_DTYPE;
+    if (clamp_at != T3_CLAMP_GATE_IN && clamp_at != T3_CLAMP_SILU_OUT) return T3_INVALID_CLAMP;
+    uint32_t mask;
+    if (int rc = decode_mask(dec, mask)) return rc;
+    if (rows > T3_DECODE_ROWS_MAX) return T3_ENGINE_NOT_IMPLEMENTED;  // the prefill chain is a separate engine
+    const size_t need = t3_moe_workspace_bytes(rows, topk, bank);
+    if (!workspace || workspace_bytes < need) return T3_WORKSPACE_TOO_SMALL;
+
+    MoeArgs a = {};
+    a.x = x;
+    a.x_dt = x_dtype;
+    a.inds = inds;
+    a.scores = scores;
+    a.score_dt = scores_dtype;
+    a.gate_t = static_cast<const uint8_t*>(bank->gate.trellis);
+    a.up_t = static_cast<const uint8_t*>(bank->up.trellis);
+    a.down_t = static_cast<const uint8_t*>(bank->down.trellis);
+    a.gate_suh = bank->gate.suh;
+    a.gate_svh = bank->gate.svh;
+    a.up_suh = bank->up.suh;
+    a.up_svh = bank->up.svh;
+    a.down_suh = bank->down.suh;
+    a.down_svh = bank->down.svh;
+    a.experts = (uint32_t)bank->experts;
+    a.hidden = (uint32_t)bank->hidden;
+    a.inter = (uint32_t)bank->inter;
+    a.topk = (uint32_t)topk;
+    a.rows = (uint32_t)rows;
+    a.n = (uint32_t)bank->n_gate;
+    a.mask = mask;
+    a.limit = (float)limit;
+    a.clamp_at = clamp_at;
+    const size_t slots = rows * (size_t)topk;
+    a.hd = workspace;
+    a.v = static_cast<uint8_t*>(workspace) + align256(slots * a.inter * 2u);
+    a.y = y;
+    a.shared = shared;
+    const uint32_t rm = row_cap_for(a.rows);
+    a.split_gu = pow2_at_most(a.hidden / 128u, 4u);
+    a.slice_max_gu = largest_slice(a.hidden / 128u, a.split_gu);
+    a.split_d = pow2_at_most(a.inter / 128u, 8u);
+    a.slice_max_d = largest_slice(a.inter / 128u, a.split_d);
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        if (!plan_ring(rm, a.slice_max_gu, a.n, a.ring_gu) || !plan_ring(rm, a.slice_max_d, a.n, a.ring_d))
+            return T3_ENGINE_NOT_IMPLEMENTED;
+    }
+    a.err = dev_error_ptr();
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (int rc = cuda_status(launch_moe_gate_up(a, dec.codebook, s))) return rc;
+    if (int rc = cuda_status(launch_moe_down(a, dec.codebook, s))) return rc;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cuda_status(launch_moe_merge(a, s));
+}
+
+}  // namespace
+
+size_t t3_moe_workspace_bytes(size_t rows, int topk, const t3_bank* bank) {
+    if (!bank || topk <= 0 || bank->inter <= 0 || bank->hidden <= 0) return 0;
+    const size_t slots = rows * (size_t)topk;
+    return align256(slots * (size_t)bank->inter * 2u) + align256(slots * (size_t)bank->hidden * 2u);
+}
+
+int t3_moe(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds, const void* scores,
+           int scores_dtype, int topk, t3_decode dec, void* y, void* workspace, size_t workspace_bytes, void* stream) {
+    return moe_call(x, x_dtype, rows, bank, inds, scores, scores_dtype, topk, dec, 0, T3_CLAMP_GATE_IN, nullptr, y,
+                    workspace, workspace_bytes, stream);
+}
+
+int t3_moe_swiglu(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds, const void* scores,
+                  int scores_dtype, int topk, t3_decode dec, uint32_t limit, int clamp_at, void* y, void* workspace,
+                  size_t workspace_bytes, void* stream) {
+    return moe_call(x, x_dtype, rows, bank, inds, scores, scores_dtype, topk, dec, limit, clamp_at, nullptr, y, workspace,
+                    workspace_bytes, stream);
+}
+
+int t3_moe_clamped(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds, const void* scores,
+                   int scores_dtype, int topk, t3_decode dec, int limit, void* y, void* workspace,
+                   size_t workspace_bytes, void* stream) {
+    if (limit <= 0 || limit > 128) return T3_INVALID_CLAMP;
+    return moe_call(x, x_dtype, rows, bank, inds, scores, scores_dtype, topk, dec, (uint32_t)limit, T3_CLAMP_GATE_IN,
+                    nullptr, y, workspace, workspace_bytes, stream);
+}
+
+int t3_moe_with_shared(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds,
+                       const void* scores, int scores_dtype, int topk, t3_decode dec, const void* shared, void* y,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+    if (!shared) return T3_NULL_POINTER;
+    return moe_call(x, x_dtype, rows, bank, inds, scores, scores_dtype, topk, dec, 0, T3_CLAMP_GATE_IN, shared, y,
+                    workspace, workspace_bytes, stream);
+}
+
+}  // extern "C"

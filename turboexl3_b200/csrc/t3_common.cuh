@@ -1,0 +1,129 @@
+// Device helpers shared by every kernel group: activation loads and stores, the 128-point Hadamard on a warp, the
+// warp-level tensor-core step, and the mbarrier / bulk-copy plumbing with bounded waits.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "t3_lane.cuh"
+
+namespace t3 {
+
+// activation dtypes, numbered as the reference's kernels number them (src/kernels/hip/common.hpp:21)
+enum Dtype : int { kF32 = 0, kF16 = 1, kBf16 = 2 };
+
+constexpr float kHadScale = 0.08838834764831845f;  // 1 / sqrt(128), format.zig:14
+
+// bits of the device error word (see t3.h: t3_device_error)
+enum DevError : uint32_t {
+    kErrFullWait = 1u,    // a consumer gave up waiting for a bulk copy to land
+    kErrEmptyWait = 2u,   // the producer gave up waiting for a ring slot
+    kErrMmaWait = 4u,     // a tensor-core completion never arrived
+    kErrTmemAlloc = 8u,   // tensor memory could not be allocated
+};
+
+__device__ __forceinline__ float round_half(float v) { return __half2float(__float2half_rn(v)); }
+
+// element i of an activation array as f32
+__device__ __forceinline__ float load_act(const void* p, int dt, size_t i) {
+    if (dt == kF32) return static_cast<const float*>(p)[i];
+    if (dt == kF16) return __half2float(static_cast<const __half*>(p)[i]);
+    return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+// v into element i of an array of dtype dt (round to nearest even)
+__device__ __forceinline__ void store_act(void* p, int dt, size_t i, float v) {
+    if (dt == kF32) static_cast<float*>(p)[i] = v;
+    else if (dt == kF16) static_cast<__half*>(p)[i] = __float2half_rn(v);
+    else static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+
+// Unscaled Walsh-Hadamard of a 128-block spread over a warp: lane L holds elements L + 32 j in v[j]. Index bits 0-4
+// are butterflies across lanes, bits 5-6 inside the lane. (format.hadamard128, format.zig:265-273, is the dense
+// 128x128 sum this equals up to f32 summation order.)
+__device__ __forceinline__ void h128_warp(float (&v)[4], uint32_t lane) {
+#pragma unroll
+    for (uint32_t bit = 1; bit < 32u; bit <<= 1) {
+        const bool upper = (lane & bit) != 0u;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float other = __shfl_xor_sync(0xFFFFFFFFu, v[j], bit);
+            v[j] = upper ? other - v[j] : v[j] + other;
+        }
+    }
+    const float s01 = v[0] + v[1], d01 = v[0] - v[1], s23 = v[2] + v[3], d23 = v[2] - v[3];
+    v[0] = s01 + s23;
+    v[1] = d01 + d23;
+    v[2] = s01 - s23;
+    v[3] = d01 - d23;
+}
+
+// D += A (16x16, row) * B (16x8, col), f16 operands, f32 accumulate
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---- shared-memory barriers and bulk copies ------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
+}
+
+// makes freshly initialised barriers visible to the copy engine and to the cluster
+__device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+
+// Waits for the barrier's phase of the given parity, at most kSpinLimit polls (each poll may itself sleep for a
+// hardware-defined time). Returns false after giving up; the caller records the error and carries on to its exit
+// path, so a lost copy never hangs the device.
+constexpr uint32_t kSpinLimit = 1u << 22;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_addr(bar);
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// `bytes` (a multiple of 16) from 16-byte-aligned global memory to 16-byte-aligned shared memory of this CTA; completion
+// is counted on `bar`. No multicast.
+__device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_addr(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+
+// a named barrier over `threads` threads of the CTA (id 1..15; 0 is __syncthreads')
+__device__ __forceinline__ void named_sync(uint32_t id, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__device__ __forceinline__ void report(uint32_t* err, uint32_t bit) {
+    if (err) atomicOr(err, bit);
+}
+
+}  // namespace t3

@@ -1,0 +1,389 @@
+// Decode-row kernels (up to 32 activation rows): the fused dense linear, the routed experts' gate|up and down launches
+// and the score-weighted merge. Compiled once per codebook (-DT3_CB=0 MUL1, 1 MCG) so the two halves build in parallel.
+//
+// Dense linear = one launch: prepare (input rotation) in shared memory, split-K GEMV over a thread-block cluster,
+// output rotation by the cluster's leader. The reference takes three launches for the same values
+// (prep_s -> dgemv -> dfinish, src/core/dense.zig:1229-1252, src/kernels/hip/dense/dense.hip).
+//
+// Routed chain = three launches: gate|up (+ SwiGLU + the down projection's prepare), down (+ its finish), merge.
+// The reference's served chain is four or five (src/core/decode.zig:483-517). Row-slots that share an expert are found
+// inside the kernels (each CTA scans the call's <= 1024 expert ids), so one decode of an expert's tiles feeds every row
+// that routed to it, as the reference's grouped members do (src/core/kernels/decode/gemv_core.metal:4-21).
+#include "t3_gemv.cuh"
+#include "t3_internal.h"
+
+#ifndef T3_CB
+#error "compile with -DT3_CB=0 (MUL1) or -DT3_CB=1 (MCG)"
+#endif
+
+namespace t3 {
+namespace {
+
+constexpr int CB = T3_CB;
+constexpr uint32_t kMaxSlots = 1024;  // 32 rows x 32 top-k
+
+// ---------------------------------------------------------------------------------------------- dense linear
+
+template <int N, int RM>
+__global__ void __launch_bounds__(kGemvThreads, 2) dense_gemv_kernel(const DenseArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t rank = cluster.block_rank(), blk = blockIdx.y;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    uint32_t b0, b1;
+    slice_blocks(a.in / 128u, a.split, rank, b0, b1);
+    const uint32_t nblk = b1 - b0, nrows = nblk * 8u;
+    const uint32_t tile_bytes = 2u * a.n, row_bytes = 16u * a.n, out_tiles = a.out / 16u;
+    const Ring rc{a.ring.stage_rows, a.ring.stages};
+    const GemvSmem L = gemv_smem(RM, a.slice_max, rc.stage_rows * row_bytes, rc.stages);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);
+    uint64_t* empty = full + kMaxStages;
+    __half* xp = reinterpret_cast<__half*>(smem + L.xp);
+    float* partial = reinterpret_cast<float*>(smem + L.partial);
+    uint8_t* ring = smem + L.ring;
+    const uint32_t xstride = a.slice_max + kXpPad;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < rc.stages; ++s) {
+            mbar_init(&full[s], 1u);
+            mbar_init(&empty[s], kConsumerWarps);
+        }
+        mbar_init_fence();
+    }
+    for (uint32_t i = a.rows * xstride + tid; i < RM * xstride; i += kGemvThreads) xp[i] = __float2half_rn(0.0f);
+    __syncthreads();
+
+    uint32_t chunk = 0;
+    if (warp == kConsumerWarps) {
+        const uint8_t* src = a.trellis + ((size_t)(b0 * 8u) * out_tiles + blk * 8u) * tile_bytes;
+        produce_slab(ring, full, empty, src, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, chunk, lane, a.err);
+    } else {
+        for (uint32_t task = warp; task < a.rows * nblk; task += kConsumerWarps) {
+            const uint32_t row = task / nblk, b = task - row * nblk;
+            const uint32_t k0 = (b0 + b) * 128u;
+            prepare_block(a.x, a.x_dt, (size_t)row * a.in + k0, static_cast<const __half*>(a.suh) + k0,
+                          xp + row * xstride + b * 128u, lane);
+        }
+        named_sync(1, 32u * kConsumerWarps);
+        float acc[RowCap<RM>::kMB][2][4] = {};
+        consume_slab<N, CB, RM>(ring, full, empty, nrows, a.n, a.mask, rc, xp, xstride, chunk, warp, lane, acc, a.err);
+        store_partial<RM>(partial, acc, warp, lane);
+    }
+    cluster.sync();
+    if (rank == 0 && warp < kConsumerWarps) {
+        for (uint32_t row = warp; row < a.rows; row += kConsumerWarps) {
+            float v[4];
+            gather_row(cluster, partial, row, 0, 1, a.split, lane, v);
+            finish_block(v, static_cast<const __half*>(a.svh) + blk * 128u, lane);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) store_act(a.y, a.x_dt, (size_t)row * a.out + blk * 128u + lane + 32u * j, v[j]);
+        }
+    }
+    cluster.sync();
+}
+
+// ---------------------------------------------------------------------------------------------- routed experts
+
+struct Members {
+    uint32_t expert, count;
+    bool skip;
+};
+
+// Row-slot j's expert and every row-slot of the call on that expert, ascending, into `members`; skip = an earlier
+// row-slot already owns this expert (its CTAs do the work). All threads of the CTA must call this.
+__device__ __forceinline__ Members find_members(const uint32_t* inds, uint32_t slots, uint32_t experts, uint32_t j,
+                                                uint32_t* s_inds, uint16_t* members, uint32_t* s_count) {
+    const uint32_t tid = threadIdx.x;
+    for (uint32_t s = tid; s < slots; s += blockDim.x) s_inds[s] = min(inds[s], experts - 1u);
+    __syncthreads();
+    Members m;
+    m.expert = s_inds[j];
+    int earlier = 0;
+    for (uint32_t s = tid; s < j; s += blockDim.x) earlier |= (s_inds[s] == m.expert);
+    m.skip = __syncthreads_or(earlier) != 0;
+    m.count = 0;
+    if (m.skip) return m;
+    if (tid < 32u) {
+        uint32_t count = 0;
+        for (uint32_t base = j & ~31u; base < slots; base += 32u) {
+            const uint32_t s = base + tid;
+            const bool hit = s >= j && s < slots && s_inds[s] == m.expert;
+            const uint32_t votes = __ballot_sync(0xFFFFFFFFu, hit);
+            if (hit) members[count + __popc(votes & ((1u << tid) - 1u))] = (uint16_t)s;
+            count += __popc(votes);
+        }
+        if (tid == 0) *s_count = count;
+    }
+    __syncthreads();
+    m.count = *s_count;
+    return m;
+}
+
+// SwiGLU of one element in f32 with the optional clamp (turboexl3 src/core/ref.zig:124-140)
+__device__ __forceinline__ float swiglu(float g, float u, float limit, int clamp_at) {
+    if (limit > 0.0f) {
+        u = u > limit ? limit : (u < -limit ? -limit : u);
+        if (clamp_at == 0) g = g > limit ? limit : g;
+    }
+    float s = g / (1.0f + expf(-g));
+    if (limit > 0.0f && clamp_at != 0) s = s > limit ? limit : s;
+    return s * u;
+}
+
+// grid (2 SG, inter/128, row-slots), cluster (2 SG, 1, 1): cluster rank r streams projection r & 1 (0 gate, 1 up), K
+// slice r >> 1. The leader finishes both projections, applies SwiGLU and prepares the 128 values as inputs of the down
+// projection (ref.moeRow's middle, ref.zig:98-105; the reference kernels' "mid": src/kernels/hip/routed.hpp:64-112).
+template <int N, int RM>
+__global__ void __launch_bounds__(kGemvThreads, 2) moe_gate_up_kernel(const MoeArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint32_t s_inds[kMaxSlots];
+    __shared__ uint16_t s_members[kMaxSlots];
+    __shared__ uint32_t s_count;
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t rank = cluster.block_rank(), ib = blockIdx.y, j = blockIdx.z;
+    const uint32_t proj = rank & 1u, kpart = rank >> 1;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t H = a.hidden, I = a.inter;
+    const Members mem = find_members(static_cast<const uint32_t*>(a.inds), a.rows * a.topk, a.experts, j, s_inds,
+                                     s_members, &s_count);
+    if (mem.skip) return;
+    const uint32_t e = mem.expert;
+
+    uint32_t b0, b1;
+    slice_blocks(H / 128u, a.split_gu, kpart, b0, b1);
+    const uint32_t nblk = b1 - b0, nrows = nblk * 8u;
+    const uint32_t tile_bytes = 2u * a.n, row_bytes = 16u * a.n, out_tiles = I / 16u;
+    const Ring rc{a.ring_gu.stage_rows, a.ring_gu.stages};
+    const GemvSmem L = gemv_smem(RM, a.slice_max_gu, rc.stage_rows * row_bytes, rc.stages);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);
+    uint64_t* empty = full + kMaxStages;
+    __half* xp = reinterpret_cast<__half*>(smem + L.xp);
+    float* partial = reinterpret_cast<float*>(smem + L.partial);
+    uint8_t* ring = smem + L.ring;
+    const uint32_t xstride = a.slice_max_gu + kXpPad;
+    if (tid == 0) {
+        for (uint32_t s = 0; s < rc.stages; ++s) {
+            mbar_init(&full[s], 1u);
+            mbar_init(&empty[s], kConsumerWarps);
+        }
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    const size_t expert_bytes = (size_t)(H / 16u) * out_tiles * tile_bytes;
+    const uint8_t* wsrc = (proj ? a.up_t : a.gate_t) + e * expert_bytes + ((size_t)(b0 * 8u) * out_tiles + ib * 8u) * tile_bytes;
+    const __half* suh = static_cast<const __half*>(proj ? a.up_suh : a.gate_suh) + (size_t)e * H;
+    uint32_t chunk = 0;
+    for (uint32_t m0 = 0; m0 < mem.count; m0 += RM) {
+        const uint32_t mcount = min((uint32_t)RM, mem.count - m0);
+        if (warp == kConsumerWarps) {
+            produce_slab(ring, full, empty, wsrc, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, chunk, lane, a.err);
+        } else {
+            for (uint32_t i = mcount * xstride + tid; i < RM * xstride; i += 32u * kConsumerWarps)
+                xp[i] = __float2half_rn(0.0f);
+            for (uint32_t task = warp; task < mcount * nblk; task += kConsumerWarps) {
+                const uint32_t m = task / nblk, b = task - m * nblk;
+                const uint32_t row = s_members[m0 + m] / a.topk, k0 = (b0 + b) * 128u;
+                prepare_block(a.x, a.x_dt, (size_t)row * H + k0, suh + k0, xp + m * xstride + b * 128u, lane);
+            }
+            named_sync(1, 32u * kConsumerWarps);
+            float acc[RowCap<RM>::kMB][2][4] = {};
+            consume_slab<N, CB, RM>(ring, full, empty, nrows, a.n, a.mask, rc, xp, xstride, chunk, warp, lane, acc, a.err);
+            store_partial<RM>(partial, acc, warp, lane);
+        }
+        cluster.sync();
+        if (rank == 0 && warp < kConsumerWarps) {
+            const size_t eo = (size_t)e * I + ib * 128u;
+            for (uint32_t m = warp; m < mcount; m += kConsumerWarps) {
+                float g[4], u[4];
+                gather_row(cluster, partial, m, 0, 2, a.split_gu, lane, g);
+                gather_row(cluster, partial, m, 1, 2, a.split_gu, lane, u);
+                finish_block(g, static_cast<const __half*>(a.gate_svh) + eo, lane);
+                finish_block(u, static_cast<const __half*>(a.up_svh) + eo, lane);
+                float d[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    d[q] = round_half(swiglu(g[q], u[q], a.limit, a.clamp_at)) *
+                           __half2float(static_cast<const __half*>(a.down_suh)[eo + lane + 32u * q]);
+                h128_warp(d, lane);
+                __half* hd = static_cast<__half*>(a.hd) + (size_t)s_members[m0 + m] * I + ib * 128u;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) hd[lane + 32u * q] = __float2half_rn(d[q] * kHadScale);
+            }
+        }
+        cluster.sync();
+    }
+}
+
+// grid (SD, hidden/128, row-slots), cluster (SD, 1, 1): the down projection of every member of the slot's expert from the
+// prepared rows hd, finished per row-slot into v (f16): the value the merge weights by the slot's score.
+template <int N, int RM>
+__global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint32_t s_inds[kMaxSlots];
+    __shared__ uint16_t s_members[kMaxSlots];
+    __shared__ uint32_t s_count;
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t rank = cluster.block_rank(), hb = blockIdx.y, j = blockIdx.z;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t H = a.hidden, I = a.inter;
+    const Members mem = find_members(static_cast<const uint32_t*>(a.inds), a.rows * a.topk, a.experts, j, s_inds,
+                                     s_members, &s_count);
+    if (mem.skip) return;
+    const uint32_t e = mem.expert;
+
+    uint32_t b0, b1;
+    slice_blocks(I / 128u, a.split_d, rank, b0, b1);
+    const uint32_t nblk = b1 - b0, nrows = nblk * 8u;
+    const uint32_t tile_bytes = 2u * a.n, row_bytes = 16u * a.n, out_tiles = H / 16u;
+    const Ring rc{a.ring_d.stage_rows, a.ring_d.stages};
+    const GemvSmem L = gemv_smem(RM, a.slice_max_d, rc.stage_rows * row_bytes, rc.stages);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);
+    uint64_t* empty = full + kMaxStages;
+    __half* xp = reinterpret_cast<__half*>(smem + L.xp);
+    float* partial = reinterpret_cast<float*>(smem + L.partial);
+    uint8_t* ring = smem + L.ring;
+    const uint32_t xstride = a.slice_max_d + kXpPad;
+    if (tid == 0) {
+        for (uint32_t s = 0; s < rc.stages; ++s) {
+            mbar_init(&full[s], 1u);
+            mbar_init(&empty[s], kConsumerWarps);
+        }
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    const size_t expert_bytes = (size_t)(I / 16u) * out_tiles * tile_bytes;
+    const uint8_t* wsrc = a.down_t + e * expert_bytes + ((size_t)(b0 * 8u) * out_tiles + hb * 8u) * tile_bytes;
+    uint32_t chunk = 0;
+    for (uint32_t m0 = 0; m0 < mem.count; m0 += RM) {
+        const uint32_t mcount = min((uint32_t)RM, mem.count - m0);
+        if (warp == kConsumerWarps) {
+            produce_slab(ring, full, empty, wsrc, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, chunk, lane, a.err);
+        } else {
+            for (uint32_t i = mcount * xstride + tid; i < RM * xstride; i += 32u * kConsumerWarps)
+                xp[i] = __float2half_rn(0.0f);
+            for (uint32_t task = warp; task < mcount * nblk; task += kConsumerWarps) {
+                const uint32_t m = task / nblk, b = task - m * nblk;
+                const __half* src = static_cast<const __half*>(a.hd) + (size_t)s_members[m0 + m] * I + (b0 + b) * 128u;
+                __half* dst = xp + m * xstride + b * 128u;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint32_t i = lane + 32u * q;
+                    dst[(i & ~15u) | lane_order16(i & 15u)] = src[i];
+                }
+            }
+            named_sync(1, 32u * kConsumerWarps);
+            float acc[RowCap<RM>::kMB][2][4] = {};
+            consume_slab<N, CB, RM>(ring, full, empty, nrows, a.n, a.mask, rc, xp, xstride, chunk, warp, lane, acc, a.err);
+            store_partial<RM>(partial, acc, warp, lane);
+        }
+        cluster.sync();
+        if (rank == 0 && warp < kConsumerWarps) {
+            for (uint32_t m = warp; m < mcount; m += kConsumerWarps) {
+                float v[4];
+                gather_row(cluster, partial, m, 0, 1, a.split_d, lane, v);
+                finish_block(v, static_cast<const __half*>(a.down_svh) + (size_t)e * H + hb * 128u, lane);
+                __half* vo = static_cast<__half*>(a.v) + (size_t)s_members[m0 + m] * H + hb * 128u;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) vo[lane + 32u * q] = __float2half_rn(v[q]);
+            }
+        }
+        cluster.sync();
+    }
+}
+
+// grid (ceil(hidden / 256), rows): y[row] = sum over the row's slots, in slot order, of score * v in f32 (a multiply and an
+// add, as ref.moeRow has it, ref.zig:106), stored in x's dtype; then the optional shared-expert add in that dtype
+// (root.moeWithShared, src/root.zig:976-984).
+__global__ void __launch_bounds__(256) moe_merge_kernel(const MoeArgs a) {
+    const uint32_t i = blockIdx.x * 256u + threadIdx.x, row = blockIdx.y;
+    if (i >= a.hidden) return;
+    float acc = 0.0f;
+    for (uint32_t k = 0; k < a.topk; ++k) {
+        const size_t s = (size_t)row * a.topk + k;
+        const float w = load_act(a.scores, a.score_dt, s);
+        acc = __fadd_rn(acc, __fmul_rn(w, __half2float(static_cast<const __half*>(a.v)[s * a.hidden + i])));
+    }
+    const size_t o = (size_t)row * a.hidden + i;
+    if (a.shared) {
+        store_act(a.y, a.x_dt, o, acc);
+        acc = __fadd_rn(load_act(a.y, a.x_dt, o), load_act(a.shared, a.x_dt, o));
+    }
+    store_act(a.y, a.x_dt, o, acc);
+}
+
+// ---------------------------------------------------------------------------------------------- launch plumbing
+
+template <typename Args>
+using KernelFn = void (*)(const Args);
+
+template <typename Args>
+cudaError_t launch_cluster(KernelFn<Args> fn, const Args& a, dim3 grid, uint32_t cluster_x, uint32_t smem_bytes,
+                           cudaStream_t stream) {
+    cudaError_t rc = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)smem_bytes);
+    if (rc != cudaSuccess) return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kGemvThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster_x;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, fn, a);
+}
+
+#define T3_PICK_RM(KERNEL, NN, rm) \
+    ((rm) == 8 ? KERNEL<NN, 8> : ((rm) == 16 ? KERNEL<NN, 16> : KERNEL<NN, 32>))
+
+#define T3_PICK(KERNEL, n, rm)                                                       \
+    ((n) == 16    ? T3_PICK_RM(KERNEL, 16, rm)                                        \
+     : (n) == 32  ? T3_PICK_RM(KERNEL, 32, rm)                                        \
+     : (n) == 48  ? T3_PICK_RM(KERNEL, 48, rm)                                        \
+     : (n) == 64  ? T3_PICK_RM(KERNEL, 64, rm)                                        \
+     : (n) == 80  ? T3_PICK_RM(KERNEL, 80, rm)                                        \
+     : (n) == 96  ? T3_PICK_RM(KERNEL, 96, rm)                                        \
+     : (n) == 112 ? T3_PICK_RM(KERNEL, 112, rm)                                       \
+     : (n) == 128 ? T3_PICK_RM(KERNEL, 128, rm)                                       \
+                  : T3_PICK_RM(KERNEL, 0, rm))
+
+}  // namespace
+
+#define T3_CAT2(a, b) a##b
+#define T3_CAT(a, b) T3_CAT2(a, b)
+
+cudaError_t T3_CAT(launch_dense_gemv_cb, T3_CB)(const DenseArgs& a, cudaStream_t stream) {
+    const uint32_t rm = row_cap_for(a.rows);
+    KernelFn<DenseArgs> fn = T3_PICK(dense_gemv_kernel, a.n, rm);
+    return launch_cluster(fn, a, dim3(a.split, a.out / 128u, 1), a.split, gemv_smem_bytes(rm, a.slice_max, a.n, a.ring),
+                          stream);
+}
+
+cudaError_t T3_CAT(launch_moe_gate_up_cb, T3_CB)(const MoeArgs& a, cudaStream_t stream) {
+    const uint32_t rm = row_cap_for(a.rows);
+    KernelFn<MoeArgs> fn = T3_PICK(moe_gate_up_kernel, a.n, rm);
+    return launch_cluster(fn, a, dim3(2u * a.split_gu, a.inter / 128u, a.rows * a.topk), 2u * a.split_gu,
+                          gemv_smem_bytes(rm, a.slice_max_gu, a.n, a.ring_gu), stream);
+}
+
+cudaError_t T3_CAT(launch_moe_down_cb, T3_CB)(const MoeArgs& a, cudaStream_t stream) {
+    const uint32_t rm = row_cap_for(a.rows);
+    KernelFn<MoeArgs> fn = T3_PICK(moe_down_kernel, a.n, rm);
+    return launch_cluster(fn, a, dim3(a.split_d, a.hidden / 128u, a.rows * a.topk), a.split_d,
+                          gemv_smem_bytes(rm, a.slice_max_d, a.n, a.ring_d), stream);
+}
+
+#if T3_CB == 0
+cudaError_t launch_moe_merge(const MoeArgs& a, cudaStream_t stream) {
+    moe_merge_kernel<<<dim3((a.hidden + 255u) / 256u, a.rows, 1), 256, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+#endif
+
+}  // namespace t3

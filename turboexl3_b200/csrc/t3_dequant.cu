@@ -1,0 +1,77 @@
+// W_hat: the trellis decoded to the inner (un-rotated) f16 weight [in, out], bit for bit what turboexl3's host
+// reference reconstructs (format.reconstructInner, src/core/format.zig:276-291; the reference's kernel of the same job is
+// turboexl3_dense_dequant, src/core/dense.zig:65-71). Used by the bit-exact decode check and by the dense prefill path.
+//
+// grid (out / 128, in / 16), 256 threads: warp w decodes tile (tk, 8 bx + w) from global memory in registers, the CTA
+// transposes the 16 x 128 strip through shared memory and writes whole 256-byte rows.
+#include "t3_common.cuh"
+#include "t3_internal.h"
+
+namespace t3 {
+namespace {
+
+constexpr uint32_t kStripStride = 128 + 8;  // halfs per strip row (padding spreads the 2-byte scatter over banks)
+
+template <int N, int CB>
+__global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict__ trellis, uint32_t out, uint32_t n,
+                                                      uint32_t mask, __half* __restrict__ what) {
+    __shared__ __align__(16) uint16_t strip[16 * kStripStride];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t tk = blockIdx.y, tn = blockIdx.x * 8u + warp, out_tiles = out / 16u;
+    const uint32_t* tile = reinterpret_cast<const uint32_t*>(trellis + ((size_t)tk * out_tiles + tn) * 2u * n);
+    uint32_t b[4];
+    if (N > 0) {
+        LanePlan<(N > 0 ? N : 16)> plan;
+        plan.init(lane);
+        decode_lane<(N > 0 ? N : 16), CB>(tile, plan, mask, b);
+    } else {
+        decode_lane_any<CB>(tile, n, lane, mask, b);
+    }
+#pragma unroll
+    for (uint32_t m = 0; m < 8u; ++m)
+        strip[tile_row(lane, m) * kStripStride + warp * 16u + tile_col(lane, m)] = (uint16_t)(b[m >> 1] >> ((m & 1u) * 16u));
+    __syncthreads();
+    const uint32_t r = tid >> 4, c = (tid & 15u) * 8u;  // 16 rows x 16 chunks of 8 halfs
+    const uint4 v = *reinterpret_cast<const uint4*>(&strip[r * kStripStride + c]);
+    *reinterpret_cast<uint4*>(what + ((size_t)tk * 16u + r) * out + blockIdx.x * 128u + c) = v;
+}
+
+template <int CB>
+__global__ void codebook_table_kernel(uint32_t mask, uint16_t* out) {
+    const uint32_t cw = 2u * (blockIdx.x * blockDim.x + threadIdx.x);
+    if (cw >= 65536u) return;
+    const uint32_t w = decode2<CB>(cw & mask, (cw + 1u) & mask);
+    out[cw] = (uint16_t)w;
+    out[cw + 1u] = (uint16_t)(w >> 16);
+}
+
+template <int CB>
+cudaError_t launch_dequant_cb(const uint8_t* trellis, uint32_t in, uint32_t out, uint32_t n, uint32_t mask, void* what,
+                              cudaStream_t stream) {
+    const dim3 grid(out / 128u, in / 16u, 1);
+    __half* w = static_cast<__half*>(what);
+    switch (n) {
+#define T3_CASE(NN) \
+    case NN: dequant_kernel<NN, CB><<<grid, 256, 0, stream>>>(trellis, out, n, mask, w); break;
+        T3_CASE(16) T3_CASE(32) T3_CASE(48) T3_CASE(64) T3_CASE(80) T3_CASE(96) T3_CASE(112) T3_CASE(128)
+#undef T3_CASE
+        default: dequant_kernel<0, CB><<<grid, 256, 0, stream>>>(trellis, out, n, mask, w); break;
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_dequant(const uint8_t* trellis, uint32_t in, uint32_t out, uint32_t n, uint32_t mask, int codebook,
+                           void* what, cudaStream_t stream) {
+    return codebook == kMcg ? launch_dequant_cb<kMcg>(trellis, in, out, n, mask, what, stream)
+                            : launch_dequant_cb<kMul1>(trellis, in, out, n, mask, what, stream);
+}
+
+cudaError_t launch_codebook_table(int codebook, uint32_t mask, uint16_t* out, cudaStream_t stream) {
+    if (codebook == kMcg) codebook_table_kernel<kMcg><<<128, 256, 0, stream>>>(mask, out);
+    else codebook_table_kernel<kMul1><<<128, 256, 0, stream>>>(mask, out);
+    return cudaGetLastError();
+}
+
+}  // namespace t3

@@ -1,0 +1,187 @@
+// The decode-row engine's core: one CTA streams a slab of trellis codes (a K slice of one 128-wide output block)
+// through a ring of shared-memory stages filled by bulk copies, decodes each tile in registers straight into
+// mma.sync B fragments, and multiplies it with up to 32 prepared activation rows held in shared memory. Decoded weights
+// never leave registers. A thread-block cluster splits K; the partial sums meet over distributed shared memory in rank
+// order (deterministic) and the leader CTA runs the output rotation.
+//
+// Roles of the 288 threads: warps 0-7 are consumers (warp w owns output tile w of the block: 16 of the 128 columns, so no
+// cross-warp reduction exists), warp 8 is the copy producer.
+//
+// What it computes follows turboexl3's host reference (src/core/format.zig:334-389): xp = f16(H128(f16(x) suh)),
+// z = f16(sum xp W_hat) with f32 accumulation, y = f16(H128(z) svh). The launch shape has no counterpart in the
+// reference, whose GEMV kernels write split-K planes to device memory and finish in a second launch
+// (src/kernels/hip/dense/dense.hip:49-145).
+#pragma once
+
+#include <cooperative_groups.h>
+
+#include "t3_common.cuh"
+
+namespace t3 {
+
+namespace cg = cooperative_groups;
+
+constexpr uint32_t kConsumerWarps = 8;
+constexpr uint32_t kGemvThreads = 32u * (kConsumerWarps + 1u);
+constexpr uint32_t kMaxStages = 32;
+constexpr uint32_t kPartialStride = 136;  // floats per row of the partial-sum tile (128 + 8: conflict-free float2 stores)
+constexpr uint32_t kXpPad = 16;           // halfs added to an xp row so a quad's 8-byte loads spread over the banks
+
+// How the ring is cut for one launch (host-chosen, see plan_ring in t3_api.cu)
+struct Ring {
+    uint32_t stage_rows;  // tk rows a stage (each row: the block's 8 tiles = 16 n bytes)
+    uint32_t stages;      // 2..kMaxStages
+};
+
+template <int RM>
+struct RowCap {
+    static_assert(RM == 8 || RM == 16 || RM == 32, "row capacity");
+    static constexpr int kMB = RM == 32 ? 2 : 1;      // 16-row MMA blocks
+    static constexpr bool kHalf = RM == 8;            // rows 8-15 of the block are absent
+    static constexpr int kPartialRows = RM;
+};
+
+// Shared-memory carve-up of a GEMV CTA (byte offsets from a 128-byte aligned base)
+struct GemvSmem {
+    uint32_t bars, xp, partial, ring, total;
+};
+__host__ __device__ inline GemvSmem gemv_smem(uint32_t rm, uint32_t slice_k, uint32_t stage_bytes, uint32_t stages) {
+    GemvSmem s;
+    s.bars = 0;
+    s.xp = 2u * kMaxStages * 8u;
+    const uint32_t xp_bytes = rm * (slice_k + kXpPad) * 2u;
+    s.partial = s.xp + ((xp_bytes + 127u) & ~127u);
+    s.ring = s.partial + ((rm * kPartialStride * 4u + 127u) & ~127u);
+    s.total = s.ring + stage_bytes * stages;
+    return s;
+}
+
+// ---- producer -----------------------------------------------------------------------------------------------------
+
+// Streams tk rows [0, nrows) of a block's slab into the ring: row r is `row_bytes` contiguous bytes at
+// src + r * src_row_stride (bytes). `chunk` continues across calls so barrier parities stay in step.
+__device__ __forceinline__ void produce_slab(uint8_t* ring, uint64_t* full, uint64_t* empty, const uint8_t* src,
+                                             size_t src_row_stride, uint32_t nrows, uint32_t row_bytes, Ring rc,
+                                             uint32_t& chunk, uint32_t lane, uint32_t* err) {
+    const uint32_t stage_bytes = rc.stage_rows * row_bytes;
+    for (uint32_t r0 = 0; r0 < nrows; r0 += rc.stage_rows, ++chunk) {
+        const uint32_t slot = chunk % rc.stages, use = chunk / rc.stages;
+        if (use > 0 && !mbar_wait(&empty[slot], (use - 1u) & 1u)) report(err, kErrEmptyWait);
+        const uint32_t here = min(rc.stage_rows, nrows - r0);
+        if (lane == 0) mbar_arrive_expect_tx(&full[slot], here * row_bytes);
+        __syncwarp();
+        for (uint32_t r = lane; r < here; r += 32u)
+            bulk_copy_g2s(ring + slot * stage_bytes + r * row_bytes, src + (size_t)(r0 + r) * src_row_stride, row_bytes,
+                          &full[slot]);
+    }
+}
+
+// ---- consumer -----------------------------------------------------------------------------------------------------
+
+// Warp `warp` folds its tile column of tk rows [0, nrows) into acc. xp: prepared rows in lane order, row stride
+// `xstride` halfs, k = 0 at the slab's first input. acc[mb][nt] is the mma C fragment of rows 16 mb .. 16 mb + 15,
+// columns 16 warp + 8 nt .. + 7.
+template <int N, int CB, int RM>
+__device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full, uint64_t* empty, uint32_t nrows,
+                                             uint32_t n, uint32_t mask, Ring rc, const __half* xp, uint32_t xstride,
+                                             uint32_t& chunk, uint32_t warp, uint32_t lane,
+                                             float (&acc)[RowCap<RM>::kMB][2][4], uint32_t* err) {
+    constexpr int MB = RowCap<RM>::kMB;
+    const uint32_t tile_bytes = 2u * n, row_bytes = 16u * n, stage_bytes = rc.stage_rows * row_bytes;
+    const __half* xa = xp + (lane >> 2) * xstride + 4u * (lane & 3u);
+    LanePlan<(N > 0 ? N : 16)> plan;
+    if (N > 0) plan.init(lane);
+    for (uint32_t r0 = 0; r0 < nrows; r0 += rc.stage_rows, ++chunk) {
+        const uint32_t slot = chunk % rc.stages, use = chunk / rc.stages;
+        if (!mbar_wait(&full[slot], use & 1u)) report(err, kErrFullWait);
+        const uint32_t here = min(rc.stage_rows, nrows - r0);
+        const uint8_t* st = ring + slot * stage_bytes + warp * tile_bytes;
+#pragma unroll 2
+        for (uint32_t r = 0; r < here; ++r) {
+            uint32_t b[4];
+            const uint32_t* tile = reinterpret_cast<const uint32_t*>(st + r * row_bytes);
+            if (N > 0) decode_lane<(N > 0 ? N : 16), CB>(tile, plan, mask, b);
+            else decode_lane_any<CB>(tile, n, lane, mask, b);
+            const __half* xk = xa + (r0 + r) * 16u;
+#pragma unroll
+            for (int mb = 0; mb < MB; ++mb) {
+                const uint2 lo = *reinterpret_cast<const uint2*>(xk + (mb * 16) * xstride);
+                uint2 hi = make_uint2(0u, 0u);
+                if (!RowCap<RM>::kHalf) hi = *reinterpret_cast<const uint2*>(xk + (mb * 16 + 8) * xstride);
+                mma16816(acc[mb][0], lo.x, hi.x, lo.y, hi.y, b[0], b[1]);
+                mma16816(acc[mb][1], lo.x, hi.x, lo.y, hi.y, b[2], b[3]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[slot]);
+    }
+}
+
+// the warp's accumulators into the CTA's partial-sum tile [RM][kPartialStride]
+template <int RM>
+__device__ __forceinline__ void store_partial(float* partial, const float (&acc)[RowCap<RM>::kMB][2][4], uint32_t warp,
+                                              uint32_t lane) {
+    const uint32_t g = lane >> 2, q = lane & 3u;
+#pragma unroll
+    for (int mb = 0; mb < RowCap<RM>::kMB; ++mb)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const uint32_t col = warp * 16u + nt * 8u + 2u * q;
+            *reinterpret_cast<float2*>(partial + (mb * 16 + g) * kPartialStride + col) =
+                make_float2(acc[mb][nt][0], acc[mb][nt][1]);
+            if (!RowCap<RM>::kHalf)
+                *reinterpret_cast<float2*>(partial + (mb * 16 + g + 8) * kPartialStride + col) =
+                    make_float2(acc[mb][nt][2], acc[mb][nt][3]);
+        }
+}
+
+// ---- prepare ------------------------------------------------------------------------------------------------------
+
+// One (row, 128-block) of the input rotation by one warp (format.prepareInput, format.zig:334-345): the block's elements
+// x[i] (dtype dt) times suh[i], H128, scaled, rounded to f16, into xp_row at the block's lane-ordered slots.
+__device__ __forceinline__ void prepare_block(const void* x, int dt, size_t x_off, const __half* suh, __half* xp_blk,
+                                              uint32_t lane) {
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t i = lane + 32u * j;
+        v[j] = round_half(load_act(x, dt, x_off + i)) * __half2float(suh[i]);
+    }
+    h128_warp(v, lane);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t i = lane + 32u * j;
+        xp_blk[(i & ~15u) | lane_order16(i & 15u)] = __float2half_rn(v[j] * kHadScale);
+    }
+}
+
+// The output rotation of one row's 128-block by one warp (format.finishOutput, format.zig:370-380): v[j] holds the
+// f32 inner product of column lane + 32 j; returns y = f16(H128(f16(v)) svh) as f32 values in v.
+__device__ __forceinline__ void finish_block(float (&v)[4], const __half* svh_blk, uint32_t lane) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = round_half(v[j]);
+    h128_warp(v, lane);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = round_half(v[j] * kHadScale * __half2float(svh_blk[lane + 32u * j]));
+}
+
+// Sum of the cluster's partial tiles for one row, taken in the given rank order (first, first + step, ...), for the
+// lane's four columns lane + 32 j.
+__device__ __forceinline__ void gather_row(cg::cluster_group& cluster, float* partial, uint32_t row, uint32_t first,
+                                           uint32_t step, uint32_t count, uint32_t lane, float (&v)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = 0.0f;
+    for (uint32_t i = 0; i < count; ++i) {
+        const float* rp = cluster.map_shared_rank(partial, first + i * step) + row * kPartialStride + lane;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = (i == 0) ? rp[32 * j] : v[j] + rp[32 * j];
+    }
+}
+
+// K blocks [b0, b1) of rank r when nb 128-blocks are cut over s ranks
+__host__ __device__ inline void slice_blocks(uint32_t nb, uint32_t s, uint32_t r, uint32_t& b0, uint32_t& b1) {
+    b0 = nb * r / s;
+    b1 = nb * (r + 1u) / s;
+}
+
+}  // namespace t3

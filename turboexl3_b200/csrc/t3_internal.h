@@ -1,0 +1,66 @@
+// Host-side declarations shared by the library's translation units (not part of the public C ABI).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace t3 {
+
+struct RingPlan {
+    uint32_t stage_rows, stages;
+};
+
+// One dense linear at decode rows (rows <= 32)
+struct DenseArgs {
+    const void* x;            // [rows, in], dtype x_dt
+    void* y;                  // [rows, out], dtype x_dt
+    const uint8_t* trellis;   // [in/16, out/16, n] u16
+    const void* suh;          // f16 [in]
+    const void* svh;          // f16 [out]
+    uint32_t rows, in, out, n, mask;
+    int x_dt;
+    uint32_t split;           // cluster size: K slices
+    uint32_t slice_max;       // inputs of the largest K slice
+    RingPlan ring;
+    uint32_t* err;
+};
+
+// The routed chain at decode rows (rows <= 32): row-slot s = row * topk + k runs expert inds[s]
+struct MoeArgs {
+    const void* x;            // [rows, hidden], dtype x_dt
+    int x_dt;
+    const void* inds;         // [rows * topk] i32/u32
+    const void* scores;       // [rows * topk], dtype score_dt
+    int score_dt;
+    const uint8_t *gate_t, *up_t, *down_t;
+    const void *gate_suh, *gate_svh, *up_suh, *up_svh, *down_suh, *down_svh;  // f16, expert-major
+    uint32_t experts, hidden, inter, topk, rows, n, mask;
+    float limit;              // SwiGLU clamp, 0 = none
+    int clamp_at;             // 0 gate_in, 1 silu_out
+    void* hd;                 // scratch f16 [rows * topk, inter]: the down projection's prepared inputs
+    void* v;                  // scratch f16 [rows * topk, hidden]: each row-slot's finished down output
+    void* y;                  // [rows, hidden], dtype x_dt
+    const void* shared;       // optional [rows, hidden] dtype x_dt added at y's rounding point, or null
+    uint32_t split_gu, slice_max_gu;   // K slices of gate|up (cluster = 2 * split_gu), largest slice
+    uint32_t split_d, slice_max_d;     // K slices of down
+    RingPlan ring_gu, ring_d;
+    uint32_t* err;
+};
+
+cudaError_t launch_dense_gemv(const DenseArgs& a, int codebook, cudaStream_t stream);
+cudaError_t launch_moe_gate_up(const MoeArgs& a, int codebook, cudaStream_t stream);
+cudaError_t launch_moe_down(const MoeArgs& a, int codebook, cudaStream_t stream);
+cudaError_t launch_moe_merge(const MoeArgs& a, cudaStream_t stream);
+
+// shared-memory bytes the GEMV CTAs of a plan need (for admission before launch)
+uint32_t gemv_smem_bytes(uint32_t row_cap, uint32_t slice_max, uint32_t n, RingPlan ring);
+uint32_t row_cap_for(uint32_t rows);
+
+// W_hat [in, out] f16 from the trellis
+cudaError_t launch_dequant(const uint8_t* trellis, uint32_t in, uint32_t out, uint32_t n, uint32_t mask, int codebook,
+                           void* what, cudaStream_t stream);
+// all 65,536 codewords through the kernels' decoders: out[cw] = f16 bits (test hook)
+cudaError_t launch_codebook_table(int codebook, uint32_t mask, uint16_t* out, cudaStream_t stream);
+
+}  // namespace t3
