@@ -91,7 +91,9 @@ int t3_parse_expert_quant(const char* json, size_t len, t3_spec* out);
 typedef struct {
     int prefill;             /* 0: rows past T3_DECODE_ROWS_MAX refuse Exl3EngineNotImplemented (Config.prefill) */
     uint32_t ring_bytes;     /* shared-memory bytes a GEMV CTA's code ring may take; 0 = default */
-    uint32_t dense_split;    /* K slices of a dense GEMV cluster (1, 2, 4, 8); 0 = choose from the shape */
+    uint32_t dense_split;    /* K slices of a dense GEMV cluster (1, 2, 4, 8, 16); 0 = choose from the shape */
+    int no_overlap;          /* 1: launches wait for the stream's previous kernel to finish before they start (no
+                                programmatic dependent launch); for measurements */
 } t3_config;
 void t3_config_default(t3_config* out);
 int t3_configure(const t3_config* cfg);                  /* InvalidTurboexl3Config on a bad value */
@@ -132,6 +134,12 @@ int t3_moe_clamped(const void* x, int x_dtype, size_t rows, const t3_bank* bank,
 int t3_moe_with_shared(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds,
                        const void* scores, int scores_dtype, int topk, t3_decode dec, const void* shared, void* y,
                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* Measurement hook (the reference has probe kernels for the same purpose, src/core/decode.zig:34-35): when set to a
+ * device array of 8 uint64, the next t3_linear launches at decode rows record the SM cycle counter of their CTA (0, 0) at:
+ * [0] entry, [1] barriers initialised, [2] activations prepared, [3] first code stage landed, [4] GEMV done and partials
+ * pushed, [5] cluster reduce complete, [6] outputs stored. Null switches it off. */
+void t3_set_trace(void* device_u64x8);
 
 /* Kernels this library launched since the process started (for benches that must report their launch count). */
 uint64_t t3_launch_count(void);

@@ -63,11 +63,43 @@ def test_config2_sweep_decode_rows(shape, k):
     assert t3.device_error() == 0
 
 
-def test_rows_past_the_register_path_still_match():
-    """rows > 32 run as chunks of 32; rows of the reference's wider cases (src/core/gpu_test.zig:396)."""
-    for rows in (33, 40, 129, 200):
-        got, ref, _ = run_case(512, 256, 64, t3.MUL1, 16, "f16", rows, seed=rows)
-        check(got, ref, "f16", rows)
+# (in, out, n, codebook, window, dtype): the reference's GEMM cases (src/hip_tests.zig:839-881, src/core/gpu_test.zig:384-398)
+GEMM_CASES = [
+    (512, 256, 64, t3.MCG, 16, "f32"), (512, 256, 64, t3.MUL1, 16, "f16"), (512, 384, 36, t3.MUL1, 12, "f16"),
+    (2560, 640, 80, t3.MUL1, 16, "bf16"), (640, 2560, 112, t3.MUL1, 16, "f16"), (2560, 512, 96, t3.MCG, 16, "f16"),
+]
+
+
+@pytest.mark.parametrize("case", GEMM_CASES)
+def test_reference_gemm_cases(case):
+    """rows > 32: prepare -> tcgen05 GEMM with the trellis decoded in its weight loader -> finish."""
+    in_dim, out_dim, n, cb, w, dt = case
+    for rows in (33, 40, 129, 200, 256, 257, 600):
+        got, ref, _ = run_case(in_dim, out_dim, n, cb, w, dt, rows, seed=in_dim + rows)
+        check(got, ref, dt, (case, rows))
+    assert t3.device_error() == 0
+
+
+def test_config2_sweep_gemm_rows():
+    """BASELINE config 2 at the GEMM rows {33, 512, 4096}: every K at 2048x2048, K = 4 at the two wide shapes; +-1 signs."""
+    cases = [((2048, 2048), k) for k in (1, 2, 3, 4, 5, 6, 8)] + [((2048, 6144), 4), ((6144, 2048), 4)]
+    for (in_dim, out_dim), k in cases:
+        for rows in (33, 512, 4096):
+            if rows == 4096 and (in_dim, out_dim) != (2048, 2048):
+                continue  # the oracle is the slow side
+            got, ref, _ = run_case(in_dim, out_dim, 16 * k, t3.MUL1, 16, "f16", rows, seed=11 * k + rows, scaled=False)
+            check(got, ref, "f16", ((in_dim, out_dim), k, rows))
+    assert t3.device_error() == 0
+
+
+def test_gemm_first_rows_are_byte_stable():
+    """The first 17 rows' bytes are the same in a 40-row and a 200-row call (src/hip_tests.zig:870-880)."""
+    trellis, suh, svh = synth.linear(51, 512, 256, 64, scaled=True)
+    t, a, b = dev(trellis), dev(suh), dev(svh)
+    x = dev(synth.activations(52, 200, 512))
+    y200 = bits16(t3.linear(x, t, a, b))
+    y40 = bits16(t3.linear(x[:40].contiguous(), t, a, b))
+    assert np.array_equal(y200[:17], y40[:17])
 
 
 def test_a_row_alone_equals_the_row_in_a_batch():
@@ -107,7 +139,7 @@ def test_split_choices_agree_within_rounding():
     t, a, b = dev(trellis), dev(suh), dev(svh)
     outs = []
     try:
-        for split in (1, 2, 4, 8):
+        for split in (1, 2, 4, 8, 16):
             t3.configure(dense_split=split)
             outs.append(host_f32(t3.linear(x, t, a, b)))
     finally:

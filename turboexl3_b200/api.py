@@ -52,7 +52,7 @@ class _Spec(C.Structure):
 
 
 class _Config(C.Structure):
-    _fields_ = [("prefill", C.c_int), ("ring_bytes", C.c_uint32), ("dense_split", C.c_uint32)]
+    _fields_ = [("prefill", C.c_int), ("ring_bytes", C.c_uint32), ("dense_split", C.c_uint32), ("no_overlap", C.c_int)]
 
 
 # every symbol include/t3.h declares: (restype, argtypes)
@@ -75,6 +75,7 @@ SYMBOLS = {
     "t3_moe_swiglu": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _u32, _i, _vp, _vp, _sz, _vp]),
     "t3_moe_clamped": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _i, _vp, _vp, _sz, _vp]),
     "t3_moe_with_shared": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp, _vp, _sz, _vp]),
+    "t3_set_trace": (None, [_vp]),
     "t3_launch_count": (C.c_uint64, []),
 }
 
@@ -152,9 +153,9 @@ def _trellis_ok(t: torch.Tensor) -> bool:
     return t.dtype in (torch.uint16, torch.int16)
 
 
-def configure(prefill: bool = True, ring_bytes: int = 0, dense_split: int = 0) -> None:
+def configure(prefill: bool = True, ring_bytes: int = 0, dense_split: int = 0, no_overlap: bool = False) -> None:
     """core.config.configure (src/core/config.zig:175): process-wide, before the first call."""
-    cfg = _Config(int(prefill), ring_bytes, dense_split)
+    cfg = _Config(int(prefill), ring_bytes, dense_split, int(no_overlap))
     _check(lib().t3_configure(C.byref(cfg)))
 
 

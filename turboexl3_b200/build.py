@@ -22,6 +22,8 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 
 # (source, object stem, extra flags)
 UNITS = [
+    ("t3_table.cu", "t3_table", []),
+    ("t3_prefill.cu", "t3_prefill", []),
     ("t3_api.cu", "t3_api", []),
     ("t3_dequant.cu", "t3_dequant", []),
     ("t3_decode_rows.cu", "t3_decode_rows_cb0", ["-DT3_CB=0"]),

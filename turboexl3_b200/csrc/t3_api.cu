@@ -27,10 +27,11 @@ std::atomic<uint64_t> g_launches{0};
 __device__ uint32_t g_dev_error_word;
 
 std::mutex g_mu;
-t3_config g_cfg = {1, 0, 0};
+t3_config g_cfg = {1, 0, 0, 0};
 uint32_t* g_err_ptr[64] = {};
+unsigned long long* g_trace = nullptr;
 
-constexpr uint32_t kSmemCap = 220u * 1024u;      // dynamic shared memory a GEMV CTA may ask for
+constexpr uint32_t kSmemCap = kGemvSmemLimit - kSmemSlack;  // what the carve-up of a GEMV CTA may add up to
 constexpr uint32_t kDefaultRing = 64u * 1024u;
 
 uint32_t* dev_error_ptr() {
@@ -51,6 +52,26 @@ uint32_t pow2_at_most(uint32_t v, uint32_t cap) {
     return s;
 }
 
+// CTAs that fit on the device at once (two GEMV CTAs a multiprocessor)
+uint32_t one_wave() {
+    static uint32_t ctas = [] {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            sms <= 0)
+            sms = 148;
+        return 2u * (uint32_t)sms;
+    }();
+    return ctas;
+}
+
+// K slices for `units` independent (output block, job) pairs over nb 128-blocks of K: the largest power of two, at most
+// `cap`, that keeps the whole grid (units x slices x `fan` CTAs a slice) inside one wave; 1 when even that does not fit.
+uint32_t pick_split(uint32_t nb, uint32_t units, uint32_t fan, uint32_t cap) {
+    uint32_t s = 1;
+    while (s * 2u <= nb && s * 2u <= cap && (uint64_t)units * fan * s * 2u <= one_wave()) s *= 2u;
+    return s;
+}
+
 uint32_t largest_slice(uint32_t nb, uint32_t split) {
     uint32_t mx = 0;
     for (uint32_t r = 0; r < split; ++r) {
@@ -61,15 +82,14 @@ uint32_t largest_slice(uint32_t nb, uint32_t split) {
     return mx * 128u;
 }
 
-// The ring of one GEMV CTA: stages of about 8 KB, as many as the slab needs or the budget holds.
-bool plan_ring(uint32_t row_cap, uint32_t slice_max, uint32_t n, RingPlan& ring) {
-    const uint32_t row_bytes = 16u * n, nrows = slice_max / 16u;
-    uint32_t stage_rows = 8192u / row_bytes;
-    stage_rows = stage_rows < 1u ? 1u : (stage_rows > 32u ? 32u : stage_rows);
-    stage_rows = stage_rows > nrows ? nrows : stage_rows;
+// The ring of one GEMV CTA: stages of kStageRows tk rows (one 128-input block), as many as the slab needs or the budget
+// holds.
+bool plan_ring(uint32_t row_cap, uint32_t slice_max, uint32_t cluster, uint32_t n, RingPlan& ring) {
+    const uint32_t row_bytes = 16u * n, nrows = slice_max / 16u;  // nrows is a multiple of 8 (whole 128-blocks)
+    const uint32_t stage_rows = kStageRows;
     const uint32_t stage_bytes = stage_rows * row_bytes;
     const uint32_t need = (nrows + stage_rows - 1u) / stage_rows;
-    const uint32_t fixed = gemv_smem(row_cap, slice_max, stage_bytes, 0).total;
+    const uint32_t fixed = gemv_smem(row_cap, slice_max, cluster, stage_bytes, 0).total;
     if (fixed + stage_bytes > kSmemCap) return false;
     uint32_t budget = g_cfg.ring_bytes ? g_cfg.ring_bytes : kDefaultRing;
     if (budget > kSmemCap - fixed) budget = kSmemCap - fixed;
@@ -100,8 +120,8 @@ int cuda_status(cudaError_t rc) { return rc == cudaSuccess ? T3_OK : T3_CUDA_ERR
 
 uint32_t row_cap_for(uint32_t rows) { return rows <= 8u ? 8u : (rows <= 16u ? 16u : 32u); }
 
-uint32_t gemv_smem_bytes(uint32_t row_cap, uint32_t slice_max, uint32_t n, RingPlan ring) {
-    return gemv_smem(row_cap, slice_max, ring.stage_rows * 16u * n, ring.stages).total;
+uint32_t gemv_smem_bytes(uint32_t row_cap, uint32_t slice_max, uint32_t cluster, uint32_t n, RingPlan ring) {
+    return gemv_smem(row_cap, slice_max, cluster, ring.stage_rows * 16u * n, ring.stages).total + kSmemSlack;
 }
 
 cudaError_t launch_dense_gemv(const DenseArgs& a, int codebook, cudaStream_t stream) {
@@ -248,13 +268,15 @@ void t3_config_default(t3_config* out) {
     out->prefill = 1;
     out->ring_bytes = 0;
     out->dense_split = 0;
+    out->no_overlap = 0;
 }
 
 int t3_configure(const t3_config* cfg) {
     if (!cfg) return T3_NULL_POINTER;
     const uint32_t s = cfg->dense_split;
-    if (s != 0 && s != 1 && s != 2 && s != 4 && s != 8) return T3_INVALID_CONFIG;
-    if (cfg->ring_bytes != 0 && (cfg->ring_bytes < 4096u || cfg->ring_bytes > kSmemCap)) return T3_INVALID_CONFIG;
+    if (s != 0 && s != 1 && s != 2 && s != 4 && s != 8 && s != 16) return T3_INVALID_CONFIG;
+    if (cfg->no_overlap != 0 && cfg->no_overlap != 1) return T3_INVALID_CONFIG;
+    if (cfg->ring_bytes != 0 && (cfg->ring_bytes < 4096u || cfg->ring_bytes > kGemvSmemLimit)) return T3_INVALID_CONFIG;
     if (cfg->prefill != 0 && cfg->prefill != 1) return T3_INVALID_CONFIG;
     std::lock_guard<std::mutex> lock(g_mu);
     g_cfg = *cfg;
@@ -271,6 +293,11 @@ int t3_device_error(void* stream, uint32_t* bits_out, int clear) {
     if (cudaStreamSynchronize(s) != cudaSuccess) return T3_CUDA_ERROR;
     if (bits_out) *bits_out = bits;
     return T3_OK;
+}
+
+void t3_set_trace(void* device_u64x8) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    g_trace = static_cast<unsigned long long*>(device_u64x8);
 }
 
 uint64_t t3_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
@@ -298,18 +325,14 @@ int t3_codebook_table(t3_decode dec, void* out, void* stream) {
 // ---- dense linear ---------------------------------------------------------------------------------------------------
 
 size_t t3_linear_workspace_bytes(size_t rows, int in_dim, int out_dim, int n) {
-    (void)rows;
-    (void)in_dim;
-    (void)out_dim;
     (void)n;
-    return 0;  // the decode-row kernel keeps everything on chip
+    if (rows <= T3_DECODE_ROWS_MAX || in_dim <= 0 || out_dim <= 0) return 0;  // the decode-row kernel keeps everything on chip
+    return prefill_linear_workspace(rows, (uint32_t)in_dim, (uint32_t)out_dim);
 }
 
 int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, const void* suh, const void* svh,
               int in_dim, int out_dim, int n, t3_decode dec, void* y, void* workspace, size_t workspace_bytes,
               void* stream) {
-    (void)workspace;
-    (void)workspace_bytes;
     if (!x || !trellis || !suh || !svh || !y) return T3_NULL_POINTER;
     if (in_dim <= 0 || out_dim <= 0 || in_dim % 128 != 0 || out_dim % 128 != 0 || !rate_ok(n) || rows < 1 ||
         rows > (size_t)1 << 30)
@@ -322,7 +345,17 @@ int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, cons
         std::lock_guard<std::mutex> lock(g_mu);
         cfg = g_cfg;
     }
-    if (rows > T3_DECODE_ROWS_MAX && !cfg.prefill) return T3_ENGINE_NOT_IMPLEMENTED;
+    if (rows > T3_DECODE_ROWS_MAX) {
+        if (!cfg.prefill) return T3_ENGINE_NOT_IMPLEMENTED;
+        if (rows > 0x7FFFFFFFu / (size_t)(in_dim > out_dim ? in_dim : out_dim)) return T3_BAD_EXL3_SHAPE;
+        if (!workspace || workspace_bytes < t3_linear_workspace_bytes(rows, in_dim, out_dim, n)) return T3_WORKSPACE_TOO_SMALL;
+        PrefillLinearArgs p = {x, y, static_cast<const uint8_t*>(trellis), suh, svh, (uint32_t)rows, (uint32_t)in_dim,
+                               (uint32_t)out_dim, (uint32_t)n, mask, x_dtype, workspace, dev_error_ptr()};
+        int launches = 0;
+        const cudaError_t rc = launch_prefill_linear(p, dec.codebook, static_cast<cudaStream_t>(stream), &launches);
+        g_launches.fetch_add((uint64_t)launches, std::memory_order_relaxed);
+        return cuda_status(rc);
+    }
 
     DenseArgs a = {};
     a.trellis = static_cast<const uint8_t*>(trellis);
@@ -334,20 +367,21 @@ int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, cons
     a.mask = mask;
     a.x_dt = x_dtype;
     const uint32_t nb = a.in / 128u;
-    a.split = cfg.dense_split ? pow2_at_most(nb, cfg.dense_split) : pow2_at_most(nb, 8u);
+    a.split = cfg.dense_split ? pow2_at_most(nb, cfg.dense_split) : pick_split(nb, a.out / 128u, 1u, 8u);
+    a.overlap = !cfg.no_overlap;
     a.slice_max = largest_slice(nb, a.split);
     a.err = dev_error_ptr();
-    // rows past the in-register capacity run as chunks of it (each chunk decodes the matrix again)
-    const size_t cap = T3_DECODE_ROWS_MAX;
-    const size_t elt = dtype_size(x_dtype);
-    for (size_t r0 = 0; r0 < rows; r0 += cap) {
-        a.rows = (uint32_t)(rows - r0 < cap ? rows - r0 : cap);
-        if (!plan_ring(row_cap_for(a.rows), a.slice_max, a.n, a.ring)) return T3_ENGINE_NOT_IMPLEMENTED;
-        a.x = static_cast<const uint8_t*>(x) + r0 * a.in * elt;
-        a.y = static_cast<uint8_t*>(y) + r0 * a.out * elt;
-        if (int rc = cuda_status(launch_dense_gemv(a, dec.codebook, static_cast<cudaStream_t>(stream)))) return rc;
+    a.trace = g_trace;
+    a.rows = (uint32_t)rows;
+    // a slice too long for shared memory (its prepared rows) is cut further, up to the widest cluster
+    while (!plan_ring(row_cap_for(a.rows), a.slice_max, a.split, a.n, a.ring)) {
+        if (a.split * 2u > nb || a.split * 2u > 16u) return T3_ENGINE_NOT_IMPLEMENTED;
+        a.split *= 2u;
+        a.slice_max = largest_slice(nb, a.split);
     }
-    return T3_OK;
+    a.x = x;
+    a.y = y;
+    return cuda_status(launch_dense_gemv(a, dec.codebook, static_cast<cudaStream_t>(stream)));
 }
 
 // ---- routed experts -------------------------------------------------------------------------------------------------
@@ -380,7 +414,13 @@ int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const
     if (clamp_at != T3_CLAMP_GATE_IN && clamp_at != T3_CLAMP_SILU_OUT) return T3_INVALID_CLAMP;
     uint32_t mask;
     if (int rc = decode_mask(dec, mask)) return rc;
-    if (rows > T3_DECODE_ROWS_MAX) return T3_ENGINE_NOT_IMPLEMENTED;  // the prefill chain is a separate engine
+    t3_config cfg;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        cfg = g_cfg;
+    }
+    if (rows > T3_DECODE_ROWS_MAX && !cfg.prefill) return T3_ENGINE_NOT_IMPLEMENTED;  // src/root.zig:850-852
+    if (rows * (size_t)topk > 0x7FFFFFFFu / (size_t)(bank->hidden > bank->inter ? bank->hidden : bank->inter)) return T3_BAD_EXL3_SHAPE;
     const size_t need = t3_moe_workspace_bytes(rows, topk, bank);
     if (!workspace || workspace_bytes < need) return T3_WORKSPACE_TOO_SMALL;
 
@@ -409,20 +449,38 @@ int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const
     a.limit = (float)limit;
     a.clamp_at = clamp_at;
     const size_t slots = rows * (size_t)topk;
-    a.hd = workspace;
-    a.v = static_cast<uint8_t*>(workspace) + align256(slots * a.inter * 2u);
     a.y = y;
     a.shared = shared;
-    const uint32_t rm = row_cap_for(a.rows);
-    a.split_gu = pow2_at_most(a.hidden / 128u, 4u);
-    a.slice_max_gu = largest_slice(a.hidden / 128u, a.split_gu);
-    a.split_d = pow2_at_most(a.inter / 128u, 8u);
-    a.slice_max_d = largest_slice(a.inter / 128u, a.split_d);
-    {
-        std::lock_guard<std::mutex> lock(g_mu);
-        if (!plan_ring(rm, a.slice_max_gu, a.n, a.ring_gu) || !plan_ring(rm, a.slice_max_d, a.n, a.ring_d))
-            return T3_ENGINE_NOT_IMPLEMENTED;
+    a.err = dev_error_ptr();
+    if (rows > T3_DECODE_ROWS_MAX) {
+        int launches = 0;
+        const cudaError_t rc = launch_prefill_moe(a, workspace, dec.codebook, static_cast<cudaStream_t>(stream), &launches);
+        g_launches.fetch_add((uint64_t)launches, std::memory_order_relaxed);
+        return cuda_status(rc);
     }
+    a.hd = workspace;
+    a.v = static_cast<uint8_t*>(workspace) + align256(slots * a.inter * 2u);
+    const uint32_t rm = row_cap_for(a.rows);
+    a.overlap = !cfg.no_overlap;
+    // The K splits depend on the geometry only (sized for one row's slots), never on the row count: a row's summation
+    // order, hence its bytes, is the same alone and in a batch.
+    a.split_gu = pick_split(a.hidden / 128u, (a.inter / 128u) * a.topk, 2u, 4u);
+    a.slice_max_gu = largest_slice(a.hidden / 128u, a.split_gu);
+    a.split_d = pick_split(a.inter / 128u, (a.hidden / 128u) * a.topk, 1u, 8u);
+    a.slice_max_d = largest_slice(a.inter / 128u, a.split_d);
+    // sized for the widest row capacity so the split does not move with the rows either
+    while (!plan_ring(32u, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu)) {
+        if (a.split_gu * 2u > a.hidden / 128u || a.split_gu * 2u > 8u) return T3_ENGINE_NOT_IMPLEMENTED;
+        a.split_gu *= 2u;
+        a.slice_max_gu = largest_slice(a.hidden / 128u, a.split_gu);
+    }
+    while (!plan_ring(32u, a.slice_max_d, a.split_d, a.n, a.ring_d)) {
+        if (a.split_d * 2u > a.inter / 128u || a.split_d * 2u > 16u) return T3_ENGINE_NOT_IMPLEMENTED;
+        a.split_d *= 2u;
+        a.slice_max_d = largest_slice(a.inter / 128u, a.split_d);
+    }
+    if (!plan_ring(rm, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu) || !plan_ring(rm, a.slice_max_d, a.split_d, a.n, a.ring_d))
+        return T3_ENGINE_NOT_IMPLEMENTED;
     a.err = dev_error_ptr();
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (int rc = cuda_status(launch_moe_gate_up(a, dec.codebook, s))) return rc;
@@ -434,8 +492,10 @@ int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const
 }  // namespace
 
 size_t t3_moe_workspace_bytes(size_t rows, int topk, const t3_bank* bank) {
-    if (!bank || topk <= 0 || bank->inter <= 0 || bank->hidden <= 0) return 0;
+    if (!bank || topk <= 0 || bank->inter <= 0 || bank->hidden <= 0 || bank->experts <= 0) return 0;
     const size_t slots = rows * (size_t)topk;
+    if (rows > T3_DECODE_ROWS_MAX)
+        return prefill_moe_workspace(rows, (uint32_t)topk, (uint32_t)bank->experts, (uint32_t)bank->hidden, (uint32_t)bank->inter);
     return align256(slots * (size_t)bank->inter * 2u) + align256(slots * (size_t)bank->hidden * 2u);
 }
 

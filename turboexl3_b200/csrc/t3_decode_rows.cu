@@ -9,6 +9,9 @@
 // The reference's served chain is four or five (src/core/decode.zig:483-517). Row-slots that share an expert are found
 // inside the kernels (each CTA scans the call's <= 1024 expert ids), so one decode of an expert's tiles feeds every row
 // that routed to it, as the reference's grouped members do (src/core/kernels/decode/gemv_core.metal:4-21).
+#include <mutex>
+#include <unordered_set>
+
 #include "t3_gemv.cuh"
 #include "t3_internal.h"
 
@@ -22,64 +25,118 @@ namespace {
 constexpr int CB = T3_CB;
 constexpr uint32_t kMaxSlots = 1024;  // 32 rows x 32 top-k
 
+// ---------------------------------------------------------------------------------------------- shared pieces
+
+struct CtaSmem {
+    uint64_t *full, *empty;
+    __half* xp;
+    float *local, *recv;
+    uint8_t* ring;
+};
+
+__device__ __forceinline__ CtaSmem carve(uint8_t* smem, const GemvSmem& L) {
+    CtaSmem c;
+    c.full = reinterpret_cast<uint64_t*>(smem + L.bars);
+    c.empty = c.full + kMaxStages;
+    c.xp = reinterpret_cast<__half*>(smem + L.xp);
+    c.local = reinterpret_cast<float*>(smem + L.local);
+    c.recv = reinterpret_cast<float*>(smem + L.recv);
+    c.ring = smem + L.ring;
+    return c;
+}
+
+__device__ __forceinline__ void init_barriers(const CtaSmem& c, uint32_t stages) {
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < stages; ++s) {
+            mbar_init(&c.full[s], 1u);
+            mbar_init(&c.empty[s], kConsumerWarps);
+        }
+        mbar_init_fence();
+    }
+}
+
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+// The consumer side of one pass once xp is ready: GEMV over the slab, the two K groups joined, the partial pushed to the
+// rows' owners. `count` live rows.
+template <int N, int RM>
+__device__ __forceinline__ void gemv_and_push(cg::cluster_group& cluster, const CtaSmem& c, uint32_t nrows, uint32_t n,
+                                              uint32_t mask, Ring rc, uint32_t xstride, uint32_t& chunk, uint32_t count,
+                                              uint32_t rank, uint32_t csize, uint32_t warp, uint32_t lane, uint32_t* err) {
+    const uint32_t tcol = warp & (kTileWarps - 1u), kg = warp / kTileWarps;
+    float acc[RowCap<RM>::kMB][2][4] = {};
+    consume_slab<N, CB, RM>(c.ring, c.full, c.empty, nrows, n, mask, rc, c.xp, xstride, chunk, tcol, kg, lane, acc, err);
+    if (kg == 1) store_local<RM>(c.local, acc, tcol, lane);
+    named_sync(1, kConsumerThreads);
+    if (kg == 0) push_partial<RM>(cluster, c.recv, c.local, acc, count, rank, csize, tcol, lane);
+}
+
 // ---------------------------------------------------------------------------------------------- dense linear
 
+// grid (split, out / 128), cluster (split, 1, 1)
 template <int N, int RM>
 __global__ void __launch_bounds__(kGemvThreads, 2) dense_gemv_kernel(const DenseArgs a) {
-    extern __shared__ __align__(128) uint8_t smem[];
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t* smem = aligned_smem(smem_raw);
     cg::cluster_group cluster = cg::this_cluster();
-    const uint32_t rank = cluster.block_rank(), blk = blockIdx.y;
+    const uint32_t rank = cluster.block_rank(), csize = a.split, blk = blockIdx.y;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     uint32_t b0, b1;
     slice_blocks(a.in / 128u, a.split, rank, b0, b1);
     const uint32_t nblk = b1 - b0, nrows = nblk * 8u;
     const uint32_t tile_bytes = 2u * a.n, row_bytes = 16u * a.n, out_tiles = a.out / 16u;
     const Ring rc{a.ring.stage_rows, a.ring.stages};
-    const GemvSmem L = gemv_smem(RM, a.slice_max, rc.stage_rows * row_bytes, rc.stages);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);
-    uint64_t* empty = full + kMaxStages;
-    __half* xp = reinterpret_cast<__half*>(smem + L.xp);
-    float* partial = reinterpret_cast<float*>(smem + L.partial);
-    uint8_t* ring = smem + L.ring;
+    const CtaSmem c = carve(smem, gemv_smem(RM, a.slice_max, csize, rc.stage_rows * row_bytes, rc.stages));
     const uint32_t xstride = a.slice_max + kXpPad;
 
-    if (tid == 0) {
-        for (uint32_t s = 0; s < rc.stages; ++s) {
-            mbar_init(&full[s], 1u);
-            mbar_init(&empty[s], kConsumerWarps);
-        }
-        mbar_init_fence();
-    }
-    for (uint32_t i = a.rows * xstride + tid; i < RM * xstride; i += kGemvThreads) xp[i] = __float2half_rn(0.0f);
+    const bool traced = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+    if (traced && tid == 0) a.trace[0] = clock64();
+    init_barriers(c, rc.stages);
+    for (uint32_t i = a.rows * xstride + tid; i < RM * xstride; i += kGemvThreads) c.xp[i] = __float2half_rn(0.0f);
     __syncthreads();
+    if (traced && tid == 0) a.trace[1] = clock64();
 
     uint32_t chunk = 0;
     if (warp == kConsumerWarps) {
+        // the weights do not depend on the stream's previous kernel: start them, then let the next kernel do the same
         const uint8_t* src = a.trellis + ((size_t)(b0 * 8u) * out_tiles + blk * 8u) * tile_bytes;
-        produce_slab(ring, full, empty, src, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, chunk, lane, a.err);
+        produce_slab(c.ring, c.full, c.empty, src, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, chunk, lane, a.err);
+        pdl_trigger();
     } else {
+        pdl_trigger();
+        pdl_wait();  // x may be the previous kernel's output
         for (uint32_t task = warp; task < a.rows * nblk; task += kConsumerWarps) {
             const uint32_t row = task / nblk, b = task - row * nblk;
             const uint32_t k0 = (b0 + b) * 128u;
             prepare_block(a.x, a.x_dt, (size_t)row * a.in + k0, static_cast<const __half*>(a.suh) + k0,
-                          xp + row * xstride + b * 128u, lane);
+                          c.xp + row * xstride + b * 128u, lane);
         }
-        named_sync(1, 32u * kConsumerWarps);
-        float acc[RowCap<RM>::kMB][2][4] = {};
-        consume_slab<N, CB, RM>(ring, full, empty, nrows, a.n, a.mask, rc, xp, xstride, chunk, warp, lane, acc, a.err);
-        store_partial<RM>(partial, acc, warp, lane);
+        named_sync(1, kConsumerThreads);
+        if (traced && tid == 0) {
+            a.trace[2] = clock64();
+            mbar_wait(&c.full[0], 0u);
+            a.trace[3] = clock64();
+        }
+        gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, chunk, a.rows, rank, csize, warp, lane, a.err);
+        if (traced && tid == 0) a.trace[4] = clock64();
     }
-    cluster.sync();
-    if (rank == 0 && warp < kConsumerWarps) {
-        for (uint32_t row = warp; row < a.rows; row += kConsumerWarps) {
+    cluster_arrive();
+    if (rank >= a.rows) return;  // owns no row: nothing reads this CTA's shared memory after its arrival
+    cluster_wait();
+    if (traced && tid == 0) a.trace[5] = clock64();
+    if (warp < kConsumerWarps) {
+        const uint32_t owned = rows_owned(RM, csize);
+        for (uint32_t i = warp; i * csize + rank < a.rows; i += kConsumerWarps) {
+            const uint32_t row = i * csize + rank;
             float v[4];
-            gather_row(cluster, partial, row, 0, 1, a.split, lane, v);
+            gather_owned(c.recv, owned, i, 0, 1, csize, lane, v);
             finish_block(v, static_cast<const __half*>(a.svh) + blk * 128u, lane);
 #pragma unroll
             for (int j = 0; j < 4; ++j) store_act(a.y, a.x_dt, (size_t)row * a.out + blk * 128u + lane + 32u * j, v[j]);
         }
     }
-    cluster.sync();
+    if (traced && tid == 0) a.trace[6] = clock64();
 }
 
 // ---------------------------------------------------------------------------------------------- routed experts
@@ -131,19 +188,22 @@ __device__ __forceinline__ float swiglu(float g, float u, float limit, int clamp
 }
 
 // grid (2 SG, inter/128, row-slots), cluster (2 SG, 1, 1): cluster rank r streams projection r & 1 (0 gate, 1 up), K
-// slice r >> 1. The leader finishes both projections, applies SwiGLU and prepares the 128 values as inputs of the down
-// projection (ref.moeRow's middle, ref.zig:98-105; the reference kernels' "mid": src/kernels/hip/routed.hpp:64-112).
+// slice r >> 1. A row's owner finishes both projections, applies SwiGLU and prepares the 128 values as inputs of the
+// down projection (ref.moeRow's middle, ref.zig:98-105; the reference kernels' "mid": src/kernels/hip/routed.hpp:64-112).
 template <int N, int RM>
 __global__ void __launch_bounds__(kGemvThreads, 2) moe_gate_up_kernel(const MoeArgs a) {
-    extern __shared__ __align__(128) uint8_t smem[];
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t* smem = aligned_smem(smem_raw);
     __shared__ uint32_t s_inds[kMaxSlots];
     __shared__ uint16_t s_members[kMaxSlots];
     __shared__ uint32_t s_count;
     cg::cluster_group cluster = cg::this_cluster();
-    const uint32_t rank = cluster.block_rank(), ib = blockIdx.y, j = blockIdx.z;
+    const uint32_t rank = cluster.block_rank(), csize = 2u * a.split_gu, ib = blockIdx.y, j = blockIdx.z;
     const uint32_t proj = rank & 1u, kpart = rank >> 1;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t H = a.hidden, I = a.inter;
+    pdl_wait();     // the routing (and x) may be the previous kernel's output
+    pdl_trigger();  // after the wait: the down launch reads the routing ahead of its own wait
     const Members mem = find_members(static_cast<const uint32_t*>(a.inds), a.rows * a.topk, a.experts, j, s_inds,
                                      s_members, &s_count);
     if (mem.skip) return;
@@ -154,50 +214,41 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_gate_up_kernel(const MoeA
     const uint32_t nblk = b1 - b0, nrows = nblk * 8u;
     const uint32_t tile_bytes = 2u * a.n, row_bytes = 16u * a.n, out_tiles = I / 16u;
     const Ring rc{a.ring_gu.stage_rows, a.ring_gu.stages};
-    const GemvSmem L = gemv_smem(RM, a.slice_max_gu, rc.stage_rows * row_bytes, rc.stages);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);
-    uint64_t* empty = full + kMaxStages;
-    __half* xp = reinterpret_cast<__half*>(smem + L.xp);
-    float* partial = reinterpret_cast<float*>(smem + L.partial);
-    uint8_t* ring = smem + L.ring;
+    const CtaSmem c = carve(smem, gemv_smem(RM, a.slice_max_gu, csize, rc.stage_rows * row_bytes, rc.stages));
     const uint32_t xstride = a.slice_max_gu + kXpPad;
-    if (tid == 0) {
-        for (uint32_t s = 0; s < rc.stages; ++s) {
-            mbar_init(&full[s], 1u);
-            mbar_init(&empty[s], kConsumerWarps);
-        }
-        mbar_init_fence();
-    }
+    init_barriers(c, rc.stages);
     __syncthreads();
 
     const size_t expert_bytes = (size_t)(H / 16u) * out_tiles * tile_bytes;
     const uint8_t* wsrc = (proj ? a.up_t : a.gate_t) + e * expert_bytes + ((size_t)(b0 * 8u) * out_tiles + ib * 8u) * tile_bytes;
     const __half* suh = static_cast<const __half*>(proj ? a.up_suh : a.gate_suh) + (size_t)e * H;
+    const uint32_t owned = rows_owned(RM, csize);
     uint32_t chunk = 0;
     for (uint32_t m0 = 0; m0 < mem.count; m0 += RM) {
         const uint32_t mcount = min((uint32_t)RM, mem.count - m0);
         if (warp == kConsumerWarps) {
-            produce_slab(ring, full, empty, wsrc, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, chunk, lane, a.err);
+            produce_slab(c.ring, c.full, c.empty, wsrc, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, chunk, lane, a.err);
         } else {
-            for (uint32_t i = mcount * xstride + tid; i < RM * xstride; i += 32u * kConsumerWarps)
-                xp[i] = __float2half_rn(0.0f);
+            for (uint32_t i = mcount * xstride + tid; i < RM * xstride; i += kConsumerThreads) c.xp[i] = __float2half_rn(0.0f);
             for (uint32_t task = warp; task < mcount * nblk; task += kConsumerWarps) {
                 const uint32_t m = task / nblk, b = task - m * nblk;
                 const uint32_t row = s_members[m0 + m] / a.topk, k0 = (b0 + b) * 128u;
-                prepare_block(a.x, a.x_dt, (size_t)row * H + k0, suh + k0, xp + m * xstride + b * 128u, lane);
+                prepare_block(a.x, a.x_dt, (size_t)row * H + k0, suh + k0, c.xp + m * xstride + b * 128u, lane);
             }
-            named_sync(1, 32u * kConsumerWarps);
-            float acc[RowCap<RM>::kMB][2][4] = {};
-            consume_slab<N, CB, RM>(ring, full, empty, nrows, a.n, a.mask, rc, xp, xstride, chunk, warp, lane, acc, a.err);
-            store_partial<RM>(partial, acc, warp, lane);
+            named_sync(1, kConsumerThreads);
+            gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, chunk, mcount, rank, csize, warp, lane, a.err);
         }
-        cluster.sync();
-        if (rank == 0 && warp < kConsumerWarps) {
+        cluster_arrive();
+        const bool last = m0 + RM >= mem.count;
+        if (last && rank >= mcount) return;
+        cluster_wait();
+        if (warp < kConsumerWarps) {
             const size_t eo = (size_t)e * I + ib * 128u;
-            for (uint32_t m = warp; m < mcount; m += kConsumerWarps) {
+            for (uint32_t i = warp; i * csize + rank < mcount; i += kConsumerWarps) {
+                const uint32_t m = i * csize + rank;
                 float g[4], u[4];
-                gather_row(cluster, partial, m, 0, 2, a.split_gu, lane, g);
-                gather_row(cluster, partial, m, 1, 2, a.split_gu, lane, u);
+                gather_owned(c.recv, owned, i, 0, 2, a.split_gu, lane, g);
+                gather_owned(c.recv, owned, i, 1, 2, a.split_gu, lane, u);
                 finish_block(g, static_cast<const __half*>(a.gate_svh) + eo, lane);
                 finish_block(u, static_cast<const __half*>(a.up_svh) + eo, lane);
                 float d[4];
@@ -211,7 +262,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_gate_up_kernel(const MoeA
                 for (int q = 0; q < 4; ++q) hd[lane + 32u * q] = __float2half_rn(d[q] * kHadScale);
             }
         }
-        cluster.sync();
+        if (!last) cluster.sync();  // the next pass overwrites the receive tiles
     }
 }
 
@@ -219,14 +270,16 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_gate_up_kernel(const MoeA
 // prepared rows hd, finished per row-slot into v (f16): the value the merge weights by the slot's score.
 template <int N, int RM>
 __global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs a) {
-    extern __shared__ __align__(128) uint8_t smem[];
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t* smem = aligned_smem(smem_raw);
     __shared__ uint32_t s_inds[kMaxSlots];
     __shared__ uint16_t s_members[kMaxSlots];
     __shared__ uint32_t s_count;
     cg::cluster_group cluster = cg::this_cluster();
-    const uint32_t rank = cluster.block_rank(), hb = blockIdx.y, j = blockIdx.z;
+    const uint32_t rank = cluster.block_rank(), csize = a.split_d, hb = blockIdx.y, j = blockIdx.z;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t H = a.hidden, I = a.inter;
+    // the routing was complete before the gate|up launch started, so it can be read ahead of pdl_wait
     const Members mem = find_members(static_cast<const uint32_t*>(a.inds), a.rows * a.topk, a.experts, j, s_inds,
                                      s_members, &s_count);
     if (mem.skip) return;
@@ -237,59 +290,53 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs
     const uint32_t nblk = b1 - b0, nrows = nblk * 8u;
     const uint32_t tile_bytes = 2u * a.n, row_bytes = 16u * a.n, out_tiles = H / 16u;
     const Ring rc{a.ring_d.stage_rows, a.ring_d.stages};
-    const GemvSmem L = gemv_smem(RM, a.slice_max_d, rc.stage_rows * row_bytes, rc.stages);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);
-    uint64_t* empty = full + kMaxStages;
-    __half* xp = reinterpret_cast<__half*>(smem + L.xp);
-    float* partial = reinterpret_cast<float*>(smem + L.partial);
-    uint8_t* ring = smem + L.ring;
+    const CtaSmem c = carve(smem, gemv_smem(RM, a.slice_max_d, csize, rc.stage_rows * row_bytes, rc.stages));
     const uint32_t xstride = a.slice_max_d + kXpPad;
-    if (tid == 0) {
-        for (uint32_t s = 0; s < rc.stages; ++s) {
-            mbar_init(&full[s], 1u);
-            mbar_init(&empty[s], kConsumerWarps);
-        }
-        mbar_init_fence();
-    }
+    init_barriers(c, rc.stages);
     __syncthreads();
 
     const size_t expert_bytes = (size_t)(I / 16u) * out_tiles * tile_bytes;
     const uint8_t* wsrc = a.down_t + e * expert_bytes + ((size_t)(b0 * 8u) * out_tiles + hb * 8u) * tile_bytes;
+    const uint32_t owned = rows_owned(RM, csize);
     uint32_t chunk = 0;
     for (uint32_t m0 = 0; m0 < mem.count; m0 += RM) {
         const uint32_t mcount = min((uint32_t)RM, mem.count - m0);
         if (warp == kConsumerWarps) {
-            produce_slab(ring, full, empty, wsrc, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, chunk, lane, a.err);
+            produce_slab(c.ring, c.full, c.empty, wsrc, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, chunk, lane, a.err);
+            pdl_trigger();
         } else {
-            for (uint32_t i = mcount * xstride + tid; i < RM * xstride; i += 32u * kConsumerWarps)
-                xp[i] = __float2half_rn(0.0f);
+            pdl_trigger();
+            pdl_wait();  // hd is the gate|up launch's output
+            for (uint32_t i = mcount * xstride + tid; i < RM * xstride; i += kConsumerThreads) c.xp[i] = __float2half_rn(0.0f);
             for (uint32_t task = warp; task < mcount * nblk; task += kConsumerWarps) {
                 const uint32_t m = task / nblk, b = task - m * nblk;
                 const __half* src = static_cast<const __half*>(a.hd) + (size_t)s_members[m0 + m] * I + (b0 + b) * 128u;
-                __half* dst = xp + m * xstride + b * 128u;
+                __half* dst = c.xp + m * xstride + b * 128u;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const uint32_t i = lane + 32u * q;
                     dst[(i & ~15u) | lane_order16(i & 15u)] = src[i];
                 }
             }
-            named_sync(1, 32u * kConsumerWarps);
-            float acc[RowCap<RM>::kMB][2][4] = {};
-            consume_slab<N, CB, RM>(ring, full, empty, nrows, a.n, a.mask, rc, xp, xstride, chunk, warp, lane, acc, a.err);
-            store_partial<RM>(partial, acc, warp, lane);
+            named_sync(1, kConsumerThreads);
+            gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, chunk, mcount, rank, csize, warp, lane, a.err);
         }
-        cluster.sync();
-        if (rank == 0 && warp < kConsumerWarps) {
-            for (uint32_t m = warp; m < mcount; m += kConsumerWarps) {
+        cluster_arrive();
+        const bool last = m0 + RM >= mem.count;
+        if (last && rank >= mcount) return;
+        cluster_wait();
+        if (warp < kConsumerWarps) {
+            for (uint32_t i = warp; i * csize + rank < mcount; i += kConsumerWarps) {
+                const uint32_t m = i * csize + rank;
                 float v[4];
-                gather_row(cluster, partial, m, 0, 1, a.split_d, lane, v);
+                gather_owned(c.recv, owned, i, 0, 1, csize, lane, v);
                 finish_block(v, static_cast<const __half*>(a.down_svh) + (size_t)e * H + hb * 128u, lane);
                 __half* vo = static_cast<__half*>(a.v) + (size_t)s_members[m0 + m] * H + hb * 128u;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) vo[lane + 32u * q] = __float2half_rn(v[q]);
             }
         }
-        cluster.sync();
+        if (!last) cluster.sync();
     }
 }
 
@@ -298,6 +345,8 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs
 // (root.moeWithShared, src/root.zig:976-984).
 __global__ void __launch_bounds__(256) moe_merge_kernel(const MoeArgs a) {
     const uint32_t i = blockIdx.x * 256u + threadIdx.x, row = blockIdx.y;
+    pdl_trigger();
+    pdl_wait();  // v is the down launch's output
     if (i >= a.hidden) return;
     float acc = 0.0f;
     for (uint32_t k = 0; k < a.topk; ++k) {
@@ -318,24 +367,40 @@ __global__ void __launch_bounds__(256) moe_merge_kernel(const MoeArgs a) {
 template <typename Args>
 using KernelFn = void (*)(const Args);
 
+// Raises a kernel's dynamic shared-memory limit once per process (the call is not free, the launches are hot).
+cudaError_t allow_big_smem(const void* fn) {
+    static std::mutex mu;
+    static std::unordered_set<const void*> done;
+    std::lock_guard<std::mutex> lock(mu);
+    if (done.count(fn)) return cudaSuccess;
+    cudaError_t rc = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemvSmemLimit);
+    if (rc == cudaSuccess) rc = cudaFuncSetAttribute(fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);  // clusters of 16
+    if (rc == cudaSuccess) done.insert(fn);
+    return rc;
+}
+
+// A cluster launch that may start while the stream's previous kernel is still running (the kernels order themselves
+// with griddepcontrol).
 template <typename Args>
 cudaError_t launch_cluster(KernelFn<Args> fn, const Args& a, dim3 grid, uint32_t cluster_x, uint32_t smem_bytes,
-                           cudaStream_t stream) {
-    cudaError_t rc = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)smem_bytes);
+                           bool overlap, cudaStream_t stream) {
+    if (smem_bytes > kGemvSmemLimit) return cudaErrorInvalidValue;
+    cudaError_t rc = allow_big_smem(reinterpret_cast<const void*>(fn));
     if (rc != cudaSuccess) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(kGemvThreads, 1, 1);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = cluster_x;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = overlap ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, fn, a);
 }
 
@@ -361,28 +426,36 @@ cudaError_t launch_cluster(KernelFn<Args> fn, const Args& a, dim3 grid, uint32_t
 cudaError_t T3_CAT(launch_dense_gemv_cb, T3_CB)(const DenseArgs& a, cudaStream_t stream) {
     const uint32_t rm = row_cap_for(a.rows);
     KernelFn<DenseArgs> fn = T3_PICK(dense_gemv_kernel, a.n, rm);
-    return launch_cluster(fn, a, dim3(a.split, a.out / 128u, 1), a.split, gemv_smem_bytes(rm, a.slice_max, a.n, a.ring),
-                          stream);
+    return launch_cluster(fn, a, dim3(a.split, a.out / 128u, 1), a.split, gemv_smem_bytes(rm, a.slice_max, a.split, a.n, a.ring),
+                          a.overlap != 0, stream);
 }
 
 cudaError_t T3_CAT(launch_moe_gate_up_cb, T3_CB)(const MoeArgs& a, cudaStream_t stream) {
     const uint32_t rm = row_cap_for(a.rows);
     KernelFn<MoeArgs> fn = T3_PICK(moe_gate_up_kernel, a.n, rm);
     return launch_cluster(fn, a, dim3(2u * a.split_gu, a.inter / 128u, a.rows * a.topk), 2u * a.split_gu,
-                          gemv_smem_bytes(rm, a.slice_max_gu, a.n, a.ring_gu), stream);
+                          gemv_smem_bytes(rm, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu), a.overlap != 0, stream);
 }
 
 cudaError_t T3_CAT(launch_moe_down_cb, T3_CB)(const MoeArgs& a, cudaStream_t stream) {
     const uint32_t rm = row_cap_for(a.rows);
     KernelFn<MoeArgs> fn = T3_PICK(moe_down_kernel, a.n, rm);
     return launch_cluster(fn, a, dim3(a.split_d, a.hidden / 128u, a.rows * a.topk), a.split_d,
-                          gemv_smem_bytes(rm, a.slice_max_d, a.n, a.ring_d), stream);
+                          gemv_smem_bytes(rm, a.slice_max_d, a.split_d, a.n, a.ring_d), a.overlap != 0, stream);
 }
 
 #if T3_CB == 0
 cudaError_t launch_moe_merge(const MoeArgs& a, cudaStream_t stream) {
-    moe_merge_kernel<<<dim3((a.hidden + 255u) / 256u, a.rows, 1), 256, 0, stream>>>(a);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((a.hidden + 255u) / 256u, a.rows, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = a.overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, moe_merge_kernel, a);
 }
 #endif
 

@@ -1,11 +1,12 @@
 // The decode-row engine's core: one CTA streams a slab of trellis codes (a K slice of one 128-wide output block)
 // through a ring of shared-memory stages filled by bulk copies, decodes each tile in registers straight into
 // mma.sync B fragments, and multiplies it with up to 32 prepared activation rows held in shared memory. Decoded weights
-// never leave registers. A thread-block cluster splits K; the partial sums meet over distributed shared memory in rank
-// order (deterministic) and the leader CTA runs the output rotation.
+// never leave registers. A thread-block cluster splits K; every CTA pushes its partial sums over distributed shared
+// memory to the CTA that owns the row (a reduce-scatter in rank order, deterministic), and the owner runs the output
+// rotation.
 //
-// Roles of the 288 threads: warps 0-7 are consumers (warp w owns output tile w of the block: 16 of the 128 columns, so no
-// cross-warp reduction exists), warp 8 is the copy producer.
+// Roles of the 544 threads: warps 0-15 are consumers (warp w owns output tile w % 8 of the block, 16 of its 128 columns,
+// and every second tk row, starting at w / 8), warp 16 is the copy producer.
 //
 // What it computes follows turboexl3's host reference (src/core/format.zig:334-389): xp = f16(H128(f16(x) suh)),
 // z = f16(sum xp W_hat) with f32 accumulation, y = f16(H128(z) svh). The launch shape has no counterpart in the
@@ -21,40 +22,60 @@ namespace t3 {
 
 namespace cg = cooperative_groups;
 
-constexpr uint32_t kConsumerWarps = 8;
-constexpr uint32_t kGemvThreads = 32u * (kConsumerWarps + 1u);
+constexpr uint32_t kTileWarps = 8;                         // output tiles of a 128-wide block
+constexpr uint32_t kKGroups = 2;                           // warps sharing an output tile, interleaved over tk rows
+constexpr uint32_t kConsumerWarps = kTileWarps * kKGroups;
+constexpr uint32_t kConsumerThreads = 32u * kConsumerWarps;
+constexpr uint32_t kGemvThreads = kConsumerThreads + 32u;
 constexpr uint32_t kMaxStages = 32;
-constexpr uint32_t kPartialStride = 136;  // floats per row of the partial-sum tile (128 + 8: conflict-free float2 stores)
+constexpr uint32_t kPartialStride = 136;  // floats per row of a partial-sum tile (128 + 8: conflict-free float2 stores)
 constexpr uint32_t kXpPad = 16;           // halfs added to an xp row so a quad's 8-byte loads spread over the banks
+constexpr uint32_t kBatch = 4;            // tiles a warp decodes back to back before their MMAs (instruction-level overlap)
+constexpr uint32_t kStageRows = kKGroups * kBatch;  // tk rows of a ring stage: one 128-input block, one batch a warp
 
-// How the ring is cut for one launch (host-chosen, see plan_ring in t3_api.cu)
+// How the ring is cut for one launch (host-chosen)
 struct Ring {
-    uint32_t stage_rows;  // tk rows a stage (each row: the block's 8 tiles = 16 n bytes)
-    uint32_t stages;      // 2..kMaxStages
+    uint32_t stage_rows;  // tk rows a stage, always kStageRows (each row: the block's 8 tiles = 16 n bytes)
+    uint32_t stages;      // 1..kMaxStages
 };
 
 template <int RM>
 struct RowCap {
     static_assert(RM == 8 || RM == 16 || RM == 32, "row capacity");
-    static constexpr int kMB = RM == 32 ? 2 : 1;      // 16-row MMA blocks
-    static constexpr bool kHalf = RM == 8;            // rows 8-15 of the block are absent
-    static constexpr int kPartialRows = RM;
+    static constexpr int kMB = RM == 32 ? 2 : 1;  // 16-row MMA blocks
+    static constexpr bool kHalf = RM == 8;        // rows 8-15 of the block are absent
 };
 
-// Shared-memory carve-up of a GEMV CTA (byte offsets from a 128-byte aligned base)
+// Shared-memory carve-up of a GEMV CTA (byte offsets from a 128-byte aligned base). `cluster` CTAs reduce together.
 struct GemvSmem {
-    uint32_t bars, xp, partial, ring, total;
+    uint32_t bars, xp, local, recv, ring, total;
 };
-__host__ __device__ inline GemvSmem gemv_smem(uint32_t rm, uint32_t slice_k, uint32_t stage_bytes, uint32_t stages) {
+__host__ __device__ inline uint32_t rows_owned(uint32_t rm, uint32_t cluster) { return (rm + cluster - 1u) / cluster; }
+__host__ __device__ inline GemvSmem gemv_smem(uint32_t rm, uint32_t slice_k, uint32_t cluster, uint32_t stage_bytes,
+                                              uint32_t stages) {
     GemvSmem s;
     s.bars = 0;
     s.xp = 2u * kMaxStages * 8u;
     const uint32_t xp_bytes = rm * (slice_k + kXpPad) * 2u;
-    s.partial = s.xp + ((xp_bytes + 127u) & ~127u);
-    s.ring = s.partial + ((rm * kPartialStride * 4u + 127u) & ~127u);
+    s.local = s.xp + ((xp_bytes + 127u) & ~127u);
+    s.recv = s.local + ((rm * kPartialStride * 4u + 127u) & ~127u);
+    s.ring = s.recv + ((cluster * rows_owned(rm, cluster) * kPartialStride * 4u + 127u) & ~127u);
     s.total = s.ring + stage_bytes * stages;
     return s;
 }
+
+// The CTA's dynamic shared memory rounded up to 128 bytes (launches ask for kSmemSlack bytes more than the carve-up).
+constexpr uint32_t kSmemSlack = 128;
+__device__ __forceinline__ uint8_t* aligned_smem(uint8_t* raw) {
+    const uint32_t a = smem_addr(raw);
+    return raw + (((a + 127u) & ~127u) - a);
+}
+
+// Programmatic dependent launch: `pdl_trigger` lets the next kernel of the stream start its own prologue (its weight
+// copies do not depend on this kernel); `pdl_wait` blocks until the previous kernel of the stream has completed and its
+// writes are visible. Both are no-ops for a launch without the attribute.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---- producer -----------------------------------------------------------------------------------------------------
 
@@ -63,11 +84,11 @@ __host__ __device__ inline GemvSmem gemv_smem(uint32_t rm, uint32_t slice_k, uin
 __device__ __forceinline__ void produce_slab(uint8_t* ring, uint64_t* full, uint64_t* empty, const uint8_t* src,
                                              size_t src_row_stride, uint32_t nrows, uint32_t row_bytes, Ring rc,
                                              uint32_t& chunk, uint32_t lane, uint32_t* err) {
-    const uint32_t stage_bytes = rc.stage_rows * row_bytes;
-    for (uint32_t r0 = 0; r0 < nrows; r0 += rc.stage_rows, ++chunk) {
+    const uint32_t stage_bytes = kStageRows * row_bytes;
+    for (uint32_t r0 = 0; r0 < nrows; r0 += kStageRows, ++chunk) {
         const uint32_t slot = chunk % rc.stages, use = chunk / rc.stages;
         if (use > 0 && !mbar_wait(&empty[slot], (use - 1u) & 1u)) report(err, kErrEmptyWait);
-        const uint32_t here = min(rc.stage_rows, nrows - r0);
+        const uint32_t here = min(kStageRows, nrows - r0);
         if (lane == 0) mbar_arrive_expect_tx(&full[slot], here * row_bytes);
         __syncwarp();
         for (uint32_t r = lane; r < here; r += 32u)
@@ -78,38 +99,66 @@ __device__ __forceinline__ void produce_slab(uint8_t* ring, uint64_t* full, uint
 
 // ---- consumer -----------------------------------------------------------------------------------------------------
 
-// Warp `warp` folds its tile column of tk rows [0, nrows) into acc. xp: prepared rows in lane order, row stride
-// `xstride` halfs, k = 0 at the slab's first input. acc[mb][nt] is the mma C fragment of rows 16 mb .. 16 mb + 15,
-// columns 16 warp + 8 nt .. + 7.
+// one decoded tile times the prepared rows at inputs [16 tk, 16 tk + 16): xk points at the lane's first row there
+template <int RM>
+__device__ __forceinline__ void mma_tile(float (&acc)[RowCap<RM>::kMB][2][4], const __half* xk, uint32_t xstride,
+                                         const uint32_t (&b)[4]) {
+#pragma unroll
+    for (int mb = 0; mb < RowCap<RM>::kMB; ++mb) {
+        const uint2 lo = *reinterpret_cast<const uint2*>(xk + (mb * 16) * xstride);
+        uint2 hi = make_uint2(0u, 0u);
+        if (!RowCap<RM>::kHalf) hi = *reinterpret_cast<const uint2*>(xk + (mb * 16 + 8) * xstride);
+        mma16816(acc[mb][0], lo.x, hi.x, lo.y, hi.y, b[0], b[1]);
+        mma16816(acc[mb][1], lo.x, hi.x, lo.y, hi.y, b[2], b[3]);
+    }
+}
+
+// Consumer warp (tile column `tcol`, K group `kg`) folds tk rows kg, kg + kKGroups, ... of [0, nrows) into acc.
+// xp: prepared rows in lane order, row stride `xstride` halfs, k = 0 at the slab's first input. acc[mb][nt] is the mma C
+// fragment of rows 16 mb .. 16 mb + 15, columns 16 tcol + 8 nt .. + 7.
+// A stage holds kStageRows tk rows, so a warp's share of a full stage is exactly one batch of kBatch tiles, and with the
+// rate a template constant every shared-memory offset inside a stage is an immediate.
 template <int N, int CB, int RM>
 __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full, uint64_t* empty, uint32_t nrows,
-                                             uint32_t n, uint32_t mask, Ring rc, const __half* xp, uint32_t xstride,
-                                             uint32_t& chunk, uint32_t warp, uint32_t lane,
+                                             uint32_t n_rt, uint32_t mask, Ring rc, const __half* xp, uint32_t xstride,
+                                             uint32_t& chunk, uint32_t tcol, uint32_t kg, uint32_t lane,
                                              float (&acc)[RowCap<RM>::kMB][2][4], uint32_t* err) {
-    constexpr int MB = RowCap<RM>::kMB;
-    const uint32_t tile_bytes = 2u * n, row_bytes = 16u * n, stage_bytes = rc.stage_rows * row_bytes;
-    const __half* xa = xp + (lane >> 2) * xstride + 4u * (lane & 3u);
-    LanePlan<(N > 0 ? N : 16)> plan;
+    constexpr int NP = N > 0 ? N : 16;
+    constexpr uint32_t kRaw = raw_words(NP);
+    const uint32_t n = N > 0 ? (uint32_t)N : n_rt;
+    const uint32_t tile_bytes = 2u * n, row_bytes = 16u * n, stage_bytes = kStageRows * row_bytes;
+    LanePlan<NP> plan;
     if (N > 0) plan.init(lane);
-    for (uint32_t r0 = 0; r0 < nrows; r0 += rc.stage_rows, ++chunk) {
+    // byte offsets of the lane's raw words inside a tile row of the block, from the warp's first row of a stage
+    uint32_t woff[kRaw];
+#pragma unroll
+    for (uint32_t i = 0; i < kRaw; ++i) woff[i] = tcol * tile_bytes + kg * row_bytes + plan.idx[i] * 4u;
+    const __half* xa = xp + (lane >> 2) * xstride + 4u * (lane & 3u) + kg * 16u;
+    for (uint32_t r0 = 0; r0 < nrows; r0 += kStageRows, ++chunk) {
         const uint32_t slot = chunk % rc.stages, use = chunk / rc.stages;
         if (!mbar_wait(&full[slot], use & 1u)) report(err, kErrFullWait);
-        const uint32_t here = min(rc.stage_rows, nrows - r0);
-        const uint8_t* st = ring + slot * stage_bytes + warp * tile_bytes;
-#pragma unroll 2
-        for (uint32_t r = 0; r < here; ++r) {
-            uint32_t b[4];
-            const uint32_t* tile = reinterpret_cast<const uint32_t*>(st + r * row_bytes);
-            if (N > 0) decode_lane<(N > 0 ? N : 16), CB>(tile, plan, mask, b);
-            else decode_lane_any<CB>(tile, n, lane, mask, b);
-            const __half* xk = xa + (r0 + r) * 16u;
+        const uint32_t here = min(kStageRows, nrows - r0);
+        const uint8_t* st = ring + slot * stage_bytes;
+        const __half* xs = xa + r0 * 16u;
+        if (N > 0 && here == kKGroups * kBatch) {
+            uint32_t raw[kBatch][kRaw];
 #pragma unroll
-            for (int mb = 0; mb < MB; ++mb) {
-                const uint2 lo = *reinterpret_cast<const uint2*>(xk + (mb * 16) * xstride);
-                uint2 hi = make_uint2(0u, 0u);
-                if (!RowCap<RM>::kHalf) hi = *reinterpret_cast<const uint2*>(xk + (mb * 16 + 8) * xstride);
-                mma16816(acc[mb][0], lo.x, hi.x, lo.y, hi.y, b[0], b[1]);
-                mma16816(acc[mb][1], lo.x, hi.x, lo.y, hi.y, b[2], b[3]);
+            for (uint32_t i = 0; i < kBatch; ++i)
+#pragma unroll
+                for (uint32_t w = 0; w < kRaw; ++w)
+                    raw[i][w] = *reinterpret_cast<const uint32_t*>(st + woff[w] + i * kKGroups * row_bytes);
+            uint32_t b[kBatch][4];
+#pragma unroll
+            for (uint32_t i = 0; i < kBatch; ++i) decode_raw<NP, CB>(raw[i], plan, mask, b[i]);
+#pragma unroll
+            for (uint32_t i = 0; i < kBatch; ++i) mma_tile<RM>(acc, xs + i * kKGroups * 16u, xstride, b[i]);
+        } else {
+            for (uint32_t r = kg; r < here; r += kKGroups) {
+                uint32_t b[4];
+                const uint32_t* tile = reinterpret_cast<const uint32_t*>(st + tcol * tile_bytes + r * row_bytes);
+                if (N > 0) decode_lane<NP, CB>(tile, plan, mask, b);
+                else decode_lane_any<CB>(tile, n, lane, mask, b);
+                mma_tile<RM>(acc, xp + (lane >> 2) * xstride + 4u * (lane & 3u) + (r0 + r) * 16u, xstride, b);
             }
         }
         __syncwarp();
@@ -117,28 +166,66 @@ __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full
     }
 }
 
-// the warp's accumulators into the CTA's partial-sum tile [RM][kPartialStride]
+// ---- the cluster reduce-scatter -----------------------------------------------------------------------------------
+
+// K group 1's accumulators into the CTA's local tile [RM][kPartialStride]
 template <int RM>
-__device__ __forceinline__ void store_partial(float* partial, const float (&acc)[RowCap<RM>::kMB][2][4], uint32_t warp,
-                                              uint32_t lane) {
+__device__ __forceinline__ void store_local(float* local, const float (&acc)[RowCap<RM>::kMB][2][4], uint32_t tcol,
+                                            uint32_t lane) {
     const uint32_t g = lane >> 2, q = lane & 3u;
 #pragma unroll
     for (int mb = 0; mb < RowCap<RM>::kMB; ++mb)
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-            const uint32_t col = warp * 16u + nt * 8u + 2u * q;
-            *reinterpret_cast<float2*>(partial + (mb * 16 + g) * kPartialStride + col) =
-                make_float2(acc[mb][nt][0], acc[mb][nt][1]);
+            const uint32_t col = tcol * 16u + nt * 8u + 2u * q;
+            *reinterpret_cast<float2*>(local + (mb * 16 + g) * kPartialStride + col) = make_float2(acc[mb][nt][0], acc[mb][nt][1]);
             if (!RowCap<RM>::kHalf)
-                *reinterpret_cast<float2*>(partial + (mb * 16 + g + 8) * kPartialStride + col) =
+                *reinterpret_cast<float2*>(local + (mb * 16 + g + 8) * kPartialStride + col) =
                     make_float2(acc[mb][nt][2], acc[mb][nt][3]);
         }
 }
 
-// ---- prepare ------------------------------------------------------------------------------------------------------
+// K group 0 adds group 1's tile to its accumulators and pushes each live row m (< count) to the CTA that owns it,
+// rank m % csize, into that CTA's recv[my rank][m / csize][column]. Remote stores; the cluster barrier that follows
+// makes them visible.
+template <int RM>
+__device__ __forceinline__ void push_partial(cg::cluster_group& cluster, float* recv, const float* local,
+                                             const float (&acc)[RowCap<RM>::kMB][2][4], uint32_t count, uint32_t rank,
+                                             uint32_t csize, uint32_t tcol, uint32_t lane) {
+    const uint32_t g = lane >> 2, q = lane & 3u;
+    const uint32_t owned = rows_owned(RM, csize);
+#pragma unroll
+    for (int mb = 0; mb < RowCap<RM>::kMB; ++mb)
+#pragma unroll
+        for (int h = 0; h < (RowCap<RM>::kHalf ? 1 : 2); ++h) {
+            const uint32_t m = mb * 16 + h * 8 + g;
+            if (m >= count) continue;
+            float* dst = cluster.map_shared_rank(recv, m % csize) + (rank * owned + m / csize) * kPartialStride;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const uint32_t col = tcol * 16u + nt * 8u + 2u * q;
+                const float2 o = *reinterpret_cast<const float2*>(local + m * kPartialStride + col);
+                *reinterpret_cast<float2*>(dst + col) = make_float2(acc[mb][nt][2 * h] + o.x, acc[mb][nt][2 * h + 1] + o.y);
+            }
+        }
+}
+
+// Sum over ranks first, first + step, ... (count of them) of owned row `slot`, for the lane's columns lane + 32 j
+__device__ __forceinline__ void gather_owned(const float* recv, uint32_t owned, uint32_t slot, uint32_t first,
+                                             uint32_t step, uint32_t count, uint32_t lane, float (&v)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = 0.0f;
+    for (uint32_t i = 0; i < count; ++i) {
+        const float* rp = recv + ((first + i * step) * owned + slot) * kPartialStride + lane;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = (i == 0) ? rp[32 * j] : v[j] + rp[32 * j];
+    }
+}
+
+// ---- prepare / finish ---------------------------------------------------------------------------------------------
 
 // One (row, 128-block) of the input rotation by one warp (format.prepareInput, format.zig:334-345): the block's elements
-// x[i] (dtype dt) times suh[i], H128, scaled, rounded to f16, into xp_row at the block's lane-ordered slots.
+// x[i] (dtype dt) times suh[i], H128, scaled, rounded to f16, into xp_blk at the block's lane-ordered slots.
 __device__ __forceinline__ void prepare_block(const void* x, int dt, size_t x_off, const __half* suh, __half* xp_blk,
                                               uint32_t lane) {
     float v[4];
@@ -163,19 +250,6 @@ __device__ __forceinline__ void finish_block(float (&v)[4], const __half* svh_bl
     h128_warp(v, lane);
 #pragma unroll
     for (int j = 0; j < 4; ++j) v[j] = round_half(v[j] * kHadScale * __half2float(svh_blk[lane + 32u * j]));
-}
-
-// Sum of the cluster's partial tiles for one row, taken in the given rank order (first, first + step, ...), for the
-// lane's four columns lane + 32 j.
-__device__ __forceinline__ void gather_row(cg::cluster_group& cluster, float* partial, uint32_t row, uint32_t first,
-                                           uint32_t step, uint32_t count, uint32_t lane, float (&v)[4]) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = 0.0f;
-    for (uint32_t i = 0; i < count; ++i) {
-        const float* rp = cluster.map_shared_rank(partial, first + i * step) + row * kPartialStride + lane;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] = (i == 0) ? rp[32 * j] : v[j] + rp[32 * j];
-    }
 }
 
 // K blocks [b0, b1) of rank r when nb 128-blocks are cut over s ranks

@@ -23,7 +23,9 @@ struct DenseArgs {
     uint32_t split;           // cluster size: K slices
     uint32_t slice_max;       // inputs of the largest K slice
     RingPlan ring;
+    int overlap;              // launch with the programmatic-dependent-launch attribute
     uint32_t* err;
+    unsigned long long* trace;  // optional: SM cycle counts at the phases of CTA (0, 0) (see t3_set_trace)
 };
 
 // The routed chain at decode rows (rows <= 32): row-slot s = row * topk + k runs expert inds[s]
@@ -45,6 +47,7 @@ struct MoeArgs {
     uint32_t split_gu, slice_max_gu;   // K slices of gate|up (cluster = 2 * split_gu), largest slice
     uint32_t split_d, slice_max_d;     // K slices of down
     RingPlan ring_gu, ring_d;
+    int overlap;
     uint32_t* err;
 };
 
@@ -54,8 +57,28 @@ cudaError_t launch_moe_down(const MoeArgs& a, int codebook, cudaStream_t stream)
 cudaError_t launch_moe_merge(const MoeArgs& a, cudaStream_t stream);
 
 // shared-memory bytes the GEMV CTAs of a plan need (for admission before launch)
-uint32_t gemv_smem_bytes(uint32_t row_cap, uint32_t slice_max, uint32_t n, RingPlan ring);
+uint32_t gemv_smem_bytes(uint32_t row_cap, uint32_t slice_max, uint32_t cluster, uint32_t n, RingPlan ring);
+// the most dynamic shared memory a GEMV CTA may be launched with
+constexpr uint32_t kGemvSmemLimit = 200u * 1024u;
 uint32_t row_cap_for(uint32_t rows);
+
+// One dense linear at prefill rows (rows > 32): prepare -> tcgen05 GEMM with the decode in its weight loader -> finish
+struct PrefillLinearArgs {
+    const void* x;
+    void* y;
+    const uint8_t* trellis;
+    const void* suh;
+    const void* svh;
+    uint32_t rows, in, out, n, mask;
+    int x_dt;
+    void* workspace;  // prefill_linear_workspace bytes
+    uint32_t* err;
+};
+size_t prefill_linear_workspace(size_t rows, uint32_t in, uint32_t out);
+cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cudaStream_t stream, int* launches);
+// The routed chain at prefill rows: route -> prepare -> GEMM(gate|up) -> mid -> GEMM(down) -> finish
+size_t prefill_moe_workspace(size_t rows, uint32_t topk, uint32_t experts, uint32_t hidden, uint32_t inter);
+cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, cudaStream_t stream, int* launches);
 
 // W_hat [in, out] f16 from the trellis
 cudaError_t launch_dequant(const uint8_t* trellis, uint32_t in, uint32_t out, uint32_t n, uint32_t mask, int codebook,

@@ -202,15 +202,19 @@ T3_HD uint32_t window_at(const uint32_t (&w)[NW], uint32_t pos, uint32_t mask) {
     return shr_pair(w[q], w[q + 1 < NW ? q + 1 : q], 48u - b) & mask;
 }
 
-// The lane's eight weights of one tile as four half2 words: {w0,w1}, {w2,w3}, {w4,w5}, {w6,w7}; b[0], b[1] are the
-// mma.m16n8k16 B fragment of tile columns 0-7, b[2], b[3] of columns 8-15. `tile` points at the tile's first word
-// (shared or global memory); `mask` is the pack's codeword-width mask (format.zig:60-62).
-template <int N, int CB>
-T3_HD void decode_lane(const uint32_t* tile, const LanePlan<N>& plan, uint32_t mask, uint32_t (&b)[4]) {
-    constexpr uint32_t kRaw = raw_words(N);
-    uint32_t raw[kRaw];
+// The lane's raw words of one tile (`tile` points at the tile's first word, shared or global memory).
+template <int N>
+T3_HD void load_lane(const uint32_t* tile, const LanePlan<N>& plan, uint32_t (&raw)[raw_words(N)]) {
 #pragma unroll
-    for (uint32_t i = 0; i < kRaw; ++i) raw[i] = tile[plan.idx[i]];
+    for (uint32_t i = 0; i < raw_words(N); ++i) raw[i] = tile[plan.idx[i]];
+}
+
+// The lane's eight weights from its raw words as four half2 words: {w0,w1}, {w2,w3}, {w4,w5}, {w6,w7}; b[0], b[1] are
+// the mma.m16n8k16 B fragment of tile columns 0-7, b[2], b[3] of columns 8-15. `mask` is the pack's codeword-width mask
+// (format.zig:60-62).
+template <int N, int CB>
+T3_HD void decode_raw(const uint32_t (&raw)[raw_words(N)], const LanePlan<N>& plan, uint32_t mask, uint32_t (&b)[4]) {
+    constexpr uint32_t kRaw = raw_words(N);
     uint32_t cw[8];
     if (uniform_shift(N)) {
         constexpr uint32_t o = (win_end(N, 0) + 16u * N - 16u) & 31u;
@@ -226,6 +230,14 @@ T3_HD void decode_lane(const uint32_t* tile, const LanePlan<N>& plan, uint32_t m
     }
 #pragma unroll
     for (uint32_t j = 0; j < 4u; ++j) b[j] = decode2<CB>(cw[2 * j], cw[2 * j + 1]);
+}
+
+// load_lane + decode_raw
+template <int N, int CB>
+T3_HD void decode_lane(const uint32_t* tile, const LanePlan<N>& plan, uint32_t mask, uint32_t (&b)[4]) {
+    uint32_t raw[raw_words(N)];
+    load_lane<N>(tile, plan, raw);
+    decode_raw<N, CB>(raw, plan, mask, b);
 }
 
 // The same for a rate known only at run time (any even n in [16, 128]): the plain per-window read, two words a window.

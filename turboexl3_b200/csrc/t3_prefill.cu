@@ -1,0 +1,674 @@
+// Prefill-row kernels (more than 32 activation rows): the trellis is decoded inside the weight loader of a tcgen05 GEMM.
+//
+//   route   : counting sort of the row-slots by expert + a table of 256-row M tiles (the reference's route:
+//             src/core/kernels/prefill/froute_count.metal, table_2.metal; src/kernels/hip/prefill/prefill.hip:22-71)
+//   prep    : input rotation of every sorted row, f16, natural order (format.prepareInput, src/core/format.zig:334-345)
+//   gemm    : z = f16(xp W_hat), 256 x 128 output tile per CTA, K in stages of 64. Warp 0 streams the activation tile
+//             with TMA (128-byte swizzle), warps 2-9 decode the stage's 32 weight tiles in registers and store them as
+//             the K-major 128-byte-swizzled B operand, warp 1 issues tcgen05.mma (two M = 128 halves share each decoded
+//             B tile; f32 accumulators in tensor memory), then warps 2-9 read the accumulators back (tcgen05.ld), round
+//             to f16 and store. (The reference's GEMM with the decode in the loader: src/core/kernels/prefill/gemm_4.metal,
+//             src/kernels/hip/prefill/prefill.hip:125-216, on Apple / gfx11 matrix units.)
+//   mid     : gate and up finish, SwiGLU, the down projection's prepare (src/kernels/hip/routed.hpp:64-112)
+//   fin     : per row, every slot's down finish and the score-weighted sum in slot order
+//             (src/kernels/hip/prefill/prefill.hip:243-264); dense linears use the plain finish.
+// Every wait is bounded: a wait that runs out sets a bit of the device error word and the kernel walks to its exit,
+// freeing its tensor memory on the way.
+#include <cuda.h>
+
+#include "t3_common.cuh"
+#include "t3_internal.h"
+
+namespace t3 {
+namespace {
+
+constexpr uint32_t kBM = 256, kBN = 128, kBK = 64;
+constexpr uint32_t kStages = 4;
+constexpr uint32_t kABytes = kBM * kBK * 2u;  // 32 KB
+constexpr uint32_t kBBytes = kBN * kBK * 2u;  // 16 KB
+constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kDecodeWarps = 8;
+constexpr uint32_t kGemmThreads = 32u * (2u + kDecodeWarps);
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kGemmSmem = kStages * kStageBytes + 1024u /* alignment slack */ + 256u /* barriers */;
+
+// ---- tcgen05 / TMA wrappers ----------------------------------------------------------------------------------------
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_addr(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_addr(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(dst_smem)), "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// generic-proxy writes to shared memory made visible to the tensor core's (async proxy) reads
+__device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_byte_addr >> 4) & 0x3FFFu);  // start address
+    d |= (uint64_t)1u << 16;                            // leading byte offset (unused with 128-byte swizzle)
+    d |= (uint64_t)(1024u >> 4) << 32;                  // stride byte offset: next 8-row group
+    d |= (uint64_t)1u << 46;                            // descriptor version of this architecture
+    d |= (uint64_t)2u << 61;                            // 128-byte swizzle
+    return d;
+}
+
+// kind::f16, f16 x f16 -> f32, both operands K-major, M = 128, N = kBN
+constexpr uint32_t kIdesc = (1u << 4) | ((kBN >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        :
+        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate)
+        : "memory");
+}
+
+// the barrier gets one arrival when every tcgen05.mma issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
+                 : "memory");
+}
+
+// 32 consecutive f32 columns of this thread's tensor-memory lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---- the GEMM ------------------------------------------------------------------------------------------------------
+
+struct GemmArgs {
+    const uint8_t* trellis[2];  // op 0 (gate / the dense weight) and op 1 (up), expert 0's first tile
+    size_t expert_bytes;
+    uint32_t K, N;              // one op's inner and outer widths
+    uint32_t n, mask, ops;
+    uint32_t a_op_rows;         // rows between op 0's and op 1's activations in the A buffer
+    const int4* tiles;          // (expert, first row, rows, 0) per M tile; null: one matrix, M tiles of kBM rows
+    uint32_t dense_rows;
+    __half* z;                  // [ops][z_rows][N]
+    size_t z_op_stride;         // elements between the ops' outputs
+    uint32_t* err;
+};
+
+template <int NN, int CB>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmArgs a) {
+    int e = 0, first = 0, rows = 0;
+    if (a.tiles) {
+        const int4 t = a.tiles[blockIdx.y];
+        e = t.x, first = t.y, rows = t.z;
+    } else {
+        first = (int)(blockIdx.y * kBM);
+        rows = min((int)kBM, (int)a.dense_rows - first);
+    }
+    if (rows <= 0) return;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_addr(smem_raw);
+    uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+    uint64_t* full_a = bars;
+    uint64_t* full_b = bars + kStages;
+    uint64_t* empty = bars + 2 * kStages;
+    uint64_t* acc_full = bars + 3 * kStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 1);
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t per_op = a.N / kBN, op = blockIdx.x / per_op, nt = blockIdx.x - op * per_op;
+    const uint32_t ksteps = a.K / kBK;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < kStages; ++s) {
+            mbar_init(&full_a[s], 1u);
+            mbar_init(&full_b[s], kDecodeWarps);
+            mbar_init(&empty[s], 1u);
+        }
+        mbar_init(acc_full, 1u);
+        mbar_init_fence();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (uint32_t ks = 0; ks < ksteps; ++ks) {
+                const uint32_t s = ks % kStages, u = ks / kStages;
+                if (u > 0 && !mbar_wait(&empty[s], (u - 1u) & 1u)) report(a.err, kErrEmptyWait);
+                mbar_arrive_expect_tx(&full_a[s], kABytes);
+                tma_load_2d(smem + s * kStageBytes, &tmap_a, (int)(ks * kBK), (int)(op * a.a_op_rows) + first, &full_a[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            for (uint32_t ks = 0; ks < ksteps; ++ks) {
+                const uint32_t s = ks % kStages, u = ks / kStages;
+                if (!mbar_wait(&full_a[s], u & 1u)) report(a.err, kErrFullWait);
+                if (!mbar_wait(&full_b[s], u & 1u)) report(a.err, kErrFullWait);
+                tc_fence_after();
+                const uint32_t a_addr = smem_addr(smem + s * kStageBytes), b_addr = a_addr + kABytes;
+#pragma unroll
+                for (uint32_t kk = 0; kk < kBK / 16u; ++kk) {
+                    const uint64_t bdesc = umma_desc(b_addr + kk * 32u);
+                    umma_f16(tmem, umma_desc(a_addr + kk * 32u), bdesc, (ks | kk) != 0u);
+                    umma_f16(tmem + 128u, umma_desc(a_addr + 128u * 128u + kk * 32u), bdesc, (ks | kk) != 0u);
+                }
+                umma_commit(&empty[s]);
+            }
+            umma_commit(acc_full);
+        }
+    } else {
+        const uint32_t dw = warp - 2u;
+        const uint32_t tile_bytes = 2u * a.n, out_tiles = a.N / 16u;
+        const uint8_t* wbase = a.trellis[op] + (size_t)e * a.expert_bytes + (size_t)(nt * 8u + dw) * tile_bytes;
+        const size_t tk_stride = (size_t)out_tiles * tile_bytes;
+        constexpr int NP = NN > 0 ? NN : 16;
+        constexpr uint32_t kRaw = raw_words(NP);
+        LanePlan<NP> plan;
+        plan.init(lane);
+        uint32_t nxt[4][kRaw];
+        if (NN > 0) {
+#pragma unroll
+            for (uint32_t i = 0; i < 4u; ++i) load_lane<NP>(reinterpret_cast<const uint32_t*>(wbase + i * tk_stride), plan, nxt[i]);
+        }
+        const uint32_t g = lane >> 2, q = lane & 3u;
+        for (uint32_t ks = 0; ks < ksteps; ++ks) {
+            const uint32_t s = ks % kStages, u = ks / kStages;
+            uint32_t cur[4][kRaw];
+            if (NN > 0) {
+#pragma unroll
+                for (uint32_t i = 0; i < 4u; ++i)
+#pragma unroll
+                    for (uint32_t w = 0; w < kRaw; ++w) cur[i][w] = nxt[i][w];
+                if (ks + 1u < ksteps) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 4u; ++i)
+                        load_lane<NP>(reinterpret_cast<const uint32_t*>(wbase + (size_t)((ks + 1u) * 4u + i) * tk_stride), plan,
+                                      nxt[i]);
+                }
+            }
+            if (u > 0 && !mbar_wait(&empty[s], (u - 1u) & 1u)) report(a.err, kErrEmptyWait);
+            uint8_t* bst = smem + s * kStageBytes + kABytes;
+#pragma unroll
+            for (uint32_t i = 0; i < 4u; ++i) {
+                uint32_t b[4];
+                if (NN > 0) decode_raw<NP, CB>(cur[i], plan, a.mask, b);
+                else
+                    decode_lane_any<CB>(reinterpret_cast<const uint32_t*>(wbase + (size_t)(ks * 4u + i) * tk_stride), a.n, lane,
+                                        a.mask, b);
+                // B[n][k] at n * 128 + ((k / 8) ^ (n % 8)) * 16 + (k % 8) * 2; this lane: k = 16 i + 2 q (+8), n = 16 dw + g (+8)
+                const uint32_t row0 = (dw * 16u + g) * 128u, row1 = row0 + 8u * 128u;
+                const uint32_t c0 = ((2u * i) ^ g) * 16u + 4u * q, c1 = ((2u * i + 1u) ^ g) * 16u + 4u * q;
+                *reinterpret_cast<uint32_t*>(bst + row0 + c0) = b[0];
+                *reinterpret_cast<uint32_t*>(bst + row0 + c1) = b[1];
+                *reinterpret_cast<uint32_t*>(bst + row1 + c0) = b[2];
+                *reinterpret_cast<uint32_t*>(bst + row1 + c1) = b[3];
+            }
+            proxy_fence();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_b[s]);
+        }
+        // epilogue: this warp reads tensor-memory lanes 32 (warp % 4) .. + 31 of accumulator half dw / 4
+        if (!mbar_wait(acc_full, 0u)) report(a.err, kErrMmaWait);
+        tc_fence_after();
+        const uint32_t half = dw >> 2, quarter = warp & 3u;
+        const int r = (int)(half * 128u + quarter * 32u + lane);
+        __half* zrow = a.z + op * a.z_op_stride + (size_t)(first + r) * a.N + nt * kBN;
+#pragma unroll 1
+        for (uint32_t c = 0; c < kBN / 32u; ++c) {
+            uint32_t v[32];
+            tmem_ld32(tmem + ((quarter * 32u) << 16) + half * 128u + c * 32u, v);
+            if (r < rows) {
+                uint32_t packed[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const __half2 h = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                    packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(zrow + c * 32u);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+// ---- route ---------------------------------------------------------------------------------------------------------
+
+__global__ void route_count_kernel(const uint32_t* inds, uint32_t slots, uint32_t experts, uint32_t* counts) {
+    const uint32_t s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s < slots) atomicAdd(&counts[min(inds[s], experts - 1u)], 1u);
+}
+
+// one CTA: each expert's first sorted position (exclusive scan of the counts) into `cursor`, and the M-tile table
+__global__ void __launch_bounds__(1024) route_plan_kernel(const uint32_t* counts, uint32_t experts, uint32_t* cursor,
+                                                          int4* tiles, uint32_t max_tiles) {
+    __shared__ uint32_t s_pos[1024], s_tile[1024];
+    const uint32_t tid = threadIdx.x;
+    // experts are walked in chunks of 1024 with running bases
+    __shared__ uint32_t base_pos, base_tile;
+    if (tid == 0) base_pos = base_tile = 0;
+    __syncthreads();
+    for (uint32_t e0 = 0; e0 < experts; e0 += 1024u) {
+        const uint32_t e = e0 + tid;
+        const uint32_t c = e < experts ? counts[e] : 0u;
+        const uint32_t t = (c + kBM - 1u) / kBM;
+        s_pos[tid] = c;
+        s_tile[tid] = t;
+        __syncthreads();
+        for (uint32_t off = 1; off < 1024u; off <<= 1) {  // inclusive Hillis-Steele scan
+            const uint32_t p = tid >= off ? s_pos[tid - off] : 0u, tt = tid >= off ? s_tile[tid - off] : 0u;
+            __syncthreads();
+            s_pos[tid] += p;
+            s_tile[tid] += tt;
+            __syncthreads();
+        }
+        const uint32_t pos0 = base_pos + s_pos[tid] - c, tile0 = base_tile + s_tile[tid] - t;
+        if (e < experts) {
+            cursor[e] = pos0;
+            for (uint32_t i = 0; i < t && tile0 + i < max_tiles; ++i)
+                tiles[tile0 + i] = make_int4((int)e, (int)(pos0 + i * kBM), (int)min(kBM, c - i * kBM), 0);
+        }
+        __syncthreads();
+        if (tid == 1023u) {
+            base_pos += s_pos[1023];
+            base_tile += s_tile[1023];
+        }
+        __syncthreads();
+    }
+    for (uint32_t i = base_tile + tid; i < max_tiles; i += 1024u) tiles[i] = make_int4(0, 0, 0, 0);
+}
+
+__global__ void route_scatter_kernel(const uint32_t* inds, uint32_t slots, uint32_t experts, uint32_t* cursor,
+                                     uint32_t* order, uint32_t* inv) {
+    const uint32_t s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= slots) return;
+    const uint32_t p = atomicAdd(&cursor[min(inds[s], experts - 1u)], 1u);
+    order[p] = s;
+    inv[s] = p;
+}
+
+// ---- prepare / mid / finish ------------------------------------------------------------------------------------------
+
+// grid (K / 128, ceil(P / 8), ops), 256 threads: warp = one (position, 128-block). Dense: position = row, suh shared.
+// Routed: position p -> slot order[p] -> row slot / topk, suh of the slot's expert; op 1 uses the up projection's suh.
+struct PrepArgs {
+    const void* x;
+    int x_dt;
+    const __half* suh[2];
+    uint32_t K, positions, topk, experts;
+    const uint32_t *order, *inds;  // null for a dense linear
+    __half* xp;                    // [ops][positions][K]
+};
+__global__ void __launch_bounds__(256) prep_rows_kernel(const PrepArgs a) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t p = blockIdx.y * 8u + warp, blk = blockIdx.x, op = blockIdx.z;
+    if (p >= a.positions) return;
+    uint32_t row = p, e = 0;
+    if (a.order) {
+        const uint32_t slot = a.order[p];
+        row = slot / a.topk;
+        e = min(a.inds[slot], a.experts - 1u);
+    }
+    const __half* suh = a.suh[op] + (size_t)e * a.K + blk * 128u;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        v[j] = round_half(load_act(a.x, a.x_dt, (size_t)row * a.K + blk * 128u + lane + 32u * j)) * __half2float(suh[lane + 32u * j]);
+    h128_warp(v, lane);
+    __half* dst = a.xp + ((size_t)op * a.positions + p) * a.K + blk * 128u;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[lane + 32u * j] = __float2half_rn(v[j] * kHadScale);
+}
+
+__device__ __forceinline__ void finish4(float (&v)[4], const __half* svh, uint32_t lane) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = round_half(v[j]);
+    h128_warp(v, lane);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = round_half(v[j] * kHadScale * __half2float(svh[lane + 32u * j]));
+}
+
+// grid (out / 128, ceil(rows / 8)): the plain finish of a dense linear (format.finishOutput, format.zig:370-380)
+struct FinishArgs {
+    const __half* z;
+    const __half* svh;
+    void* y;
+    int y_dt;
+    uint32_t rows, out;
+};
+__global__ void __launch_bounds__(256) finish_rows_kernel(const FinishArgs a) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t row = blockIdx.y * 8u + warp, blk = blockIdx.x;
+    if (row >= a.rows) return;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = __half2float(a.z[(size_t)row * a.out + blk * 128u + lane + 32u * j]);
+    finish4(v, a.svh + blk * 128u, lane);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) store_act(a.y, a.y_dt, (size_t)row * a.out + blk * 128u + lane + 32u * j, v[j]);
+}
+
+__device__ __forceinline__ float swiglu_f32(float g, float u, float limit, int clamp_at) {
+    if (limit > 0.0f) {
+        u = u > limit ? limit : (u < -limit ? -limit : u);
+        if (clamp_at == 0) g = g > limit ? limit : g;
+    }
+    float s = g / (1.0f + expf(-g));
+    if (limit > 0.0f && clamp_at != 0) s = s > limit ? limit : s;
+    return s * u;
+}
+
+// grid (inter / 128, ceil(P / 8)): gate and up finish, SwiGLU, the down projection's prepare, per sorted position
+struct MidArgs {
+    const __half* z;  // [2][P][inter]
+    const __half *gate_svh, *up_svh, *down_suh;
+    const uint32_t *order, *inds;
+    uint32_t positions, inter, experts;
+    float limit;
+    int clamp_at;
+    __half* hd;  // [P][inter]
+};
+__global__ void __launch_bounds__(256) mid_kernel(const MidArgs a) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t p = blockIdx.y * 8u + warp, blk = blockIdx.x;
+    if (p >= a.positions) return;
+    const uint32_t e = min(a.inds[a.order[p]], a.experts - 1u);
+    const size_t eo = (size_t)e * a.inter + blk * 128u, zo = (size_t)p * a.inter + blk * 128u;
+    float g[4], u[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        g[j] = __half2float(a.z[zo + lane + 32u * j]);
+        u[j] = __half2float(a.z[(size_t)a.positions * a.inter + zo + lane + 32u * j]);
+    }
+    finish4(g, a.gate_svh + eo, lane);
+    finish4(u, a.up_svh + eo, lane);
+    float d[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        d[j] = round_half(swiglu_f32(g[j], u[j], a.limit, a.clamp_at)) * __half2float(a.down_suh[eo + lane + 32u * j]);
+    h128_warp(d, lane);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) a.hd[zo + lane + 32u * j] = __float2half_rn(d[j] * kHadScale);
+}
+
+// grid (hidden / 128, ceil(rows / 8)): per row, each slot's down finish (through inv) and the score-weighted sum in slot
+// order, then the optional shared-expert add in the output dtype
+struct FinArgs {
+    const __half* zd;  // [P][hidden]
+    const __half* down_svh;
+    const uint32_t *inv, *inds;
+    const void* scores;
+    int score_dt;
+    const void* shared;
+    void* y;
+    int y_dt;
+    uint32_t rows, hidden, topk, experts;
+};
+__global__ void __launch_bounds__(256) moe_fin_kernel(const FinArgs a) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t row = blockIdx.y * 8u + warp, blk = blockIdx.x;
+    if (row >= a.rows) return;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (uint32_t k = 0; k < a.topk; ++k) {
+        const size_t slot = (size_t)row * a.topk + k;
+        const uint32_t p = a.inv[slot], e = min(a.inds[slot], a.experts - 1u);
+        const float w = load_act(a.scores, a.score_dt, slot);
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = __half2float(a.zd[(size_t)p * a.hidden + blk * 128u + lane + 32u * j]);
+        finish4(v, a.down_svh + (size_t)e * a.hidden + blk * 128u, lane);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] = __fadd_rn(acc[j], __fmul_rn(w, v[j]));
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const size_t o = (size_t)row * a.hidden + blk * 128u + lane + 32u * j;
+        float r = acc[j];
+        if (a.shared) {
+            store_act(a.y, a.y_dt, o, r);
+            r = __fadd_rn(load_act(a.y, a.y_dt, o), load_act(a.shared, a.y_dt, o));
+        }
+        store_act(a.y, a.y_dt, o, r);
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// f16 [rows, K] row-major, boxes of kBK x kBM, 128-byte swizzle, rows past the end read as zero
+bool make_a_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {K, rows};
+    const cuuint64_t strides[1] = {K * 2u};
+    const cuuint32_t box[2] = {kBK, kBM};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int CB>
+cudaError_t launch_gemm_cb(const CUtensorMap& map, const GemmArgs& g, uint32_t max_tiles, cudaStream_t stream) {
+    void (*fn)(const CUtensorMap, const GemmArgs) = nullptr;
+    switch (g.n) {
+#define T3_CASE(NN) \
+    case NN: fn = gemm_decode_kernel<NN, CB>; break;
+        T3_CASE(16) T3_CASE(32) T3_CASE(48) T3_CASE(64) T3_CASE(80) T3_CASE(96) T3_CASE(112) T3_CASE(128)
+#undef T3_CASE
+        default: fn = gemm_decode_kernel<0, CB>; break;
+    }
+    cudaError_t rc = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)kGemmSmem);
+    if (rc != cudaSuccess) return rc;
+    fn<<<dim3(g.ops * g.N / kBN, max_tiles, 1), kGemmThreads, kGemmSmem, stream>>>(map, g);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gemm(const CUtensorMap& map, const GemmArgs& g, uint32_t max_tiles, int codebook, cudaStream_t stream) {
+    return codebook == kMcg ? launch_gemm_cb<kMcg>(map, g, max_tiles, stream) : launch_gemm_cb<kMul1>(map, g, max_tiles, stream);
+}
+
+size_t up256(size_t v) { return (v + 255u) & ~(size_t)255u; }
+
+}  // namespace
+
+// ---- dense linear, more than 32 rows ---------------------------------------------------------------------------------
+
+size_t prefill_linear_workspace(size_t rows, uint32_t in, uint32_t out) {
+    return up256(rows * in * 2u) + up256(rows * out * 2u);
+}
+
+cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cudaStream_t stream, int* launches) {
+    uint8_t* ws = static_cast<uint8_t*>(p.workspace);
+    __half* xp = reinterpret_cast<__half*>(ws);
+    __half* z = reinterpret_cast<__half*>(ws + up256((size_t)p.rows * p.in * 2u));
+    PrepArgs pa = {};
+    pa.x = p.x;
+    pa.x_dt = p.x_dt;
+    pa.suh[0] = pa.suh[1] = static_cast<const __half*>(p.suh);
+    pa.K = p.in;
+    pa.positions = p.rows;
+    pa.topk = 1;
+    pa.experts = 1;
+    pa.xp = xp;
+    prep_rows_kernel<<<dim3(p.in / 128u, (p.rows + 7u) / 8u, 1), 256, 0, stream>>>(pa);
+    CUtensorMap map;
+    if (!make_a_map(&map, xp, p.rows, p.in)) return cudaErrorNotSupported;
+    GemmArgs g = {};
+    g.trellis[0] = g.trellis[1] = p.trellis;
+    g.K = p.in;
+    g.N = p.out;
+    g.n = p.n;
+    g.mask = p.mask;
+    g.ops = 1;
+    g.dense_rows = p.rows;
+    g.z = z;
+    g.err = p.err;
+    cudaError_t rc = launch_gemm(map, g, (p.rows + kBM - 1u) / kBM, codebook, stream);
+    if (rc != cudaSuccess) return rc;
+    FinishArgs f = {z, static_cast<const __half*>(p.svh), p.y, p.x_dt, p.rows, p.out};
+    finish_rows_kernel<<<dim3(p.out / 128u, (p.rows + 7u) / 8u, 1), 256, 0, stream>>>(f);
+    *launches += 3;
+    return cudaGetLastError();
+}
+
+// ---- routed experts, more than 32 rows --------------------------------------------------------------------------------
+
+namespace {
+struct MoeWs {
+    uint32_t *counts, *cursor, *order, *inv;
+    int4* tiles;
+    __half *xp, *zgu, *hd, *zd;
+    uint32_t max_tiles;
+    size_t total;
+};
+MoeWs carve_moe(uint8_t* base, size_t slots, uint32_t experts, uint32_t hidden, uint32_t inter) {
+    MoeWs w;
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        uint8_t* p = base ? base + off : nullptr;
+        off += up256(bytes);
+        return p;
+    };
+    w.max_tiles = (uint32_t)((slots + kBM - 1u) / kBM) + experts;
+    w.counts = reinterpret_cast<uint32_t*>(take((size_t)experts * 4u));
+    w.cursor = reinterpret_cast<uint32_t*>(take((size_t)experts * 4u));
+    w.order = reinterpret_cast<uint32_t*>(take(slots * 4u));
+    w.inv = reinterpret_cast<uint32_t*>(take(slots * 4u));
+    w.tiles = reinterpret_cast<int4*>(take((size_t)w.max_tiles * 16u));
+    w.xp = reinterpret_cast<__half*>(take(2u * slots * hidden * 2u));
+    w.zgu = reinterpret_cast<__half*>(take(2u * slots * inter * 2u));
+    w.hd = reinterpret_cast<__half*>(take(slots * inter * 2u));
+    w.zd = reinterpret_cast<__half*>(take(slots * hidden * 2u));
+    w.total = off;
+    return w;
+}
+}  // namespace
+
+size_t prefill_moe_workspace(size_t rows, uint32_t topk, uint32_t experts, uint32_t hidden, uint32_t inter) {
+    return carve_moe(nullptr, rows * topk, experts, hidden, inter).total;
+}
+
+cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, cudaStream_t stream, int* launches) {
+    const size_t slots = (size_t)a.rows * a.topk;
+    const uint32_t S = (uint32_t)slots, H = a.hidden, I = a.inter;
+    MoeWs w = carve_moe(static_cast<uint8_t*>(workspace), slots, a.experts, H, I);
+    const uint32_t* inds = static_cast<const uint32_t*>(a.inds);
+    cudaError_t rc = cudaMemsetAsync(w.counts, 0, (size_t)a.experts * 4u, stream);
+    if (rc != cudaSuccess) return rc;
+    route_count_kernel<<<(S + 255u) / 256u, 256, 0, stream>>>(inds, S, a.experts, w.counts);
+    route_plan_kernel<<<1, 1024, 0, stream>>>(w.counts, a.experts, w.cursor, w.tiles, w.max_tiles);
+    route_scatter_kernel<<<(S + 255u) / 256u, 256, 0, stream>>>(inds, S, a.experts, w.cursor, w.order, w.inv);
+
+    PrepArgs pa = {};
+    pa.x = a.x;
+    pa.x_dt = a.x_dt;
+    pa.suh[0] = static_cast<const __half*>(a.gate_suh);
+    pa.suh[1] = static_cast<const __half*>(a.up_suh);
+    pa.K = H;
+    pa.positions = S;
+    pa.topk = a.topk;
+    pa.experts = a.experts;
+    pa.order = w.order;
+    pa.inds = inds;
+    pa.xp = w.xp;
+    prep_rows_kernel<<<dim3(H / 128u, (S + 7u) / 8u, 2), 256, 0, stream>>>(pa);
+
+    const uint32_t tile_bytes = 2u * a.n;
+    CUtensorMap map_gu, map_d;
+    if (!make_a_map(&map_gu, w.xp, 2u * slots, H) || !make_a_map(&map_d, w.hd, slots, I)) return cudaErrorNotSupported;
+    GemmArgs g = {};
+    g.trellis[0] = a.gate_t;
+    g.trellis[1] = a.up_t;
+    g.expert_bytes = (size_t)(H / 16u) * (I / 16u) * tile_bytes;
+    g.K = H;
+    g.N = I;
+    g.n = a.n;
+    g.mask = a.mask;
+    g.ops = 2;
+    g.a_op_rows = S;
+    g.tiles = w.tiles;
+    g.z = w.zgu;
+    g.z_op_stride = slots * I;
+    g.err = a.err;
+    rc = launch_gemm(map_gu, g, w.max_tiles, codebook, stream);
+    if (rc != cudaSuccess) return rc;
+
+    MidArgs m = {w.zgu, static_cast<const __half*>(a.gate_svh), static_cast<const __half*>(a.up_svh),
+                 static_cast<const __half*>(a.down_suh), w.order, inds, S, I, a.experts, a.limit, a.clamp_at, w.hd};
+    mid_kernel<<<dim3(I / 128u, (S + 7u) / 8u, 1), 256, 0, stream>>>(m);
+
+    GemmArgs d = {};
+    d.trellis[0] = d.trellis[1] = a.down_t;
+    d.expert_bytes = g.expert_bytes;
+    d.K = I;
+    d.N = H;
+    d.n = a.n;
+    d.mask = a.mask;
+    d.ops = 1;
+    d.tiles = w.tiles;
+    d.z = w.zd;
+    d.err = a.err;
+    rc = launch_gemm(map_d, d, w.max_tiles, codebook, stream);
+    if (rc != cudaSuccess) return rc;
+
+    FinArgs f = {w.zd, static_cast<const __half*>(a.down_svh), w.inv, inds, a.scores, a.score_dt, a.shared, a.y, a.x_dt,
+                 a.rows, H, a.topk, a.experts};
+    moe_fin_kernel<<<dim3(H / 128u, (a.rows + 7u) / 8u, 1), 256, 0, stream>>>(f);
+    *launches += 8;
+    return cudaGetLastError();
+}
+
+}  // namespace t3
