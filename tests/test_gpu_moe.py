@@ -115,9 +115,10 @@ def test_config3_hybrid_layer_with_shared_expert():
         routed_ref = ob.moe_rows(obank, xf, inds, scores)
         shared_ref = ob.moe_rows(sobank, xf, zeros, g.reshape(rows, 1))
         to16 = lambda a: a.astype(np.float16).astype(np.float32)
-        ref = to16(routed_ref) + to16(shared_ref)
+        ref = to16(to16(routed_ref) + to16(shared_ref))
         check_moe(host_f32(shared).reshape(rows, H), shared_ref, "f16", ("shared", rows))
-        check_moe(host_f32(y).reshape(rows, H), ref, "f16", ("layer", rows))
+        # the layer output stacks two independently rounded calls: each may sit one rounding away from the oracle's
+        check_moe(host_f32(y).reshape(rows, H), ref, "f16", ("layer", rows), terms=1.5)
     assert t3.device_error() == 0
 
 
