@@ -36,7 +36,8 @@ typedef enum {
     T3_WORKSPACE_TOO_SMALL = 11,    /* "WorkspaceTooSmall" (no counterpart: the reference allocates its scratch) */
     T3_EXPERT_LAYOUT_UNSUPPORTED = 12, /* "ExpertLayoutUnsupported" (src/core/spec.zig:38-50) */
     T3_WINDOW_UNSUPPORTED = 13,     /* "Exl3WindowUnsupported" (src/core/spec.zig:48) */
-    T3_NULL_POINTER = 14            /* "NullPointer" */
+    T3_NULL_POINTER = 14,           /* "NullPointer" */
+    T3_SCRATCH_LIMIT_EXCEEDED = 15  /* "ScratchLimitExceeded" (t3_moe_noalloc: the call needs more than the built-in scratch) */
 } t3_status;
 
 const char* t3_status_name(int status);
@@ -134,6 +135,18 @@ int t3_moe_clamped(const void* x, int x_dtype, size_t rows, const t3_bank* bank,
 int t3_moe_with_shared(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds,
                        const void* scores, int scores_dtype, int topk, t3_decode dec, const void* shared, void* y,
                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* t3_moe without a workspace argument, for callers that cannot allocate device memory (a host whose memory pool owns the
+ * whole GPU, a plugin that is only handed activations and weights). It has no counterpart in the reference, which
+ * allocates its scratch through MLX. The scratch lives in a fixed device array inside the library image:
+ * T3_NOALLOC_SCRATCH_BYTES on every GPU that loads the library, until the process exits. Decode rows only (rows <=
+ * T3_DECODE_ROWS_MAX) and t3_moe_workspace_bytes(rows, topk, bank) <= T3_NOALLOC_SCRATCH_BYTES, else
+ * ScratchLimitExceeded before anything is launched. It calls no cudaMalloc/cudaFree. The first call on a device looks up
+ * the array's address (cudaGetSymbolAddress) and should come before any stream capture. All calls share the one array:
+ * calls whose kernels can overlap on the GPU (other streams or threads) race; keep them on one stream. */
+#define T3_NOALLOC_SCRATCH_BYTES (4u << 20)
+int t3_moe_noalloc(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds, const void* scores,
+                   int scores_dtype, int topk, t3_decode dec, void* y, void* stream);
 
 /* Measurement hook (the reference has probe kernels for the same purpose, src/core/decode.zig:34-35): when set to a
  * device array of 8 uint64, the next t3_linear launches at decode rows record the SM cycle counter of their CTA (0, 0) at:

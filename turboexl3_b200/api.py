@@ -75,6 +75,7 @@ SYMBOLS = {
     "t3_moe_swiglu": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _u32, _i, _vp, _vp, _sz, _vp]),
     "t3_moe_clamped": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _i, _vp, _vp, _sz, _vp]),
     "t3_moe_with_shared": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp, _vp, _sz, _vp]),
+    "t3_moe_noalloc": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp]),
     "t3_set_trace": (None, [_vp]),
     "t3_launch_count": (C.c_uint64, []),
 }

@@ -22,6 +22,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 
 # (source, object stem, extra flags)
 UNITS = [
+    ("t3_noalloc.cu", "t3_noalloc", []),
     ("t3_table.cu", "t3_table", []),
     ("t3_prefill.cu", "t3_prefill", []),
     ("t3_api.cu", "t3_api", []),

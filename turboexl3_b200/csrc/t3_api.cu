@@ -160,6 +160,7 @@ const char* t3_status_name(int status) {
         case T3_EXPERT_LAYOUT_UNSUPPORTED: return "ExpertLayoutUnsupported";
         case T3_WINDOW_UNSUPPORTED: return "Exl3WindowUnsupported";
         case T3_NULL_POINTER: return "NullPointer";
+        case T3_SCRATCH_LIMIT_EXCEEDED: return "ScratchLimitExceeded";
         default: return "Unknown";
     }
 }
