@@ -3,13 +3,19 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE.json configs[1], the decode-row half): the dense trunk sweep, shapes 2048x2048, 2048x6144 and
+Headline workload (BASELINE.json configs[1], decode rows): the dense trunk sweep, shapes 2048x2048, 2048x6144 and
 6144x2048 at K in {1,2,3,4,5,6,8} bits, one f16 activation row each: 21 linears a step, 106.4 MB of trellis code bytes.
-Metric: code-byte GB/s = trellis bytes read per step / step time (the reference's byte convention: code bytes only).
-Weights rotate over several copies larger than L2 together, so every step streams its codes from HBM.
+Metric: code-byte GB/s = trellis bytes read per step / step time (the reference's byte convention: code bytes only,
+src/core/gpu_test.zig:136). Weights rotate over three copies (319 MB > L2), so every step streams its codes from HBM.
+A step is ONE stream of 21 launches replayed from a CUDA graph (a dependent chain's semantics; each launch may prefetch
+its weights while its predecessor finishes, nothing else overlaps).
 
-Prints ONE JSON line (rank 0). `--impl reference` times the CPU restatement of the reference's host implementation
-(format.project) on the host cores instead.
+The JSON line also carries: `e2e` (the same step through the quant-plugin table with HOST arrays: copy in, run, copy
+out, every call), `roofline`, `cpu_baseline` (the oracle's format.project on the host cores), `submetrics` (the other two
+parts of BASELINE's metric: us per MoE layer at decode rows on config 3, prefill TFLOP/s on configs 2 and 4 shapes) and
+`concurrent` (the 21 independent linears as parallel graph branches: what the device sustains when nothing orders them).
+
+`--impl reference` times the CPU restatement of the reference's host implementation (format.project) instead.
 """
 from __future__ import annotations
 
@@ -33,6 +39,7 @@ KS = [1, 2, 3, 4, 5, 6, 8]
 METRIC = "decode_row_code_byte_throughput"
 UNIT = "GB/s"
 WORKLOAD = "configs[1] dense trunk sweep, decode rows: 3 shapes x K{1,2,3,4,5,6,8}, 1 f16 row, MUL1, +-1 signs"
+COPIES = 3  # 3 x 106 MB of codes > the 126 MB L2
 
 
 def code_bytes(in_dim: int, out_dim: int, k: int) -> int:
@@ -40,34 +47,33 @@ def code_bytes(in_dim: int, out_dim: int, k: int) -> int:
 
 
 STEP_BYTES = sum(code_bytes(i, o, k) for (i, o) in SHAPES for k in KS)
+LINEARS = len(SHAPES) * len(KS)
 
 
-def measured_peaks() -> tuple[float, str]:
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+def measured_peaks() -> dict:
     try:
-        with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return {"hbm": float(d["hbm_gbs"]), "tf": float(d["bf16_tflops"]), "kind": "of measured"}
     except Exception:
-        return 6650.0, "fallback"
+        return {"hbm": 6650.0, "tf": 1590.0, "kind": "of fallback"}
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks and throttle reasons with nvidia-smi while the GPU work runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,utilization.gpu,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
-        self.gpu = gpu_index
-        self.proc = None
-        self.lines = []
+        self.gpu, self.proc, self.lines = gpu_index, None, []
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._pump, daemon=True)
-            self.thread.start()
+            threading.Thread(target=self._pump, daemon=True).start()
         except Exception:
             self.proc = None
 
@@ -78,7 +84,7 @@ class ClockSampler:
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.1)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=2)
@@ -88,18 +94,20 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.lines:
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
+            if len(parts) < 8:
                 continue
             try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
+                clk, mxc, util = float(parts[1]), float(parts[2]), float(parts[3])
             except ValueError:
                 continue
-            for name, val in zip(names, parts[3:7]):
+            mx.append(mxc)
+            if util > 0:  # samples taken while kernels were running
+                sm.append(clk)
+            for name, val in zip(names, parts[4:8]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples_under_load": len(sm), "samples": len(mx), "reasons": sorted(reasons)}
 
 
 def host_operands(copy: int):
@@ -112,46 +120,159 @@ def host_operands(copy: int):
     return ops
 
 
-def cpu_sample(threads: int, reps: int = 1) -> dict:
+def cpu_sample(threads: int) -> dict:
     """The oracle's faithful format.project (every tile decoded per call) over one pass of the sweep, all host threads."""
     from oracle import binding as ob
     from turboexl3_b200 import synth
     ops = host_operands(0)
     xs = {i: synth.activations(7, 1, i).astype(np.float32) for i in (2048, 6144)}
     t0 = time.perf_counter()
-    for _ in range(reps):
-        for (i, o, n, trellis, suh, svh) in ops:
-            ob.linear_rows(xs[i], trellis, suh, svh, i, o, n, ob.MUL1, 16, threads=threads)
-    dt = (time.perf_counter() - t0) / reps
+    for (i, o, n, trellis, suh, svh) in ops:
+        ob.linear_rows(xs[i], trellis, suh, svh, i, o, n, ob.MUL1, 16, threads=threads)
+    dt = time.perf_counter() - t0
     return {"seconds_per_pass": dt, "value": STEP_BYTES / dt / 1e9}
 
 
 def run_reference(args) -> None:
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
     from oracle import binding as ob
     ob.build()
     threads = ob.host_threads()
-    for _ in range(max(0, min(args.warmup, 1))):
+    warm = max(0, min(args.warmup, 1))
+    for _ in range(warm):
         cpu_sample(threads)
-    times = []
-    for _ in range(max(1, min(args.steps, 3))):
-        times.append(cpu_sample(threads)["seconds_per_pass"])
+    times = [cpu_sample(threads)["seconds_per_pass"] for _ in range(max(1, min(args.steps, 5)))]
     dt = statistics.mean(times)
     value = STEP_BYTES / dt / 1e9
-    line = {
+    print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference's format.project (oracle port); "
-                   "the reference itself is Zig and cannot be built here"},
+        "steps": len(times), "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference's format.project (oracle port): the "
+                   "reference is a Zig library and cannot be built here; steps are capped at 5 passes"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": "one full pass of the 21-linear sweep per step, every tile decoded per call"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-    }
-    print(json.dumps(line))
+    }))
+
+
+# ---- GPU side ------------------------------------------------------------------------------------------------------
+
+def graph_of(fn):
+    """fn captured into a CUDA graph after one eager run (which also does every one-time set-up)."""
+    import torch
+    fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    g.replay()
+    torch.cuda.synchronize()
+    return g
+
+
+def time_us(run, reps: int) -> float:
+    import torch
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def moe_submetric(t3, synth, torch) -> dict:
+    """BASELINE config 3: hidden 2048, 512 experts x width 512, top-10, K = 3, one shared expert; us per MoE layer."""
+    H, I, E, topk, n = 2048, 512, 512, 10, 48
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    mk = lambda arrs: t3.Bank(t3.Proj(dev(arrs["gate_t"]), dev(arrs["gate_suh"]), dev(arrs["gate_svh"])),
+                              t3.Proj(dev(arrs["up_t"]), dev(arrs["up_suh"]), dev(arrs["up_svh"])),
+                              t3.Proj(dev(arrs["down_t"]), dev(arrs["down_suh"]), dev(arrs["down_svh"])))
+    bank, shared_bank = mk(synth.bank(3, E, H, I, n)), mk(synth.bank(4, 1, H, I, n))
+    out = {}
+    for rows in (1, 4, 16, 32):
+        calls, distinct = [], []
+        for c in range(8):  # eight routings a replay: fresh experts each call, codes from HBM (604 MB bank > L2)
+            inds, scores = synth.routing(50 + c + 10 * rows, rows, E, topk)
+            distinct.append(len(np.unique(inds)))
+            gate = (1.0 / (1.0 + np.exp(-np.random.default_rng(c).standard_normal((rows, 1))))).astype(np.float32)
+            calls.append((dev(synth.activations(c, rows, H)).view(1, rows, H), dev(inds).view(1, rows, topk),
+                          dev(scores).view(1, rows, topk), dev(np.zeros((rows, 1), np.int32)).view(1, rows, 1),
+                          dev(gate).view(1, rows, 1)))
+
+        def layer_burst():
+            for (x, i_, s_, z_, g_) in calls:
+                sh = t3.moe(x, shared_bank, z_, g_)
+                t3.moe_with_shared(x, bank, i_, s_, t3.Decode.mul1, sh)
+
+        g = graph_of(layer_burst)
+        us = time_us(g.replay, 10) / len(calls)
+        byts = (float(np.mean(distinct)) + 1.0) * 3 * H * I * 3 / 8
+        out[f"rows{rows}"] = {"us_per_layer": round(us, 2), "distinct_experts": float(np.mean(distinct)),
+                              "code_GBps": round(byts / us / 1e3, 1)}
+    return out
+
+
+def prefill_submetric(t3, synth, torch) -> dict:
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    out = {}
+    for (i, o, k, rows) in [(2048, 6144, 4, 4096), (2048, 2048, 4, 4096), (6144, 2048, 4, 512)]:
+        w = tuple(dev(a) for a in synth.linear(5, i, o, 16 * k))
+        x = dev(synth.activations(1, rows, i))
+        t3.linear(x, *w)
+        us = time_us(lambda: t3.linear(x, *w), 5)
+        out[f"dense_{i}x{o}_K{k}_rows{rows}"] = {"us": round(us, 1), "TFLOPS": round(2.0 * rows * i * o / us / 1e6, 1)}
+    H, I, E, topk, n = 2048, 512, 512, 10, 48
+    arrs = synth.bank(3, E, H, I, n)
+    bank = t3.Bank(t3.Proj(dev(arrs["gate_t"]), dev(arrs["gate_suh"]), dev(arrs["gate_svh"])),
+                   t3.Proj(dev(arrs["up_t"]), dev(arrs["up_suh"]), dev(arrs["up_svh"])),
+                   t3.Proj(dev(arrs["down_t"]), dev(arrs["down_suh"]), dev(arrs["down_svh"])))
+    for rows in (4096,):
+        inds, scores = synth.routing(77, rows, E, topk)
+        x = dev(synth.activations(5, rows, H)).view(1, rows, H)
+        di, ds = dev(inds).view(1, rows, topk), dev(scores).view(1, rows, topk)
+        t3.moe(x, bank, di, ds)
+        us = time_us(lambda: t3.moe(x, bank, di, ds), 3)
+        out[f"moe_config4_K3_tokens{rows}"] = {"us": round(us, 1),
+                                               "TFLOPS": round(2.0 * rows * topk * 3 * H * I / us / 1e6, 1)}
+    return out
+
+
+def run_case(args) -> None:
+    """One named case run eagerly a few times (for profilers): prints a small JSON line, not the bench contract's."""
+    import torch
+
+    import turboexl3_b200 as t3
+    from turboexl3_b200 import synth
+    torch.cuda.set_device(0)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    H, I, E, topk, n = 2048, 512, 512, 10, 48
+    reps = max(1, args.steps)
+    if args.case in ("moe_decode", "moe_prefill"):
+        arrs = synth.bank(3, E, H, I, n)
+        bank = t3.Bank(t3.Proj(dev(arrs["gate_t"]), dev(arrs["gate_suh"]), dev(arrs["gate_svh"])),
+                       t3.Proj(dev(arrs["up_t"]), dev(arrs["up_suh"]), dev(arrs["up_svh"])),
+                       t3.Proj(dev(arrs["down_t"]), dev(arrs["down_suh"]), dev(arrs["down_svh"])))
+        rows = args.rows if args.case == "moe_decode" else max(args.rows, 4096)
+        calls = []
+        for c in range(4):
+            inds, scores = synth.routing(50 + c, rows, E, topk)
+            calls.append((dev(synth.activations(c, rows, H)).view(1, rows, H), dev(inds).view(1, rows, topk),
+                          dev(scores).view(1, rows, topk)))
+        run = lambda: [t3.moe(x, bank, i_, s_) for (x, i_, s_) in calls]
+        per = len(calls)
+    else:
+        w = tuple(dev(a) for a in synth.linear(5, 2048, 6144, 64))
+        x = dev(synth.activations(1, max(args.rows, 33), 2048))
+        run = lambda: t3.linear(x, *w)
+        per = 1
+    run()
+    us = time_us(run, reps) / per
+    print(json.dumps({"case": args.case, "rows": args.rows, "us_per_call": round(us, 2), "device_error": t3.device_error()}))
 
 
 def run_ours(args) -> None:
@@ -159,6 +280,8 @@ def run_ours(args) -> None:
     import torch.distributed as dist
 
     import turboexl3_b200 as t3
+    from turboexl3_b200 import synth
+    from turboexl3_b200 import table as tb
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -169,62 +292,48 @@ def run_ours(args) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     t3.lib()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
 
-    copies = 3  # 3 x 106 MB of codes > the 126 MB L2
-    sets = []
-    for c in range(copies):
-        dev_ops = []
-        for (i, o, n, trellis, suh, svh) in host_operands(c):
-            dev_ops.append((i, o, n, torch.from_numpy(trellis).cuda(), torch.from_numpy(suh).cuda(),
-                            torch.from_numpy(svh).cuda()))
-        sets.append(dev_ops)
-    from turboexl3_b200 import synth
-    x_host = {i: torch.from_numpy(synth.activations(7, 1, i)).pin_memory() for i in (2048, 6144)}
-    x_dev = {i: v.cuda() for i, v in x_host.items()}
-    y_host = {o: torch.empty((1, o), dtype=torch.float16).pin_memory() for o in (2048, 6144)}
+    host_sets = [host_operands(c) for c in range(COPIES)]
+    sets = [[(i, o, n, torch.from_numpy(t).cuda(), torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda())
+             for (i, o, n, t, a, b) in ops] for ops in host_sets]
+    x_np = {i: synth.activations(7, 1, i) for i in (2048, 6144)}
+    x_dev = {i: torch.from_numpy(v).cuda() for i, v in x_np.items()}
     dec = t3.Decode.mul1
 
-    def step_eager(s: int):
-        for (i, o, n, t, a, b) in sets[s % copies]:
+    def step_eager(c: int):
+        for (i, o, n, t, a, b) in sets[c]:
             t3.linear(x_dev[i], t, a, b, dec)
 
-    # One CUDA graph per weight copy: the 21 launches of a step replay without host work between them. The launches
-    # carry the programmatic-dependent-launch attribute, so a linear's weight streaming overlaps its predecessor's tail.
-    graphs = []
-    launch_mode = "cuda graph per step (21 kernel nodes)"
+    def step_branches(c: int):
+        """The same 21 launches as independent branches of the graph (forked streams)."""
+        main = torch.cuda.current_stream()
+        side = [torch.cuda.Stream() for _ in range(7)]
+        for s in side:
+            s.wait_stream(main)
+        for idx, (i, o, n, t, a, b) in enumerate(sets[c]):
+            with torch.cuda.stream(side[idx % 7]):
+                t3.linear(x_dev[i], t, a, b, dec)
+        for s in side:
+            main.wait_stream(s)
+
+    graphs, launch_mode = [], "one stream, 21 kernel nodes replayed from a CUDA graph per step"
     if not args.eager:
         try:
-            for c in range(copies):
-                step_eager(c)
-            torch.cuda.synchronize()
-            for c in range(copies):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
-                    step_eager(c)
-                graphs.append(g)
-        except Exception as exc:  # capture refused: time the eager launches and say so
-            graphs = []
-            launch_mode = f"eager launches (graph capture failed: {type(exc).__name__})"
+            graphs = [graph_of(lambda c=c: step_eager(c)) for c in range(COPIES)]
+        except Exception as exc:
+            graphs, launch_mode = [], f"eager launches (graph capture failed: {type(exc).__name__})"
             torch.cuda.synchronize()
     else:
         launch_mode = "eager launches"
-    per_step_launches = len(sets[0])
 
     def step_device(s: int):
         if graphs:
-            graphs[s % copies].replay()
+            graphs[s % COPIES].replay()
         else:
-            step_eager(s)
-
-    def step_e2e(s: int):
-        last = None
-        for (i, o, n, t, a, b) in sets[s % copies]:
-            xd = x_host[i].cuda(non_blocking=True)
-            y = t3.linear(xd, t, a, b, dec)
-            y_host[o].copy_(y, non_blocking=True)
-            last = y
-        torch.cuda.current_stream().synchronize()
-        return last
+            step_eager(s % COPIES)
 
     def barrier():
         if world > 1:
@@ -235,9 +344,6 @@ def run_ours(args) -> None:
     for s in range(warm):
         step_device(s)
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     launches0 = t3.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -247,69 +353,93 @@ def run_ours(args) -> None:
     ev1.record()
     barrier()
     ms = ev0.elapsed_time(ev1)
-    launches = (t3.launch_count() - launches0) if not graphs else per_step_launches * args.steps
+    launches = LINEARS * args.steps if graphs else t3.launch_count() - launches0
 
-    # end to end: host buffers in, host buffers out, copies inside the timed region
+    # ---- end to end: the quant-plugin table on HOST arrays (weights resident, activations copied in and out per call)
+    blk = tb.Block('{"format":"exl3","codebook":"mul1"}')
+    assert blk.verdict.ok
+    table_sets = []
+    for ops in host_sets:
+        ws = []
+        for (i, o, n, t, a, b) in ops:
+            v, w = blk.load_tensor(t, a, b, i)
+            assert v.ok, v.why
+            ws.append(w)
+        table_sets.append(ws)
+    import ctypes as C
+    tab = tb.table()
+    y_np = {o: np.empty((1, o), np.float16) for o in (2048, 6144)}
+    x_arr = {i: tb.host_array(v) for i, v in x_np.items()}
+    y_arr = {o: tb.host_array(v) for o, v in y_np.items()}
+    stream_ptr = torch.cuda.current_stream().cuda_stream
+
+    def step_e2e(s: int):
+        for w in table_sets[s % COPIES]:
+            v = tab.matmul(C.byref(w), C.byref(x_arr[w.in_dim]), stream_ptr, C.byref(y_arr[w.out_dim]))
+            if v.kind != 0:
+                raise SystemExit(f"table matmul refused: {v.reason}")
+
+    e2e_steps = max(3, min(args.steps, 20))
     for s in range(2):
         step_e2e(s)
     barrier()
     t0 = time.perf_counter()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for s in range(args.steps):
-        step_e2e(warm + s)
-    e1.record()
-    barrier()
-    e2e_ms = max(e0.elapsed_time(e1), 0.0)
-    e2e_wall_ms = (time.perf_counter() - t0) * 1e3
-    clocks = sampler.stop() if rank == 0 else None
+    for s in range(e2e_steps):
+        step_e2e(2 + s)
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3  # every call ends with its result on the host: wall time is the measure
+    for ws in table_sets:
+        for w in ws:
+            tab.release(C.byref(w))
+    blk.close()
 
-    # per-case kernel times (events around repeats of one linear on rotating copies)
-    cases = {}
-    if rank == 0 and not args.no_cases:
+    extra = {}
+    if rank == 0 and not args.quick:
+        # the 21 linears with nothing ordering them
+        try:
+            bgraphs = [graph_of(lambda c=c: step_branches(c)) for c in range(COPIES)]
+            for s in range(3):
+                bgraphs[s % COPIES].replay()
+            idx = [0]
+
+            def replay_next():
+                bgraphs[idx[0] % COPIES].replay()
+                idx[0] += 1
+
+            us = time_us(replay_next, 30)
+            extra["concurrent"] = {"value": round(STEP_BYTES / us / 1e3, 1), "unit": UNIT, "us_per_step": round(us, 1),
+                                   "what": "the step's 21 independent linears as parallel branches of one CUDA graph"}
+        except Exception as exc:
+            extra["concurrent"] = {"error": type(exc).__name__}
+        # per-linear device time: a graph of one launch per weight copy
+        cases = {}
         for idx, (i, o, n, _, _, _) in enumerate(sets[0]):
-            reps = 10
-            def burst():
-                for r in range(copies):
-                    t3.linear(x_dev[i], *sets[r][idx][3:], dec)
-            burst()
-            torch.cuda.synchronize()
-            cg = None
-            if graphs:
-                cg = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(cg):
-                    burst()
-            run = cg.replay if cg is not None else burst
-            run()
-            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            a0.record()
-            for r in range(reps):
-                run()
-            a1.record()
-            torch.cuda.synchronize()
-            us = a0.elapsed_time(a1) * 1e3 / (reps * copies)
+            def burst(idx=idx, i=i):
+                for c in range(COPIES):
+                    t3.linear(x_dev[i], *sets[c][idx][3:], dec)
+            g = graph_of(burst) if graphs else None
+            us = time_us(g.replay if g is not None else burst, 10) / COPIES
             cases[f"{i}x{o}_K{n // 16}"] = {"us": round(us, 2), "GBps": round(code_bytes(i, o, n // 16) / us / 1e3, 1)}
+        extra["cases"] = cases
+        extra["submetrics"] = {"moe_layer_decode_rows_config3": moe_submetric(t3, synth, torch),
+                               "prefill": prefill_submetric(t3, synth, torch)}
 
     if t3.device_error() != 0:
         raise SystemExit("a kernel reported a bounded-wait failure; the numbers are void")
 
-    times = torch.tensor([ms, e2e_ms, e2e_wall_ms], dtype=torch.float64, device="cuda")
+    times = torch.tensor([ms / args.steps, e2e_ms / e2e_steps], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, e2e_ms, e2e_wall_ms = times.tolist()
+    ms_per_step, e2e_ms_per_step = times.tolist()
+    clocks = sampler.stop() if rank == 0 else None
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    peak, peak_kind = measured_peaks()
-    ms_per_step = ms / args.steps
+    peaks = measured_peaks()
     value = world * STEP_BYTES / (ms_per_step * 1e-3) / 1e9
-    e2e_value = world * STEP_BYTES / (max(e2e_ms, e2e_wall_ms) / args.steps * 1e-3) / 1e9
-    per_launch_bytes = STEP_BYTES / len(sets[0])
-    per_launch_s = ms_per_step * 1e-3 / len(sets[0])
-    achieved = per_launch_bytes / per_launch_s / 1e9
+    achieved = (STEP_BYTES / LINEARS) / (ms_per_step * 1e-3 / LINEARS) / 1e9
     traffic = None
     try:
         with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
@@ -326,21 +456,23 @@ def run_ours(args) -> None:
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "code_bytes_per_step": STEP_BYTES, "linears_per_step": len(sets[0]),
-                   "l2": f"weights rotate over {copies} copies ({copies * STEP_BYTES / 1e6:.0f} MB of codes > L2)",
+        "config": {"workload": WORKLOAD, "code_bytes_per_step": STEP_BYTES, "linears_per_step": LINEARS,
+                   "l2": f"weights rotate over {COPIES} copies ({COPIES * STEP_BYTES / 1e6:.0f} MB of codes > L2)",
                    "launch": launch_mode,
                    "multi_gpu": "replicas only: each rank runs the sweep on its own weight copies, no collective"},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "dense_gemv_kernel (21 launches a step)"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
+                     "frac": achieved / peaks["hbm"], "traffic": traffic, "peak_kind": peaks["kind"],
+                     "kernel": "dense_gemv_kernel (21 launches a step; bytes and time are the step's, per launch)"},
         "cpu_baseline": {"value": cpu["value"], "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": "one full pass of the 21-linear sweep, format.project decoding every tile per call"},
-        "e2e": {"value": e2e_value, "unit": UNIT,
+        "e2e": {"value": world * STEP_BYTES / (e2e_ms_per_step * 1e-3) / 1e9, "unit": UNIT,
                 "h2d_bytes_per_step": sum(i * 2 for (i, o) in SHAPES for _ in KS),
-                "d2h_bytes_per_step": sum(o * 2 for (i, o) in SHAPES for _ in KS)},
+                "d2h_bytes_per_step": sum(o * 2 for (i, o) in SHAPES for _ in KS),
+                "api": "t3_table()->matmul on host arrays, one call a linear, result on the host when it returns"},
         "gpu_launches": int(launches),
         "clocks": clocks,
-        "cases": cases,
     }
+    line.update(extra)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -349,14 +481,19 @@ def run_ours(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-cases", action="store_true", help="skip the per-linear timing table")
+    ap.add_argument("--quick", action="store_true", help="headline and e2e only (no per-linear table, no submetrics)")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of replaying CUDA graphs")
+    ap.add_argument("--case", default=None, choices=["moe_decode", "moe_prefill", "dense_prefill"],
+                    help="run one case eagerly --steps times and exit (for profilers)")
+    ap.add_argument("--rows", type=int, default=1, help="rows of --case")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.case:
+        run_case(args)
     else:
         run_ours(args)
 

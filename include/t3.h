@@ -136,6 +136,13 @@ int t3_moe_with_shared(const void* x, int x_dtype, size_t rows, const t3_bank* b
                        const void* scores, int scores_dtype, int topk, t3_decode dec, const void* shared, void* y,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* The routed chain's last step on its own: y[row] = sum over the row's slots, in slot order, of score * v, in f32 with a
+ * multiply and an add (ref.moeRow, src/core/ref.zig:106), stored in y_dtype, plus the optional shared-expert add.
+ * v is f16 [rows * topk, hidden]: each row-slot's finished down projection, the unit an expert-parallel combine returns
+ * (the reference's per-slot outputs that a caller combines: src/kernels/hip/decode/decode.hip:11-13). */
+int t3_moe_merge(const void* v, const void* scores, int scores_dtype, size_t rows, int topk, int hidden,
+                 const void* shared, void* y, int y_dtype, void* stream);
+
 /* t3_moe without a workspace argument, for callers that cannot allocate device memory (a host whose memory pool owns the
  * whole GPU, a plugin that is only handed activations and weights). It has no counterpart in the reference, which
  * allocates its scratch through MLX. The scratch lives in a fixed device array inside the library image:

@@ -75,6 +75,7 @@ SYMBOLS = {
     "t3_moe_swiglu": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _u32, _i, _vp, _vp, _sz, _vp]),
     "t3_moe_clamped": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _i, _vp, _vp, _sz, _vp]),
     "t3_moe_with_shared": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp, _vp, _sz, _vp]),
+    "t3_moe_merge": (_i, [_vp, _vp, _i, _sz, _i, _i, _vp, _vp, _i, _vp]),
     "t3_moe_noalloc": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp]),
     "t3_set_trace": (None, [_vp]),
     "t3_launch_count": (C.c_uint64, []),
@@ -288,6 +289,19 @@ def moe(x, bank: Bank, inds, scores, dec: Decode = Decode.mul1, verify_rows: boo
     """root.moe (src/root.zig:822-825): x [B, S, D], inds/scores [B, S, K]; y in x's shape and dtype."""
     del verify_rows  # accepted and ignored, as the reference does
     return _moe(x, bank, inds, scores, dec, 0, CLAMP_GATE_IN, None, "moe")
+
+
+def moe_merge(v: torch.Tensor, scores: torch.Tensor, out_dtype: torch.dtype, shared=None) -> torch.Tensor:
+    """The routed chain's last step (t3_moe_merge): v f16 [rows, topk, hidden], scores [rows, topk]; y [rows, hidden]."""
+    _need_cuda(v, scores)
+    if v.dim() != 3 or v.dtype != torch.float16 or tuple(scores.shape) != tuple(v.shape[:2]):
+        raise Exl3Error(1, "BadExl3Shape")
+    rows, topk, hidden = v.shape
+    y = torch.empty((rows, hidden), dtype=out_dtype, device=v.device)
+    _check(lib().t3_moe_merge(v.data_ptr(), scores.data_ptr(), _DTYPES[scores.dtype], rows, topk, hidden,
+                              shared.data_ptr() if shared is not None else None, y.data_ptr(), _DTYPES[out_dtype],
+                              _stream_ptr(v)))
+    return y
 
 
 def moe_swiglu(x, bank: Bank, inds, scores, dec: Decode, limit: int, clamp_at: int = CLAMP_GATE_IN) -> torch.Tensor:

@@ -66,6 +66,7 @@ uint32_t one_wave() {
 
 // K slices for `units` independent (output block, job) pairs over nb 128-blocks of K: the largest power of two, at most
 // `cap`, that keeps the whole grid (units x slices x `fan` CTAs a slice) inside one wave; 1 when even that does not fit.
+// (Other counts work too, slices may differ by a block, but measured slower than the nearest power of two below them.)
 uint32_t pick_split(uint32_t nb, uint32_t units, uint32_t fan, uint32_t cap) {
     uint32_t s = 1;
     while (s * 2u <= nb && s * 2u <= cap && (uint64_t)units * fan * s * 2u <= one_wave()) s *= 2u;
@@ -519,6 +520,27 @@ int t3_moe_clamped(const void* x, int x_dtype, size_t rows, const t3_bank* bank,
     if (limit <= 0 || limit > 128) return T3_INVALID_CLAMP;
     return moe_call(x, x_dtype, rows, bank, inds, scores, scores_dtype, topk, dec, (uint32_t)limit, T3_CLAMP_GATE_IN,
                     nullptr, y, workspace, workspace_bytes, stream);
+}
+
+int t3_moe_merge(const void* v, const void* scores, int scores_dtype, size_t rows, int topk, int hidden,
+                 const void* shared, void* y, int y_dtype, void* stream) {
+    if (!v || !scores || !y) return T3_NULL_POINTER;
+    if (rows < 1 || rows > 0x7FFFFFFFu / 32u || topk <= 0 || topk > T3_REDUCE_MAX_TOPK || hidden <= 0) return T3_BAD_EXL3_SHAPE;
+    if (rows > 65535u) return T3_BAD_EXL3_SHAPE;  // one grid row a row
+    if (!dtype_ok(scores_dtype) || !dtype_ok(y_dtype)) return T3_BAD_EXL3_DTYPE;
+    MoeArgs a = {};
+    a.v = const_cast<void*>(v);
+    a.scores = scores;
+    a.score_dt = scores_dtype;
+    a.rows = (uint32_t)rows;
+    a.topk = (uint32_t)topk;
+    a.hidden = (uint32_t)hidden;
+    a.shared = shared;
+    a.y = y;
+    a.x_dt = y_dtype;
+    a.overlap = 0;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cuda_status(launch_moe_merge(a, static_cast<cudaStream_t>(stream)));
 }
 
 int t3_moe_with_shared(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds,

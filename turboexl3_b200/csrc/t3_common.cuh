@@ -60,6 +60,60 @@ __device__ __forceinline__ void h128_warp(float (&v)[4], uint32_t lane) {
     v[3] = d01 - d23;
 }
 
+// The same transform for a lane that holds four CONSECUTIVE elements 4 L .. 4 L + 3 (so a warp's loads and stores of a
+// 128-block are one contiguous 256- or 512-byte run): index bits 0-1 inside the lane, bits 2-6 across lanes.
+__device__ __forceinline__ void h128_warp_v4(float (&v)[4], uint32_t lane) {
+    const float s01 = v[0] + v[1], d01 = v[0] - v[1], s23 = v[2] + v[3], d23 = v[2] - v[3];
+    v[0] = s01 + s23;
+    v[1] = d01 + d23;
+    v[2] = s01 - s23;
+    v[3] = d01 - d23;
+#pragma unroll
+    for (uint32_t bit = 1; bit < 32u; bit <<= 1) {
+        const bool upper = (lane & bit) != 0u;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float other = __shfl_xor_sync(0xFFFFFFFFu, v[j], bit);
+            v[j] = upper ? other - v[j] : v[j] + other;
+        }
+    }
+}
+
+// four consecutive elements i .. i + 3 (i a multiple of 4) of an activation array as f32, one vector load
+__device__ __forceinline__ void load_act4(const void* p, int dt, size_t i, float (&v)[4]) {
+    if (dt == kF32) {
+        const float4 f = *reinterpret_cast<const float4*>(static_cast<const float*>(p) + i);
+        v[0] = f.x, v[1] = f.y, v[2] = f.z, v[3] = f.w;
+    } else {
+        const uint2 u = *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(p) + i);
+        if (dt == kF16) {
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+            const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+            v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y;
+        } else {
+            v[0] = __uint_as_float(u.x << 16), v[1] = __uint_as_float(u.x & 0xFFFF0000u);
+            v[2] = __uint_as_float(u.y << 16), v[3] = __uint_as_float(u.y & 0xFFFF0000u);
+        }
+    }
+}
+
+__device__ __forceinline__ void load_half4(const __half* p, float (&v)[4]) { load_act4(p, kF16, 0, v); }
+
+// four consecutive elements stored in dtype dt (round to nearest even), one vector store
+__device__ __forceinline__ void store_act4(void* p, int dt, size_t i, const float (&v)[4]) {
+    if (dt == kF32) {
+        *reinterpret_cast<float4*>(static_cast<float*>(p) + i) = make_float4(v[0], v[1], v[2], v[3]);
+    } else if (dt == kF16) {
+        const __half2 a = __floats2half2_rn(v[0], v[1]), b = __floats2half2_rn(v[2], v[3]);
+        *reinterpret_cast<uint2*>(static_cast<__half*>(p) + i) =
+            make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+    } else {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p) + i) =
+            make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+    }
+}
+
 // D += A (16x16, row) * B (16x8, col), f16 operands, f32 accumulate
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -91,21 +145,27 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 // Waits for the barrier's phase of the given parity, at most kSpinLimit polls (each poll may itself sleep for a
 // hardware-defined time). Returns false after giving up; the caller records the error and carries on to its exit
 // path, so a lost copy never hangs the device.
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kSpinLimit = 1u << 20;
+__device__ __forceinline__ uint32_t mbar_try(uint32_t addr, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    return done;
+}
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t addr, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i)
+        if (mbar_try(addr, parity)) return true;
+    return false;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_addr(bar);
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (done) return true;
-    }
-    return false;
+    if (mbar_try(addr, parity)) return true;  // the common case costs one poll and no loop
+    return mbar_wait_slow(addr, parity);
 }
 
 // `bytes` (a multiple of 16) from 16-byte-aligned global memory to 16-byte-aligned shared memory of this CTA; completion
@@ -122,7 +182,7 @@ __device__ __forceinline__ void named_sync(uint32_t id, uint32_t threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-__device__ __forceinline__ void report(uint32_t* err, uint32_t bit) {
+static __device__ __noinline__ void report(uint32_t* err, uint32_t bit) {
     if (err) atomicOr(err, bit);
 }
 

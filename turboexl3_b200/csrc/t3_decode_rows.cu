@@ -46,11 +46,9 @@ __device__ __forceinline__ CtaSmem carve(uint8_t* smem, const GemvSmem& L) {
 }
 
 __device__ __forceinline__ void init_barriers(const CtaSmem& c, uint32_t stages) {
-    if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < stages; ++s) {
-            mbar_init(&c.full[s], 1u);
-            mbar_init(&c.empty[s], kConsumerWarps);
-        }
+    if (threadIdx.x < stages) {  // one thread a stage
+        mbar_init(&c.full[threadIdx.x], 1u);
+        mbar_init(&c.empty[threadIdx.x], kConsumerWarps);
         mbar_init_fence();
     }
 }
@@ -62,11 +60,11 @@ __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.w
 // rows' owners. `count` live rows.
 template <int N, int RM>
 __device__ __forceinline__ void gemv_and_push(cg::cluster_group& cluster, const CtaSmem& c, uint32_t nrows, uint32_t n,
-                                              uint32_t mask, Ring rc, uint32_t xstride, uint32_t& chunk, uint32_t count,
+                                              uint32_t mask, Ring rc, uint32_t xstride, RingPos& pos, uint32_t count,
                                               uint32_t rank, uint32_t csize, uint32_t warp, uint32_t lane, uint32_t* err) {
     const uint32_t tcol = warp & (kTileWarps - 1u), kg = warp / kTileWarps;
     float acc[RowCap<RM>::kMB][2][4] = {};
-    consume_slab<N, CB, RM>(c.ring, c.full, c.empty, nrows, n, mask, rc, c.xp, xstride, chunk, tcol, kg, lane, acc, err);
+    consume_slab<N, CB, RM>(c.ring, c.full, c.empty, nrows, n, mask, rc, c.xp, xstride, pos, tcol, kg, lane, acc, err);
     if (kg == 1) store_local<RM>(c.local, acc, tcol, lane);
     named_sync(1, kConsumerThreads);
     if (kg == 0) push_partial<RM>(cluster, c.recv, c.local, acc, count, rank, csize, tcol, lane);
@@ -97,14 +95,16 @@ __global__ void __launch_bounds__(kGemvThreads, 2) dense_gemv_kernel(const Dense
     __syncthreads();
     if (traced && tid == 0) a.trace[1] = clock64();
 
-    uint32_t chunk = 0;
+    RingPos pos;
+    float sv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if (warp == kConsumerWarps) {
         // the weights do not depend on the stream's previous kernel: start them, then let the next kernel do the same
         const uint8_t* src = a.trellis + ((size_t)(b0 * 8u) * out_tiles + blk * 8u) * tile_bytes;
-        produce_slab(c.ring, c.full, c.empty, src, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, chunk, lane, a.err);
+        produce_slab(c.ring, c.full, c.empty, src, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, pos, lane, a.err);
         pdl_trigger();
     } else {
         pdl_trigger();
+        load_scales(static_cast<const __half*>(a.svh) + blk * 128u, lane, sv);  // weights-side: ahead of the wait
         pdl_wait();  // x may be the previous kernel's output
         for (uint32_t task = warp; task < a.rows * nblk; task += kConsumerWarps) {
             const uint32_t row = task / nblk, b = task - row * nblk;
@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) dense_gemv_kernel(const Dense
             mbar_wait(&c.full[0], 0u);
             a.trace[3] = clock64();
         }
-        gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, chunk, a.rows, rank, csize, warp, lane, a.err);
+        gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, pos, a.rows, rank, csize, warp, lane, a.err);
         if (traced && tid == 0) a.trace[4] = clock64();
     }
     cluster_arrive();
@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) dense_gemv_kernel(const Dense
             const uint32_t row = i * csize + rank;
             float v[4];
             gather_owned(c.recv, owned, i, 0, 1, csize, lane, v);
-            finish_block(v, static_cast<const __half*>(a.svh) + blk * 128u, lane);
+            finish_block(v, sv, lane);
 #pragma unroll
             for (int j = 0; j < 4; ++j) store_act(a.y, a.x_dt, (size_t)row * a.out + blk * 128u + lane + 32u * j, v[j]);
         }
@@ -223,11 +223,11 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_gate_up_kernel(const MoeA
     const uint8_t* wsrc = (proj ? a.up_t : a.gate_t) + e * expert_bytes + ((size_t)(b0 * 8u) * out_tiles + ib * 8u) * tile_bytes;
     const __half* suh = static_cast<const __half*>(proj ? a.up_suh : a.gate_suh) + (size_t)e * H;
     const uint32_t owned = rows_owned(RM, csize);
-    uint32_t chunk = 0;
+    RingPos pos;
     for (uint32_t m0 = 0; m0 < mem.count; m0 += RM) {
         const uint32_t mcount = min((uint32_t)RM, mem.count - m0);
         if (warp == kConsumerWarps) {
-            produce_slab(c.ring, c.full, c.empty, wsrc, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, chunk, lane, a.err);
+            produce_slab(c.ring, c.full, c.empty, wsrc, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, pos, lane, a.err);
         } else {
             for (uint32_t i = mcount * xstride + tid; i < RM * xstride; i += kConsumerThreads) c.xp[i] = __float2half_rn(0.0f);
             for (uint32_t task = warp; task < mcount * nblk; task += kConsumerWarps) {
@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_gate_up_kernel(const MoeA
                 prepare_block(a.x, a.x_dt, (size_t)row * H + k0, suh + k0, c.xp + m * xstride + b * 128u, lane);
             }
             named_sync(1, kConsumerThreads);
-            gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, chunk, mcount, rank, csize, warp, lane, a.err);
+            gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, pos, mcount, rank, csize, warp, lane, a.err);
         }
         cluster_arrive();
         const bool last = m0 + RM >= mem.count;
@@ -247,15 +247,17 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_gate_up_kernel(const MoeA
             for (uint32_t i = warp; i * csize + rank < mcount; i += kConsumerWarps) {
                 const uint32_t m = i * csize + rank;
                 float g[4], u[4];
+                float sg[4], su[4], sd[4];
+                load_scales(static_cast<const __half*>(a.gate_svh) + eo, lane, sg);
+                load_scales(static_cast<const __half*>(a.up_svh) + eo, lane, su);
+                load_scales(static_cast<const __half*>(a.down_suh) + eo, lane, sd);
                 gather_owned(c.recv, owned, i, 0, 2, a.split_gu, lane, g);
                 gather_owned(c.recv, owned, i, 1, 2, a.split_gu, lane, u);
-                finish_block(g, static_cast<const __half*>(a.gate_svh) + eo, lane);
-                finish_block(u, static_cast<const __half*>(a.up_svh) + eo, lane);
+                finish_block(g, sg, lane);
+                finish_block(u, su, lane);
                 float d[4];
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    d[q] = round_half(swiglu(g[q], u[q], a.limit, a.clamp_at)) *
-                           __half2float(static_cast<const __half*>(a.down_suh)[eo + lane + 32u * q]);
+                for (int q = 0; q < 4; ++q) d[q] = round_half(swiglu(g[q], u[q], a.limit, a.clamp_at)) * sd[q];
                 h128_warp(d, lane);
                 __half* hd = static_cast<__half*>(a.hd) + (size_t)s_members[m0 + m] * I + ib * 128u;
 #pragma unroll
@@ -298,11 +300,11 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs
     const size_t expert_bytes = (size_t)(I / 16u) * out_tiles * tile_bytes;
     const uint8_t* wsrc = a.down_t + e * expert_bytes + ((size_t)(b0 * 8u) * out_tiles + hb * 8u) * tile_bytes;
     const uint32_t owned = rows_owned(RM, csize);
-    uint32_t chunk = 0;
+    RingPos pos;
     for (uint32_t m0 = 0; m0 < mem.count; m0 += RM) {
         const uint32_t mcount = min((uint32_t)RM, mem.count - m0);
         if (warp == kConsumerWarps) {
-            produce_slab(c.ring, c.full, c.empty, wsrc, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, chunk, lane, a.err);
+            produce_slab(c.ring, c.full, c.empty, wsrc, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, pos, lane, a.err);
             pdl_trigger();
         } else {
             pdl_trigger();
@@ -319,7 +321,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs
                 }
             }
             named_sync(1, kConsumerThreads);
-            gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, chunk, mcount, rank, csize, warp, lane, a.err);
+            gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, pos, mcount, rank, csize, warp, lane, a.err);
         }
         cluster_arrive();
         const bool last = m0 + RM >= mem.count;
@@ -328,9 +330,10 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs
         if (warp < kConsumerWarps) {
             for (uint32_t i = warp; i * csize + rank < mcount; i += kConsumerWarps) {
                 const uint32_t m = i * csize + rank;
-                float v[4];
+                float v[4], sv[4];
+                load_scales(static_cast<const __half*>(a.down_svh) + (size_t)e * H + hb * 128u, lane, sv);
                 gather_owned(c.recv, owned, i, 0, 1, csize, lane, v);
-                finish_block(v, static_cast<const __half*>(a.down_svh) + (size_t)e * H + hb * 128u, lane);
+                finish_block(v, sv, lane);
                 __half* vo = static_cast<__half*>(a.v) + (size_t)s_members[m0 + m] * H + hb * 128u;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) vo[lane + 32u * q] = __float2half_rn(v[q]);

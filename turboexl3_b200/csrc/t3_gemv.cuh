@@ -30,7 +30,7 @@ constexpr uint32_t kGemvThreads = kConsumerThreads + 32u;
 constexpr uint32_t kMaxStages = 32;
 constexpr uint32_t kPartialStride = 136;  // floats per row of a partial-sum tile (128 + 8: conflict-free float2 stores)
 constexpr uint32_t kXpPad = 16;           // halfs added to an xp row so a quad's 8-byte loads spread over the banks
-constexpr uint32_t kBatch = 4;            // tiles a warp decodes back to back before their MMAs (instruction-level overlap)
+constexpr uint32_t kBatch = 4;            // tiles of a stage a warp owns: their code words are loaded together
 constexpr uint32_t kStageRows = kKGroups * kBatch;  // tk rows of a ring stage: one 128-input block, one batch a warp
 
 // How the ring is cut for one launch (host-chosen)
@@ -79,21 +79,32 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 
 // ---- producer -----------------------------------------------------------------------------------------------------
 
-// Streams tk rows [0, nrows) of a block's slab into the ring: row r is `row_bytes` contiguous bytes at
-// src + r * src_row_stride (bytes). `chunk` continues across calls so barrier parities stay in step.
+// Where a warp stands in the ring: the slot it uses next and how many times it has gone round (kept as running counters:
+// the stage count is a launch value and integer division is not free).
+struct RingPos {
+    uint32_t slot = 0, lap = 0;
+    __device__ __forceinline__ void advance(uint32_t stages) {
+        if (++slot == stages) {
+            slot = 0;
+            ++lap;
+        }
+    }
+};
+
+// Streams tk rows [0, nrows) of a block's slab into the ring (nrows a multiple of kStageRows): row r is `row_bytes`
+// contiguous bytes at src + r * src_row_stride (bytes). `pos` continues across calls so barrier parities stay in step.
 __device__ __forceinline__ void produce_slab(uint8_t* ring, uint64_t* full, uint64_t* empty, const uint8_t* src,
                                              size_t src_row_stride, uint32_t nrows, uint32_t row_bytes, Ring rc,
-                                             uint32_t& chunk, uint32_t lane, uint32_t* err) {
+                                             RingPos& pos, uint32_t lane, uint32_t* err) {
     const uint32_t stage_bytes = kStageRows * row_bytes;
-    for (uint32_t r0 = 0; r0 < nrows; r0 += kStageRows, ++chunk) {
-        const uint32_t slot = chunk % rc.stages, use = chunk / rc.stages;
-        if (use > 0 && !mbar_wait(&empty[slot], (use - 1u) & 1u)) report(err, kErrEmptyWait);
-        const uint32_t here = min(kStageRows, nrows - r0);
-        if (lane == 0) mbar_arrive_expect_tx(&full[slot], here * row_bytes);
+    for (uint32_t r0 = 0; r0 < nrows; r0 += kStageRows) {
+        if (pos.lap > 0 && !mbar_wait(&empty[pos.slot], (pos.lap - 1u) & 1u)) report(err, kErrEmptyWait);
+        if (lane == 0) mbar_arrive_expect_tx(&full[pos.slot], stage_bytes);
         __syncwarp();
-        for (uint32_t r = lane; r < here; r += 32u)
-            bulk_copy_g2s(ring + slot * stage_bytes + r * row_bytes, src + (size_t)(r0 + r) * src_row_stride, row_bytes,
-                          &full[slot]);
+        if (lane < kStageRows)
+            bulk_copy_g2s(ring + pos.slot * stage_bytes + lane * row_bytes, src + (size_t)(r0 + lane) * src_row_stride,
+                          row_bytes, &full[pos.slot]);
+        pos.advance(rc.stages);
     }
 }
 
@@ -113,15 +124,15 @@ __device__ __forceinline__ void mma_tile(float (&acc)[RowCap<RM>::kMB][2][4], co
     }
 }
 
-// Consumer warp (tile column `tcol`, K group `kg`) folds tk rows kg, kg + kKGroups, ... of [0, nrows) into acc.
-// xp: prepared rows in lane order, row stride `xstride` halfs, k = 0 at the slab's first input. acc[mb][nt] is the mma C
-// fragment of rows 16 mb .. 16 mb + 15, columns 16 tcol + 8 nt .. + 7.
-// A stage holds kStageRows tk rows, so a warp's share of a full stage is exactly one batch of kBatch tiles, and with the
-// rate a template constant every shared-memory offset inside a stage is an immediate.
+// Consumer warp (tile column `tcol`, K group `kg`) folds tk rows kg, kg + kKGroups, ... of [0, nrows) into acc (nrows a
+// multiple of kStageRows). xp: prepared rows in lane order, row stride `xstride` halfs, k = 0 at the slab's first input.
+// acc[mb][nt] is the mma C fragment of rows 16 mb .. 16 mb + 15, columns 16 tcol + 8 nt .. + 7.
+// A stage holds kStageRows tk rows, so a warp's share of a stage is exactly one batch of kBatch tiles, and with the rate
+// a template constant every shared-memory offset inside a stage is an immediate.
 template <int N, int CB, int RM>
 __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full, uint64_t* empty, uint32_t nrows,
                                              uint32_t n_rt, uint32_t mask, Ring rc, const __half* xp, uint32_t xstride,
-                                             uint32_t& chunk, uint32_t tcol, uint32_t kg, uint32_t lane,
+                                             RingPos& pos, uint32_t tcol, uint32_t kg, uint32_t lane,
                                              float (&acc)[RowCap<RM>::kMB][2][4], uint32_t* err) {
     constexpr int NP = N > 0 ? N : 16;
     constexpr uint32_t kRaw = raw_words(NP);
@@ -129,18 +140,16 @@ __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full
     const uint32_t tile_bytes = 2u * n, row_bytes = 16u * n, stage_bytes = kStageRows * row_bytes;
     LanePlan<NP> plan;
     if (N > 0) plan.init(lane);
-    // byte offsets of the lane's raw words inside a tile row of the block, from the warp's first row of a stage
+    // byte offsets of the lane's raw words inside a stage, from the warp's first row
     uint32_t woff[kRaw];
 #pragma unroll
     for (uint32_t i = 0; i < kRaw; ++i) woff[i] = tcol * tile_bytes + kg * row_bytes + plan.idx[i] * 4u;
-    const __half* xa = xp + (lane >> 2) * xstride + 4u * (lane & 3u) + kg * 16u;
-    for (uint32_t r0 = 0; r0 < nrows; r0 += kStageRows, ++chunk) {
-        const uint32_t slot = chunk % rc.stages, use = chunk / rc.stages;
-        if (!mbar_wait(&full[slot], use & 1u)) report(err, kErrFullWait);
-        const uint32_t here = min(kStageRows, nrows - r0);
-        const uint8_t* st = ring + slot * stage_bytes;
-        const __half* xs = xa + r0 * 16u;
-        if (N > 0 && here == kKGroups * kBatch) {
+    const __half* xs = xp + (lane >> 2) * xstride + 4u * (lane & 3u) + kg * 16u;
+    for (uint32_t r0 = 0; r0 < nrows; r0 += kStageRows, xs += kStageRows * 16u) {
+        if (!mbar_wait(&full[pos.slot], pos.lap & 1u)) report(err, kErrFullWait);
+        const uint8_t* st = ring + pos.slot * stage_bytes;
+        if (N > 0) {
+            // the stage's four tiles of this warp: words, then decodes, then MMAs, so four dependent chains overlap
             uint32_t raw[kBatch][kRaw];
 #pragma unroll
             for (uint32_t i = 0; i < kBatch; ++i)
@@ -153,16 +162,17 @@ __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full
 #pragma unroll
             for (uint32_t i = 0; i < kBatch; ++i) mma_tile<RM>(acc, xs + i * kKGroups * 16u, xstride, b[i]);
         } else {
-            for (uint32_t r = kg; r < here; r += kKGroups) {
+#pragma unroll 1
+            for (uint32_t i = 0; i < kBatch; ++i) {
                 uint32_t b[4];
-                const uint32_t* tile = reinterpret_cast<const uint32_t*>(st + tcol * tile_bytes + r * row_bytes);
-                if (N > 0) decode_lane<NP, CB>(tile, plan, mask, b);
-                else decode_lane_any<CB>(tile, n, lane, mask, b);
-                mma_tile<RM>(acc, xp + (lane >> 2) * xstride + 4u * (lane & 3u) + (r0 + r) * 16u, xstride, b);
+                decode_lane_any<CB>(reinterpret_cast<const uint32_t*>(st + tcol * tile_bytes + (kg + i * kKGroups) * row_bytes),
+                                    n, lane, mask, b);
+                mma_tile<RM>(acc, xs + i * kKGroups * 16u, xstride, b);
             }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[slot]);
+        if (lane == 0) mbar_arrive(&empty[pos.slot]);
+        pos.advance(rc.stages);
     }
 }
 
@@ -244,12 +254,18 @@ __device__ __forceinline__ void prepare_block(const void* x, int dt, size_t x_of
 
 // The output rotation of one row's 128-block by one warp (format.finishOutput, format.zig:370-380): v[j] holds the
 // f32 inner product of column lane + 32 j; returns y = f16(H128(f16(v)) svh) as f32 values in v.
-__device__ __forceinline__ void finish_block(float (&v)[4], const __half* svh_blk, uint32_t lane) {
+__device__ __forceinline__ void finish_block(float (&v)[4], const float (&sv)[4], uint32_t lane) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) v[j] = round_half(v[j]);
     h128_warp(v, lane);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = round_half(v[j] * kHadScale * __half2float(svh_blk[lane + 32u * j]));
+    for (int j = 0; j < 4; ++j) v[j] = round_half(v[j] * kHadScale * sv[j]);
+}
+
+// the lane's four scale values of a 128-block (columns lane + 32 j), fetched ahead of the wait they would otherwise follow
+__device__ __forceinline__ void load_scales(const __half* blk, uint32_t lane, float (&sv)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sv[j] = __half2float(blk[lane + 32u * j]);
 }
 
 // K blocks [b0, b1) of rank r when nb 128-blocks are cut over s ranks

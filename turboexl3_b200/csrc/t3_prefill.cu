@@ -22,15 +22,28 @@
 namespace t3 {
 namespace {
 
-constexpr uint32_t kBM = 256, kBN = 128, kBK = 64;
-constexpr uint32_t kStages = 4;
-constexpr uint32_t kABytes = kBM * kBK * 2u;  // 32 KB
+constexpr uint32_t kBN = 128, kBK = 64;
 constexpr uint32_t kBBytes = kBN * kBK * 2u;  // 16 KB
-constexpr uint32_t kStageBytes = kABytes + kBBytes;
-constexpr uint32_t kDecodeWarps = 8;
+constexpr uint32_t kDecodeWarps = 16;
 constexpr uint32_t kGemmThreads = 32u * (2u + kDecodeWarps);
-constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kGemmSmem = kStages * kStageBytes + 1024u /* alignment slack */ + 256u /* barriers */;
+constexpr uint32_t kMaxStages = 4;      // operand stages (A by TMA, B by the decode warps)
+constexpr uint32_t kMaxCodeStages = 8;  // stages of the code ring that feeds the decode warps
+
+// The two tile heights: 256 rows (two M = 128 accumulators share every decoded B tile; dense linears and full expert
+// tiles) and 128 rows (half the shared memory and tensor memory, so two CTAs fit a multiprocessor: routed experts, whose
+// tiles are mostly part-full and whose cost is the decode).
+template <int BM>
+struct Tile {
+    static_assert(BM == 128 || BM == 256, "tile height");
+    static constexpr uint32_t kABytes = BM * kBK * 2u;
+    static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+    static constexpr uint32_t kStages = 3u;
+    static constexpr uint32_t kCodeStages = BM == 256 ? 6u : 3u;
+    static constexpr uint32_t kTmemCols = BM == 256 ? 256u : 128u;
+    static constexpr int kMinBlocks = BM == 256 ? 1 : 2;
+    // dynamic shared memory: operand stages, the code ring (4 tile rows of 16 n bytes a stage), barriers, alignment slack
+    static constexpr uint32_t smem(uint32_t n) { return kStages * kStageBytes + kCodeStages * 64u * n + 1024u + 512u; }
+};
 
 // ---- tcgen05 / TMA wrappers ----------------------------------------------------------------------------------------
 
@@ -102,6 +115,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// 16 consecutive f32 columns of this thread's tensor-memory lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
 // ---- the GEMM ------------------------------------------------------------------------------------------------------
 
 struct GemmArgs {
@@ -117,32 +142,40 @@ struct GemmArgs {
     uint32_t* err;
 };
 
-template <int NN, int CB>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int NN, int CB, int BM>
+__global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
     gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmArgs a) {
+    using T = Tile<BM>;
+    constexpr uint32_t kStages = T::kStages, kStageBytes = T::kStageBytes, kABytes = T::kABytes;
     int e = 0, first = 0, rows = 0;
     if (a.tiles) {
         const int4 t = a.tiles[blockIdx.y];
         e = t.x, first = t.y, rows = t.z;
     } else {
-        first = (int)(blockIdx.y * kBM);
-        rows = min((int)kBM, (int)a.dense_rows - first);
+        first = (int)(blockIdx.y * BM);
+        rows = min((int)BM, (int)a.dense_rows - first);
     }
     if (rows <= 0) return;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_addr(smem_raw);
     uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+    constexpr uint32_t kCodeStages = T::kCodeStages;
+    const uint32_t code_stage_bytes = 64u * a.n;  // 4 tile rows x the CTA's 8 tiles x 2 n bytes
+    uint8_t* codes = smem + kStages * kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(codes + kCodeStages * code_stage_bytes);
     uint64_t* full_a = bars;
-    uint64_t* full_b = bars + kStages;
-    uint64_t* empty = bars + 2 * kStages;
-    uint64_t* acc_full = bars + 3 * kStages;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 1);
+    uint64_t* full_b = bars + kMaxStages;
+    uint64_t* empty = bars + 2 * kMaxStages;
+    uint64_t* full_c = bars + 3 * kMaxStages;
+    uint64_t* empty_c = full_c + kMaxCodeStages;
+    uint64_t* acc_full = empty_c + kMaxCodeStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t per_op = a.N / kBN, op = blockIdx.x / per_op, nt = blockIdx.x - op * per_op;
     const uint32_t ksteps = a.K / kBK;
+    const uint32_t tile_bytes = 2u * a.n, out_tiles = a.N / 16u;
 
     if (tid == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
@@ -150,10 +183,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             mbar_init(&full_b[s], kDecodeWarps);
             mbar_init(&empty[s], 1u);
         }
+        for (uint32_t s = 0; s < kCodeStages; ++s) {
+            mbar_init(&full_c[s], 1u);
+            mbar_init(&empty_c[s], kDecodeWarps);
+        }
         mbar_init(acc_full, 1u);
         mbar_init_fence();
     }
-    if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+    if (warp == 1) tmem_alloc(tmem_slot, T::kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -161,11 +198,41 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
     if (warp == 0) {
         if (lane == 0) {
-            for (uint32_t ks = 0; ks < ksteps; ++ks) {
-                const uint32_t s = ks % kStages, u = ks / kStages;
-                if (u > 0 && !mbar_wait(&empty[s], (u - 1u) & 1u)) report(a.err, kErrEmptyWait);
-                mbar_arrive_expect_tx(&full_a[s], kABytes);
-                tma_load_2d(smem + s * kStageBytes, &tmap_a, (int)(ks * kBK), (int)(op * a.a_op_rows) + first, &full_a[s]);
+            // One thread feeds both rings and never blocks on either: it polls the two "slot free" barriers in turn, so the
+            // code stream (which runs ahead of the decode) and the activation stream (which follows the MMAs) cannot starve
+            // each other. Codes: a stage's four tile rows of the CTA's 8 tiles, 16 n contiguous bytes each.
+            const uint8_t* src = a.trellis[op] + (size_t)e * a.expert_bytes + (size_t)(nt * 8u) * tile_bytes;
+            const size_t tk_stride = (size_t)out_tiles * tile_bytes;
+            const uint32_t row_bytes = 8u * tile_bytes;
+            uint32_t ka = 0, kc = 0, idle = 0;
+            while (ka < ksteps || kc < ksteps) {
+                bool moved = false;
+                if (kc < ksteps) {
+                    const uint32_t cs = kc % kCodeStages, u = kc / kCodeStages;
+                    if (u == 0 || mbar_try(smem_addr(&empty_c[cs]), (u - 1u) & 1u)) {
+                        mbar_arrive_expect_tx(&full_c[cs], 4u * row_bytes);
+#pragma unroll
+                        for (uint32_t i = 0; i < 4u; ++i)
+                            bulk_copy_g2s(codes + cs * code_stage_bytes + i * row_bytes, src + (size_t)(kc * 4u + i) * tk_stride,
+                                          row_bytes, &full_c[cs]);
+                        ++kc;
+                        moved = true;
+                    }
+                }
+                if (ka < ksteps) {
+                    const uint32_t s = ka % kStages, u = ka / kStages;
+                    if (u == 0 || mbar_try(smem_addr(&empty[s]), (u - 1u) & 1u)) {
+                        mbar_arrive_expect_tx(&full_a[s], kABytes);
+                        tma_load_2d(smem + s * kStageBytes, &tmap_a, (int)(ka * kBK), (int)(op * a.a_op_rows) + first, &full_a[s]);
+                        ++ka;
+                        moved = true;
+                    }
+                }
+                idle = moved ? 0u : idle + 1u;
+                if (idle > kSpinLimit) {  // neither ring has freed a slot for a very long time: give up, the others will too
+                    report(a.err, kErrEmptyWait);
+                    break;
+                }
             }
         }
     } else if (warp == 1) {
@@ -180,83 +247,92 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 for (uint32_t kk = 0; kk < kBK / 16u; ++kk) {
                     const uint64_t bdesc = umma_desc(b_addr + kk * 32u);
                     umma_f16(tmem, umma_desc(a_addr + kk * 32u), bdesc, (ks | kk) != 0u);
-                    umma_f16(tmem + 128u, umma_desc(a_addr + 128u * 128u + kk * 32u), bdesc, (ks | kk) != 0u);
+                    if (BM == 256) umma_f16(tmem + 128u, umma_desc(a_addr + 128u * 128u + kk * 32u), bdesc, (ks | kk) != 0u);
                 }
                 umma_commit(&empty[s]);
             }
             umma_commit(acc_full);
         }
     } else {
-        const uint32_t dw = warp - 2u;
-        const uint32_t tile_bytes = 2u * a.n, out_tiles = a.N / 16u;
-        const uint8_t* wbase = a.trellis[op] + (size_t)e * a.expert_bytes + (size_t)(nt * 8u + dw) * tile_bytes;
-        const size_t tk_stride = (size_t)out_tiles * tile_bytes;
+        // decode warp dw: output tile column dw % 8 of the CTA's 128, input tile rows 2 (dw / 8) and 2 (dw / 8) + 1 of a stage
+        const uint32_t dw = warp - 2u, tcol = dw & 7u, tk0 = (dw >> 3) * 2u;
         constexpr int NP = NN > 0 ? NN : 16;
         constexpr uint32_t kRaw = raw_words(NP);
         LanePlan<NP> plan;
         plan.init(lane);
-        uint32_t nxt[4][kRaw];
-        if (NN > 0) {
+        // byte offsets of the lane's words of its two tiles inside a code stage
+        uint32_t woff[2][kRaw];
 #pragma unroll
-            for (uint32_t i = 0; i < 4u; ++i) load_lane<NP>(reinterpret_cast<const uint32_t*>(wbase + i * tk_stride), plan, nxt[i]);
-        }
+        for (uint32_t i = 0; i < 2u; ++i)
+#pragma unroll
+            for (uint32_t w = 0; w < kRaw; ++w) woff[i][w] = ((tk0 + i) * 8u + tcol) * tile_bytes + plan.idx[w] * 4u;
         const uint32_t g = lane >> 2, q = lane & 3u;
+        // where the lane's eight half2 words of its two tiles go in a B stage:
+        // B[n][k] at n * 128 + ((k / 8) ^ (n % 8)) * 16 + (k % 8) * 2; k = 16 tk + 2 q (+8), n = 16 tcol + g (+8)
+        const uint32_t row0 = (tcol * 16u + g) * 128u + 4u * q;
+        uint32_t boff[2][2];
+#pragma unroll
+        for (uint32_t i = 0; i < 2u; ++i) {
+            boff[i][0] = row0 + ((2u * (tk0 + i)) ^ g) * 16u;
+            boff[i][1] = row0 + ((2u * (tk0 + i) + 1u) ^ g) * 16u;
+        }
         for (uint32_t ks = 0; ks < ksteps; ++ks) {
-            const uint32_t s = ks % kStages, u = ks / kStages;
-            uint32_t cur[4][kRaw];
+            const uint32_t s = ks % kStages, u = ks / kStages, cs = ks % kCodeStages, uc = ks / kCodeStages;
+            if (!mbar_wait(&full_c[cs], uc & 1u)) report(a.err, kErrFullWait);
+            const uint8_t* cst = codes + cs * code_stage_bytes;
+            uint32_t b[2][4];
             if (NN > 0) {
+                uint32_t raw[2][kRaw];
 #pragma unroll
-                for (uint32_t i = 0; i < 4u; ++i)
+                for (uint32_t i = 0; i < 2u; ++i)
 #pragma unroll
-                    for (uint32_t w = 0; w < kRaw; ++w) cur[i][w] = nxt[i][w];
-                if (ks + 1u < ksteps) {
+                    for (uint32_t w = 0; w < kRaw; ++w) raw[i][w] = *reinterpret_cast<const uint32_t*>(cst + woff[i][w]);
 #pragma unroll
-                    for (uint32_t i = 0; i < 4u; ++i)
-                        load_lane<NP>(reinterpret_cast<const uint32_t*>(wbase + (size_t)((ks + 1u) * 4u + i) * tk_stride), plan,
-                                      nxt[i]);
-                }
+                for (uint32_t i = 0; i < 2u; ++i) decode_raw<NP, CB>(raw[i], plan, a.mask, b[i]);
+            } else {
+#pragma unroll
+                for (uint32_t i = 0; i < 2u; ++i)
+                    decode_lane_any<CB>(reinterpret_cast<const uint32_t*>(cst + ((tk0 + i) * 8u + tcol) * tile_bytes), a.n, lane,
+                                        a.mask, b[i]);
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_c[cs]);  // the words are in registers: the code stage may be refilled
             if (u > 0 && !mbar_wait(&empty[s], (u - 1u) & 1u)) report(a.err, kErrEmptyWait);
             uint8_t* bst = smem + s * kStageBytes + kABytes;
 #pragma unroll
-            for (uint32_t i = 0; i < 4u; ++i) {
-                uint32_t b[4];
-                if (NN > 0) decode_raw<NP, CB>(cur[i], plan, a.mask, b);
-                else
-                    decode_lane_any<CB>(reinterpret_cast<const uint32_t*>(wbase + (size_t)(ks * 4u + i) * tk_stride), a.n, lane,
-                                        a.mask, b);
-                // B[n][k] at n * 128 + ((k / 8) ^ (n % 8)) * 16 + (k % 8) * 2; this lane: k = 16 i + 2 q (+8), n = 16 dw + g (+8)
-                const uint32_t row0 = (dw * 16u + g) * 128u, row1 = row0 + 8u * 128u;
-                const uint32_t c0 = ((2u * i) ^ g) * 16u + 4u * q, c1 = ((2u * i + 1u) ^ g) * 16u + 4u * q;
-                *reinterpret_cast<uint32_t*>(bst + row0 + c0) = b[0];
-                *reinterpret_cast<uint32_t*>(bst + row0 + c1) = b[1];
-                *reinterpret_cast<uint32_t*>(bst + row1 + c0) = b[2];
-                *reinterpret_cast<uint32_t*>(bst + row1 + c1) = b[3];
+            for (uint32_t i = 0; i < 2u; ++i) {
+                *reinterpret_cast<uint32_t*>(bst + boff[i][0]) = b[i][0];
+                *reinterpret_cast<uint32_t*>(bst + boff[i][1]) = b[i][1];
+                *reinterpret_cast<uint32_t*>(bst + boff[i][0] + 8u * 128u) = b[i][2];
+                *reinterpret_cast<uint32_t*>(bst + boff[i][1] + 8u * 128u) = b[i][3];
             }
             proxy_fence();
             __syncwarp();
             if (lane == 0) mbar_arrive(&full_b[s]);
         }
-        // epilogue: this warp reads tensor-memory lanes 32 (warp % 4) .. + 31 of accumulator half dw / 4
+        // epilogue: a warp reads tensor-memory lanes 32 (warp % 4) .. + 31; the four warps of a lane quarter split the
+        // accumulator halves (BM = 256) and the columns between them
         if (!mbar_wait(acc_full, 0u)) report(a.err, kErrMmaWait);
         tc_fence_after();
-        const uint32_t half = dw >> 2, quarter = warp & 3u;
+        const uint32_t quarter = warp & 3u, grp = dw >> 2;  // grp 0..3
+        const uint32_t half = BM == 256 ? (grp & 1u) : 0u;
+        const uint32_t col0 = BM == 256 ? (grp >> 1) * 64u : grp * 32u, ncols = BM == 256 ? 64u : 32u;
         const int r = (int)(half * 128u + quarter * 32u + lane);
-        __half* zrow = a.z + op * a.z_op_stride + (size_t)(first + r) * a.N + nt * kBN;
+        __half* zrow = a.z + op * a.z_op_stride + (size_t)(first + r) * a.N + nt * kBN + col0;
 #pragma unroll 1
-        for (uint32_t c = 0; c < kBN / 32u; ++c) {
-            uint32_t v[32];
-            tmem_ld32(tmem + ((quarter * 32u) << 16) + half * 128u + c * 32u, v);
+        for (uint32_t c = 0; c < ncols; c += 16u) {
+            uint32_t v[16];
+            tmem_ld16(tmem + ((quarter * 32u) << 16) + half * 128u + col0 + c, v);
             if (r < rows) {
-                uint32_t packed[16];
+                uint32_t packed[8];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
+                for (int j = 0; j < 8; ++j) {
                     const __half2 h = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
                     packed[j] = *reinterpret_cast<const uint32_t*>(&h);
                 }
-                uint4* dst = reinterpret_cast<uint4*>(zrow + c * 32u);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                uint4* dst = reinterpret_cast<uint4*>(zrow + c);
+                dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
             }
         }
         tc_fence_before();
@@ -264,7 +340,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem, kTmemCols);
+        tmem_dealloc(tmem, T::kTmemCols);
     }
 }
 
@@ -277,7 +353,7 @@ __global__ void route_count_kernel(const uint32_t* inds, uint32_t slots, uint32_
 
 // one CTA: each expert's first sorted position (exclusive scan of the counts) into `cursor`, and the M-tile table
 __global__ void __launch_bounds__(1024) route_plan_kernel(const uint32_t* counts, uint32_t experts, uint32_t* cursor,
-                                                          int4* tiles, uint32_t max_tiles) {
+                                                          int4* tiles, uint32_t max_tiles, uint32_t bm) {
     __shared__ uint32_t s_pos[1024], s_tile[1024];
     const uint32_t tid = threadIdx.x;
     // experts are walked in chunks of 1024 with running bases
@@ -287,7 +363,7 @@ __global__ void __launch_bounds__(1024) route_plan_kernel(const uint32_t* counts
     for (uint32_t e0 = 0; e0 < experts; e0 += 1024u) {
         const uint32_t e = e0 + tid;
         const uint32_t c = e < experts ? counts[e] : 0u;
-        const uint32_t t = (c + kBM - 1u) / kBM;
+        const uint32_t t = (c + bm - 1u) / bm;
         s_pos[tid] = c;
         s_tile[tid] = t;
         __syncthreads();
@@ -302,7 +378,7 @@ __global__ void __launch_bounds__(1024) route_plan_kernel(const uint32_t* counts
         if (e < experts) {
             cursor[e] = pos0;
             for (uint32_t i = 0; i < t && tile0 + i < max_tiles; ++i)
-                tiles[tile0 + i] = make_int4((int)e, (int)(pos0 + i * kBM), (int)min(kBM, c - i * kBM), 0);
+                tiles[tile0 + i] = make_int4((int)e, (int)(pos0 + i * bm), (int)min(bm, c - i * bm), 0);
         }
         __syncthreads();
         if (tid == 1023u) {
@@ -346,22 +422,26 @@ __global__ void __launch_bounds__(256) prep_rows_kernel(const PrepArgs a) {
         e = min(a.inds[slot], a.experts - 1u);
     }
     const __half* suh = a.suh[op] + (size_t)e * a.K + blk * 128u;
-    float v[4];
+    float v[4], sc[4];
+    load_act4(a.x, a.x_dt, (size_t)row * a.K + blk * 128u + 4u * lane, v);
+    load_half4(suh + 4u * lane, sc);
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-        v[j] = round_half(load_act(a.x, a.x_dt, (size_t)row * a.K + blk * 128u + lane + 32u * j)) * __half2float(suh[lane + 32u * j]);
-    h128_warp(v, lane);
-    __half* dst = a.xp + ((size_t)op * a.positions + p) * a.K + blk * 128u;
+    for (int j = 0; j < 4; ++j) v[j] = round_half(v[j]) * sc[j];
+    h128_warp_v4(v, lane);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) dst[lane + 32u * j] = __float2half_rn(v[j] * kHadScale);
+    for (int j = 0; j < 4; ++j) v[j] *= kHadScale;
+    store_act4(a.xp, kF16, ((size_t)op * a.positions + p) * a.K + blk * 128u + 4u * lane, v);
 }
 
-__device__ __forceinline__ void finish4(float (&v)[4], const __half* svh, uint32_t lane) {
+// the output rotation of a 128-block whose elements 4 L .. 4 L + 3 lane L holds (svh_blk: the block's first scale)
+__device__ __forceinline__ void finish4(float (&v)[4], const __half* svh_blk, uint32_t lane) {
+    float sc[4];
+    load_half4(svh_blk + 4u * lane, sc);
 #pragma unroll
     for (int j = 0; j < 4; ++j) v[j] = round_half(v[j]);
-    h128_warp(v, lane);
+    h128_warp_v4(v, lane);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = round_half(v[j] * kHadScale * __half2float(svh[lane + 32u * j]));
+    for (int j = 0; j < 4; ++j) v[j] = round_half(v[j] * kHadScale * sc[j]);
 }
 
 // grid (out / 128, ceil(rows / 8)): the plain finish of a dense linear (format.finishOutput, format.zig:370-380)
@@ -377,11 +457,10 @@ __global__ void __launch_bounds__(256) finish_rows_kernel(const FinishArgs a) {
     const uint32_t row = blockIdx.y * 8u + warp, blk = blockIdx.x;
     if (row >= a.rows) return;
     float v[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = __half2float(a.z[(size_t)row * a.out + blk * 128u + lane + 32u * j]);
+    const size_t o = (size_t)row * a.out + blk * 128u + 4u * lane;
+    load_half4(a.z + o, v);
     finish4(v, a.svh + blk * 128u, lane);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) store_act(a.y, a.y_dt, (size_t)row * a.out + blk * 128u + lane + 32u * j, v[j]);
+    store_act4(a.y, a.y_dt, o, v);
 }
 
 __device__ __forceinline__ float swiglu_f32(float g, float u, float limit, int clamp_at) {
@@ -409,22 +488,20 @@ __global__ void __launch_bounds__(256) mid_kernel(const MidArgs a) {
     const uint32_t p = blockIdx.y * 8u + warp, blk = blockIdx.x;
     if (p >= a.positions) return;
     const uint32_t e = min(a.inds[a.order[p]], a.experts - 1u);
-    const size_t eo = (size_t)e * a.inter + blk * 128u, zo = (size_t)p * a.inter + blk * 128u;
-    float g[4], u[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        g[j] = __half2float(a.z[zo + lane + 32u * j]);
-        u[j] = __half2float(a.z[(size_t)a.positions * a.inter + zo + lane + 32u * j]);
-    }
+    const size_t eo = (size_t)e * a.inter + blk * 128u, zo = (size_t)p * a.inter + blk * 128u + 4u * lane;
+    float g[4], u[4], sd[4];
+    load_half4(a.z + zo, g);
+    load_half4(a.z + (size_t)a.positions * a.inter + zo, u);
+    load_half4(a.down_suh + eo + 4u * lane, sd);
     finish4(g, a.gate_svh + eo, lane);
     finish4(u, a.up_svh + eo, lane);
     float d[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-        d[j] = round_half(swiglu_f32(g[j], u[j], a.limit, a.clamp_at)) * __half2float(a.down_suh[eo + lane + 32u * j]);
-    h128_warp(d, lane);
+    for (int j = 0; j < 4; ++j) d[j] = round_half(swiglu_f32(g[j], u[j], a.limit, a.clamp_at)) * sd[j];
+    h128_warp_v4(d, lane);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) a.hd[zo + lane + 32u * j] = __float2half_rn(d[j] * kHadScale);
+    for (int j = 0; j < 4; ++j) d[j] *= kHadScale;
+    store_act4(a.hd, kF16, zo, d);
 }
 
 // grid (hidden / 128, ceil(rows / 8)): per row, each slot's down finish (through inv) and the score-weighted sum in slot
@@ -450,22 +527,21 @@ __global__ void __launch_bounds__(256) moe_fin_kernel(const FinArgs a) {
         const uint32_t p = a.inv[slot], e = min(a.inds[slot], a.experts - 1u);
         const float w = load_act(a.scores, a.score_dt, slot);
         float v[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] = __half2float(a.zd[(size_t)p * a.hidden + blk * 128u + lane + 32u * j]);
+        load_half4(a.zd + (size_t)p * a.hidden + blk * 128u + 4u * lane, v);
         finish4(v, a.down_svh + (size_t)e * a.hidden + blk * 128u, lane);
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[j] = __fadd_rn(acc[j], __fmul_rn(w, v[j]));
     }
+    const size_t o = (size_t)row * a.hidden + blk * 128u + 4u * lane;
+    if (a.shared) {
+        float t[4], sh[4];
+        store_act4(a.y, a.y_dt, o, acc);   // the routed output's rounding point
+        load_act4(a.y, a.y_dt, o, t);
+        load_act4(a.shared, a.y_dt, o, sh);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const size_t o = (size_t)row * a.hidden + blk * 128u + lane + 32u * j;
-        float r = acc[j];
-        if (a.shared) {
-            store_act(a.y, a.y_dt, o, r);
-            r = __fadd_rn(load_act(a.y, a.y_dt, o), load_act(a.shared, a.y_dt, o));
-        }
-        store_act(a.y, a.y_dt, o, r);
+        for (int j = 0; j < 4; ++j) acc[j] = __fadd_rn(t[j], sh[j]);
     }
+    store_act4(a.y, a.y_dt, o, acc);
 }
 
 // ---- host side -----------------------------------------------------------------------------------------------------
@@ -486,38 +562,45 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-// f16 [rows, K] row-major, boxes of kBK x kBM, 128-byte swizzle, rows past the end read as zero
-bool make_a_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K) {
+// f16 [rows, K] row-major, boxes of kBK x bm, 128-byte swizzle, rows past the end read as zero
+bool make_a_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t bm) {
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return false;
     const cuuint64_t dims[2] = {K, rows};
     const cuuint64_t strides[1] = {K * 2u};
-    const cuuint32_t box[2] = {kBK, kBM};
+    const cuuint32_t box[2] = {kBK, bm};
     const cuuint32_t estr[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int CB>
+template <int CB, int BM>
 cudaError_t launch_gemm_cb(const CUtensorMap& map, const GemmArgs& g, uint32_t max_tiles, cudaStream_t stream) {
     void (*fn)(const CUtensorMap, const GemmArgs) = nullptr;
     switch (g.n) {
 #define T3_CASE(NN) \
-    case NN: fn = gemm_decode_kernel<NN, CB>; break;
+    case NN: fn = gemm_decode_kernel<NN, CB, BM>; break;
         T3_CASE(16) T3_CASE(32) T3_CASE(48) T3_CASE(64) T3_CASE(80) T3_CASE(96) T3_CASE(112) T3_CASE(128)
 #undef T3_CASE
-        default: fn = gemm_decode_kernel<0, CB>; break;
+        default: fn = gemm_decode_kernel<0, CB, BM>; break;
     }
+    const uint32_t smem_bytes = Tile<BM>::smem(g.n);
     cudaError_t rc = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)kGemmSmem);
+                                          (int)Tile<BM>::smem(128u));
     if (rc != cudaSuccess) return rc;
-    fn<<<dim3(g.ops * g.N / kBN, max_tiles, 1), kGemmThreads, kGemmSmem, stream>>>(map, g);
+    fn<<<dim3(g.ops * g.N / kBN, max_tiles, 1), kGemmThreads, smem_bytes, stream>>>(map, g);
     return cudaGetLastError();
 }
 
-cudaError_t launch_gemm(const CUtensorMap& map, const GemmArgs& g, uint32_t max_tiles, int codebook, cudaStream_t stream) {
-    return codebook == kMcg ? launch_gemm_cb<kMcg>(map, g, max_tiles, stream) : launch_gemm_cb<kMul1>(map, g, max_tiles, stream);
+// bm: 256 (dense) or 128 (routed)
+cudaError_t launch_gemm(const CUtensorMap& map, const GemmArgs& g, uint32_t max_tiles, uint32_t bm, int codebook,
+                        cudaStream_t stream) {
+    if (bm == 256u)
+        return codebook == kMcg ? launch_gemm_cb<kMcg, 256>(map, g, max_tiles, stream)
+                                : launch_gemm_cb<kMul1, 256>(map, g, max_tiles, stream);
+    return codebook == kMcg ? launch_gemm_cb<kMcg, 128>(map, g, max_tiles, stream)
+                            : launch_gemm_cb<kMul1, 128>(map, g, max_tiles, stream);
 }
 
 size_t up256(size_t v) { return (v + 255u) & ~(size_t)255u; }
@@ -545,7 +628,7 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
     pa.xp = xp;
     prep_rows_kernel<<<dim3(p.in / 128u, (p.rows + 7u) / 8u, 1), 256, 0, stream>>>(pa);
     CUtensorMap map;
-    if (!make_a_map(&map, xp, p.rows, p.in)) return cudaErrorNotSupported;
+    if (!make_a_map(&map, xp, p.rows, p.in, 256u)) return cudaErrorNotSupported;
     GemmArgs g = {};
     g.trellis[0] = g.trellis[1] = p.trellis;
     g.K = p.in;
@@ -556,7 +639,7 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
     g.dense_rows = p.rows;
     g.z = z;
     g.err = p.err;
-    cudaError_t rc = launch_gemm(map, g, (p.rows + kBM - 1u) / kBM, codebook, stream);
+    cudaError_t rc = launch_gemm(map, g, (p.rows + 255u) / 256u, 256u, codebook, stream);
     if (rc != cudaSuccess) return rc;
     FinishArgs f = {z, static_cast<const __half*>(p.svh), p.y, p.x_dt, p.rows, p.out};
     finish_rows_kernel<<<dim3(p.out / 128u, (p.rows + 7u) / 8u, 1), 256, 0, stream>>>(f);
@@ -567,6 +650,7 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
 // ---- routed experts, more than 32 rows --------------------------------------------------------------------------------
 
 namespace {
+constexpr uint32_t kMoeBM = 128;  // routed experts' tile height
 struct MoeWs {
     uint32_t *counts, *cursor, *order, *inv;
     int4* tiles;
@@ -582,7 +666,7 @@ MoeWs carve_moe(uint8_t* base, size_t slots, uint32_t experts, uint32_t hidden, 
         off += up256(bytes);
         return p;
     };
-    w.max_tiles = (uint32_t)((slots + kBM - 1u) / kBM) + experts;
+    w.max_tiles = (uint32_t)((slots + kMoeBM - 1u) / kMoeBM) + experts;
     w.counts = reinterpret_cast<uint32_t*>(take((size_t)experts * 4u));
     w.cursor = reinterpret_cast<uint32_t*>(take((size_t)experts * 4u));
     w.order = reinterpret_cast<uint32_t*>(take(slots * 4u));
@@ -609,7 +693,7 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
     cudaError_t rc = cudaMemsetAsync(w.counts, 0, (size_t)a.experts * 4u, stream);
     if (rc != cudaSuccess) return rc;
     route_count_kernel<<<(S + 255u) / 256u, 256, 0, stream>>>(inds, S, a.experts, w.counts);
-    route_plan_kernel<<<1, 1024, 0, stream>>>(w.counts, a.experts, w.cursor, w.tiles, w.max_tiles);
+    route_plan_kernel<<<1, 1024, 0, stream>>>(w.counts, a.experts, w.cursor, w.tiles, w.max_tiles, kMoeBM);
     route_scatter_kernel<<<(S + 255u) / 256u, 256, 0, stream>>>(inds, S, a.experts, w.cursor, w.order, w.inv);
 
     PrepArgs pa = {};
@@ -628,7 +712,8 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
 
     const uint32_t tile_bytes = 2u * a.n;
     CUtensorMap map_gu, map_d;
-    if (!make_a_map(&map_gu, w.xp, 2u * slots, H) || !make_a_map(&map_d, w.hd, slots, I)) return cudaErrorNotSupported;
+    if (!make_a_map(&map_gu, w.xp, 2u * slots, H, kMoeBM) || !make_a_map(&map_d, w.hd, slots, I, kMoeBM))
+        return cudaErrorNotSupported;
     GemmArgs g = {};
     g.trellis[0] = a.gate_t;
     g.trellis[1] = a.up_t;
@@ -643,7 +728,7 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
     g.z = w.zgu;
     g.z_op_stride = slots * I;
     g.err = a.err;
-    rc = launch_gemm(map_gu, g, w.max_tiles, codebook, stream);
+    rc = launch_gemm(map_gu, g, w.max_tiles, kMoeBM, codebook, stream);
     if (rc != cudaSuccess) return rc;
 
     MidArgs m = {w.zgu, static_cast<const __half*>(a.gate_svh), static_cast<const __half*>(a.up_svh),
@@ -661,7 +746,7 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
     d.tiles = w.tiles;
     d.z = w.zd;
     d.err = a.err;
-    rc = launch_gemm(map_d, d, w.max_tiles, codebook, stream);
+    rc = launch_gemm(map_d, d, w.max_tiles, kMoeBM, codebook, stream);
     if (rc != cudaSuccess) return rc;
 
     FinArgs f = {w.zd, static_cast<const __half*>(a.down_svh), w.inv, inds, a.scores, a.score_dt, a.shared, a.y, a.x_dt,
