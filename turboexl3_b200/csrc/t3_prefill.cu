@@ -180,12 +180,12 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
     if (tid == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
             mbar_init(&full_a[s], 1u);
-            mbar_init(&full_b[s], kDecodeWarps);
+            mbar_init(&full_b[s], kDecodeWarps / 2u);
             mbar_init(&empty[s], 1u);
         }
         for (uint32_t s = 0; s < kCodeStages; ++s) {
             mbar_init(&full_c[s], 1u);
-            mbar_init(&empty_c[s], kDecodeWarps);
+            mbar_init(&empty_c[s], kDecodeWarps / 2u);
         }
         mbar_init(acc_full, 1u);
         mbar_init_fence();
@@ -254,57 +254,54 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
             umma_commit(acc_full);
         }
     } else {
-        // decode warp dw: output tile column dw % 8 of the CTA's 128, input tile rows 2 (dw / 8) and 2 (dw / 8) + 1 of a stage
-        const uint32_t dw = warp - 2u, tcol = dw & 7u, tk0 = (dw >> 3) * 2u;
+        // Decode warp dw: output tile column dw % 8 of the CTA's 128, all four input tile rows of every second stage
+        // (stages ks = dw / 8, dw / 8 + 2, ...). The two groups of eight warps work on consecutive stages at the same time,
+        // so a stage's decode latency (word loads, four decodes, the stores and their proxy fence) is paid once every two
+        // stages instead of once a stage.
+        const uint32_t dw = warp - 2u, tcol = dw & 7u, grp = dw >> 3;
         constexpr int NP = NN > 0 ? NN : 16;
         constexpr uint32_t kRaw = raw_words(NP);
         LanePlan<NP> plan;
         plan.init(lane);
-        // byte offsets of the lane's words of its two tiles inside a code stage
-        uint32_t woff[2][kRaw];
+        // byte offsets of the lane's words of tile row 0 inside a code stage (row i: + 8 i tile_bytes)
+        uint32_t woff[kRaw];
 #pragma unroll
-        for (uint32_t i = 0; i < 2u; ++i)
-#pragma unroll
-            for (uint32_t w = 0; w < kRaw; ++w) woff[i][w] = ((tk0 + i) * 8u + tcol) * tile_bytes + plan.idx[w] * 4u;
+        for (uint32_t w = 0; w < kRaw; ++w) woff[w] = tcol * tile_bytes + plan.idx[w] * 4u;
         const uint32_t g = lane >> 2, q = lane & 3u;
-        // where the lane's eight half2 words of its two tiles go in a B stage:
-        // B[n][k] at n * 128 + ((k / 8) ^ (n % 8)) * 16 + (k % 8) * 2; k = 16 tk + 2 q (+8), n = 16 tcol + g (+8)
+        // where the lane's half2 words go in a B stage: B[n][k] at n * 128 + ((k / 8) ^ (n % 8)) * 16 + (k % 8) * 2 with
+        // k = 16 tk + 2 q (+8), n = 16 tcol + g (+8)
         const uint32_t row0 = (tcol * 16u + g) * 128u + 4u * q;
-        uint32_t boff[2][2];
-#pragma unroll
-        for (uint32_t i = 0; i < 2u; ++i) {
-            boff[i][0] = row0 + ((2u * (tk0 + i)) ^ g) * 16u;
-            boff[i][1] = row0 + ((2u * (tk0 + i) + 1u) ^ g) * 16u;
-        }
-        for (uint32_t ks = 0; ks < ksteps; ++ks) {
+        for (uint32_t ks = grp; ks < ksteps; ks += 2u) {
             const uint32_t s = ks % kStages, u = ks / kStages, cs = ks % kCodeStages, uc = ks / kCodeStages;
             if (!mbar_wait(&full_c[cs], uc & 1u)) report(a.err, kErrFullWait);
             const uint8_t* cst = codes + cs * code_stage_bytes;
-            uint32_t b[2][4];
+            uint32_t b[4][4];
             if (NN > 0) {
-                uint32_t raw[2][kRaw];
+                uint32_t raw[4][kRaw];
 #pragma unroll
-                for (uint32_t i = 0; i < 2u; ++i)
+                for (uint32_t i = 0; i < 4u; ++i)
 #pragma unroll
-                    for (uint32_t w = 0; w < kRaw; ++w) raw[i][w] = *reinterpret_cast<const uint32_t*>(cst + woff[i][w]);
+                    for (uint32_t w = 0; w < kRaw; ++w)
+                        raw[i][w] = *reinterpret_cast<const uint32_t*>(cst + woff[w] + i * 8u * tile_bytes);
 #pragma unroll
-                for (uint32_t i = 0; i < 2u; ++i) decode_raw<NP, CB>(raw[i], plan, a.mask, b[i]);
+                for (uint32_t i = 0; i < 4u; ++i) decode_raw<NP, CB>(raw[i], plan, a.mask, b[i]);
             } else {
 #pragma unroll
-                for (uint32_t i = 0; i < 2u; ++i)
-                    decode_lane_any<CB>(reinterpret_cast<const uint32_t*>(cst + ((tk0 + i) * 8u + tcol) * tile_bytes), a.n, lane,
-                                        a.mask, b[i]);
+                for (uint32_t i = 0; i < 4u; ++i)
+                    decode_lane_any<CB>(reinterpret_cast<const uint32_t*>(cst + (i * 8u + tcol) * tile_bytes), a.n, lane, a.mask,
+                                        b[i]);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_c[cs]);  // the words are in registers: the code stage may be refilled
             if (u > 0 && !mbar_wait(&empty[s], (u - 1u) & 1u)) report(a.err, kErrEmptyWait);
-            uint8_t* bst = smem + s * kStageBytes + kABytes;
+            uint8_t* bst = smem + s * kStageBytes + kABytes + row0;
 #pragma unroll
-            for (uint32_t i = 0; i < 2u; ++i) {
-                *reinterpret_cast<uint32_t*>(bst + boff[i][0]) = b[i][0];
-                *reinterpret_cast<uint32_t*>(bst + boff[i][1]) = b[i][1];
-                *reinterpret_cast<uint32_t*>(bst + boff[i][0] + 8u * 128u) = b[i][2];
-                *reinterpret_cast<uint32_t*>(bst + boff[i][1] + 8u * 128u) = b[i][3];
+            for (uint32_t i = 0; i < 4u; ++i) {
+                const uint32_t c0 = ((2u * i) ^ g) * 16u, c1 = ((2u * i + 1u) ^ g) * 16u;
+                *reinterpret_cast<uint32_t*>(bst + c0) = b[i][0];
+                *reinterpret_cast<uint32_t*>(bst + c1) = b[i][1];
+                *reinterpret_cast<uint32_t*>(bst + c0 + 8u * 128u) = b[i][2];
+                *reinterpret_cast<uint32_t*>(bst + c1 + 8u * 128u) = b[i][3];
             }
             proxy_fence();
             __syncwarp();
@@ -314,9 +311,9 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
         // accumulator halves (BM = 256) and the columns between them
         if (!mbar_wait(acc_full, 0u)) report(a.err, kErrMmaWait);
         tc_fence_after();
-        const uint32_t quarter = warp & 3u, grp = dw >> 2;  // grp 0..3
-        const uint32_t half = BM == 256 ? (grp & 1u) : 0u;
-        const uint32_t col0 = BM == 256 ? (grp >> 1) * 64u : grp * 32u, ncols = BM == 256 ? 64u : 32u;
+        const uint32_t quarter = warp & 3u, egrp = dw >> 2;  // egrp 0..3
+        const uint32_t half = BM == 256 ? (egrp & 1u) : 0u;
+        const uint32_t col0 = BM == 256 ? (egrp >> 1) * 64u : egrp * 32u, ncols = BM == 256 ? 64u : 32u;
         const int r = (int)(half * 128u + quarter * 32u + lane);
         __half* zrow = a.z + op * a.z_op_stride + (size_t)(first + r) * a.N + nt * kBN + col0;
 #pragma unroll 1
