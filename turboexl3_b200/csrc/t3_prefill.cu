@@ -180,12 +180,12 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
     if (tid == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
             mbar_init(&full_a[s], 1u);
-            mbar_init(&full_b[s], kDecodeWarps / 2u);
+            mbar_init(&full_b[s], kDecodeWarps);
             mbar_init(&empty[s], 1u);
         }
         for (uint32_t s = 0; s < kCodeStages; ++s) {
             mbar_init(&full_c[s], 1u);
-            mbar_init(&empty_c[s], kDecodeWarps / 2u);
+            mbar_init(&empty_c[s], kDecodeWarps);
         }
         mbar_init(acc_full, 1u);
         mbar_init_fence();
@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
             // One thread feeds both rings and never blocks on either: it polls the two "slot free" barriers in turn, so the
             // code stream (which runs ahead of the decode) and the activation stream (which follows the MMAs) cannot starve
             // each other. Codes: a stage's four tile rows of the CTA's 8 tiles, 16 n contiguous bytes each.
-            const uint8_t* src = a.trellis[op] + (size_t)e * a.expert_bytes + (size_t)(nt * 8u) * tile_bytes;
+            const uint8_t* src = (op ? a.trellis[1] : a.trellis[0]) + (size_t)e * a.expert_bytes + (size_t)(nt * 8u) * tile_bytes;
             const size_t tk_stride = (size_t)out_tiles * tile_bytes;
             const uint32_t row_bytes = 8u * tile_bytes;
             uint32_t ka = 0, kc = 0, idle = 0;
@@ -254,54 +254,57 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
             umma_commit(acc_full);
         }
     } else {
-        // Decode warp dw: output tile column dw % 8 of the CTA's 128, all four input tile rows of every second stage
-        // (stages ks = dw / 8, dw / 8 + 2, ...). The two groups of eight warps work on consecutive stages at the same time,
-        // so a stage's decode latency (word loads, four decodes, the stores and their proxy fence) is paid once every two
-        // stages instead of once a stage.
-        const uint32_t dw = warp - 2u, tcol = dw & 7u, grp = dw >> 3;
+        // decode warp dw: output tile column dw % 8 of the CTA's 128, input tile rows 2 (dw / 8) and 2 (dw / 8) + 1 of a stage
+        const uint32_t dw = warp - 2u, tcol = dw & 7u, tk0 = (dw >> 3) * 2u;
         constexpr int NP = NN > 0 ? NN : 16;
         constexpr uint32_t kRaw = raw_words(NP);
         LanePlan<NP> plan;
         plan.init(lane);
-        // byte offsets of the lane's words of tile row 0 inside a code stage (row i: + 8 i tile_bytes)
-        uint32_t woff[kRaw];
+        // byte offsets of the lane's words of its two tiles inside a code stage
+        uint32_t woff[2][kRaw];
 #pragma unroll
-        for (uint32_t w = 0; w < kRaw; ++w) woff[w] = tcol * tile_bytes + plan.idx[w] * 4u;
+        for (uint32_t i = 0; i < 2u; ++i)
+#pragma unroll
+            for (uint32_t w = 0; w < kRaw; ++w) woff[i][w] = ((tk0 + i) * 8u + tcol) * tile_bytes + plan.idx[w] * 4u;
         const uint32_t g = lane >> 2, q = lane & 3u;
-        // where the lane's half2 words go in a B stage: B[n][k] at n * 128 + ((k / 8) ^ (n % 8)) * 16 + (k % 8) * 2 with
-        // k = 16 tk + 2 q (+8), n = 16 tcol + g (+8)
+        // where the lane's eight half2 words of its two tiles go in a B stage:
+        // B[n][k] at n * 128 + ((k / 8) ^ (n % 8)) * 16 + (k % 8) * 2; k = 16 tk + 2 q (+8), n = 16 tcol + g (+8)
         const uint32_t row0 = (tcol * 16u + g) * 128u + 4u * q;
-        for (uint32_t ks = grp; ks < ksteps; ks += 2u) {
+        uint32_t boff[2][2];
+#pragma unroll
+        for (uint32_t i = 0; i < 2u; ++i) {
+            boff[i][0] = row0 + ((2u * (tk0 + i)) ^ g) * 16u;
+            boff[i][1] = row0 + ((2u * (tk0 + i) + 1u) ^ g) * 16u;
+        }
+        for (uint32_t ks = 0; ks < ksteps; ++ks) {
             const uint32_t s = ks % kStages, u = ks / kStages, cs = ks % kCodeStages, uc = ks / kCodeStages;
             if (!mbar_wait(&full_c[cs], uc & 1u)) report(a.err, kErrFullWait);
             const uint8_t* cst = codes + cs * code_stage_bytes;
-            uint32_t b[4][4];
+            uint32_t b[2][4];
             if (NN > 0) {
-                uint32_t raw[4][kRaw];
+                uint32_t raw[2][kRaw];
 #pragma unroll
-                for (uint32_t i = 0; i < 4u; ++i)
+                for (uint32_t i = 0; i < 2u; ++i)
 #pragma unroll
-                    for (uint32_t w = 0; w < kRaw; ++w)
-                        raw[i][w] = *reinterpret_cast<const uint32_t*>(cst + woff[w] + i * 8u * tile_bytes);
+                    for (uint32_t w = 0; w < kRaw; ++w) raw[i][w] = *reinterpret_cast<const uint32_t*>(cst + woff[i][w]);
 #pragma unroll
-                for (uint32_t i = 0; i < 4u; ++i) decode_raw<NP, CB>(raw[i], plan, a.mask, b[i]);
+                for (uint32_t i = 0; i < 2u; ++i) decode_raw<NP, CB>(raw[i], plan, a.mask, b[i]);
             } else {
 #pragma unroll
-                for (uint32_t i = 0; i < 4u; ++i)
-                    decode_lane_any<CB>(reinterpret_cast<const uint32_t*>(cst + (i * 8u + tcol) * tile_bytes), a.n, lane, a.mask,
-                                        b[i]);
+                for (uint32_t i = 0; i < 2u; ++i)
+                    decode_lane_any<CB>(reinterpret_cast<const uint32_t*>(cst + ((tk0 + i) * 8u + tcol) * tile_bytes), a.n, lane,
+                                        a.mask, b[i]);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_c[cs]);  // the words are in registers: the code stage may be refilled
             if (u > 0 && !mbar_wait(&empty[s], (u - 1u) & 1u)) report(a.err, kErrEmptyWait);
-            uint8_t* bst = smem + s * kStageBytes + kABytes + row0;
+            uint8_t* bst = smem + s * kStageBytes + kABytes;
 #pragma unroll
-            for (uint32_t i = 0; i < 4u; ++i) {
-                const uint32_t c0 = ((2u * i) ^ g) * 16u, c1 = ((2u * i + 1u) ^ g) * 16u;
-                *reinterpret_cast<uint32_t*>(bst + c0) = b[i][0];
-                *reinterpret_cast<uint32_t*>(bst + c1) = b[i][1];
-                *reinterpret_cast<uint32_t*>(bst + c0 + 8u * 128u) = b[i][2];
-                *reinterpret_cast<uint32_t*>(bst + c1 + 8u * 128u) = b[i][3];
+            for (uint32_t i = 0; i < 2u; ++i) {
+                *reinterpret_cast<uint32_t*>(bst + boff[i][0]) = b[i][0];
+                *reinterpret_cast<uint32_t*>(bst + boff[i][1]) = b[i][1];
+                *reinterpret_cast<uint32_t*>(bst + boff[i][0] + 8u * 128u) = b[i][2];
+                *reinterpret_cast<uint32_t*>(bst + boff[i][1] + 8u * 128u) = b[i][3];
             }
             proxy_fence();
             __syncwarp();
@@ -311,9 +314,9 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
         // accumulator halves (BM = 256) and the columns between them
         if (!mbar_wait(acc_full, 0u)) report(a.err, kErrMmaWait);
         tc_fence_after();
-        const uint32_t quarter = warp & 3u, egrp = dw >> 2;  // egrp 0..3
-        const uint32_t half = BM == 256 ? (egrp & 1u) : 0u;
-        const uint32_t col0 = BM == 256 ? (egrp >> 1) * 64u : egrp * 32u, ncols = BM == 256 ? 64u : 32u;
+        const uint32_t quarter = warp & 3u, grp = dw >> 2;  // grp 0..3
+        const uint32_t half = BM == 256 ? (grp & 1u) : 0u;
+        const uint32_t col0 = BM == 256 ? (grp >> 1) * 64u : grp * 32u, ncols = BM == 256 ? 64u : 32u;
         const int r = (int)(half * 128u + quarter * 32u + lane);
         __half* zrow = a.z + op * a.z_op_stride + (size_t)(first + r) * a.N + nt * kBN + col0;
 #pragma unroll 1
@@ -397,51 +400,180 @@ __global__ void route_scatter_kernel(const uint32_t* inds, uint32_t slots, uint3
 }
 
 // ---- prepare / mid / finish ------------------------------------------------------------------------------------------
+//
+// The 128-point Hadamards of these kernels run on the tensor cores. The sign of entry (i, j) of H128 is the parity of
+// popcount(i & j), which splits over the bit fields of i = 16 i8 + i16, so H128 = H8 (x) H16 and a block viewed as an
+// 8 x 16 matrix X becomes H8 . X . H16: X . H16 is m16n8k16 steps against a constant +-1 fragment, H8 a three-level
+// butterfly over values one thread already holds. A warp works on EIGHT positions at a time, one 128-block each: quad g
+// (lanes 4g .. 4g + 3) owns position g, and lane q of the quad holds, for every i8, the four elements 16 i8 + 4q .. + 3:
+// one 8-byte (f16) or 16-byte (f32) access per i8 on the way in and on the way out. The butterfly on a warp costs twenty
+// shuffles per block, and the shuffle unit (one warp instruction per SM per cycle) bounded these kernels; this form has none.
+// f32 accumulation of +-1 products is exact per term, so the result differs from the butterfly (and from the oracle's
+// dense sum) only in summation order, as before.
 
-// grid (K / 128, ceil(P / 8), ops), 256 threads: warp = one (position, 128-block). Dense: position = row, suh shared.
-// Routed: position p -> slot order[p] -> row slot / topk, suh of the slot's expert; op 1 uses the up projection's suh.
+struct HadB {
+    uint32_t b[2][2];  // the +-1 H16 fragment of each 8-column half (t): {k 0-7 part, k 8-15 part}
+};
+
+// Matrix index <-> element maps (both free to choose): A/B index k of thread q covers elements 4q, 4q+1 (k = 2q, 2q+1) and
+// 4q+2, 4q+3 (k = 2q+8, 2q+9); output column n = 2q+b of half t is element 4q + 2t + b. So a thread's inputs and outputs
+// are the same four consecutive elements.
+__device__ __forceinline__ HadB had_b(uint32_t lane) {
+    const uint32_t g = lane >> 2, q = lane & 3u;
+    HadB h;
+#pragma unroll
+    for (uint32_t t = 0; t < 2u; ++t) {
+        const uint32_t en = 4u * (g >> 1) + 2u * t + (g & 1u);
+        uint32_t s[4];
+#pragma unroll
+        for (uint32_t b = 0; b < 4u; ++b) s[b] = (__popc((4u * q + b) & en) & 1) ? 0xBC00u : 0x3C00u;
+        h.b[t][0] = s[0] | (s[1] << 16);
+        h.b[t][1] = s[2] | (s[3] << 16);
+    }
+    return h;
+}
+
+// out[i8][e] = sum over the block of sign * value, for the position this quad owns. a[i8] = the four f16 values
+// {16 i8 + 4q .. + 3} as two packed pairs; a second set (the f16 remainders of values that are not f16 themselves) is
+// accumulated into the same sums when `use_lo` is set.
+__device__ __forceinline__ void h128_mma(const uint32_t (&a)[8][2], const uint32_t (&lo)[8][2], bool use_lo,
+                                         const HadB& hb, float (&out)[8][4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            mma16816(c, a[2 * j][0], a[2 * j + 1][0], a[2 * j][1], a[2 * j + 1][1], hb.b[t][0], hb.b[t][1]);
+            if (use_lo) mma16816(c, lo[2 * j][0], lo[2 * j + 1][0], lo[2 * j][1], lo[2 * j + 1][1], hb.b[t][0], hb.b[t][1]);
+            out[2 * j][2 * t] = c[0], out[2 * j][2 * t + 1] = c[1];
+            out[2 * j + 1][2 * t] = c[2], out[2 * j + 1][2 * t + 1] = c[3];
+        }
+#pragma unroll
+    for (int bit = 1; bit < 8; bit <<= 1)
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (!(i & bit))
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float lo_v = out[i][e], hi_v = out[i | bit][e];
+                    out[i][e] = lo_v + hi_v;
+                    out[i | bit][e] = lo_v - hi_v;
+                }
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// v (f32 values, not necessarily f16) as an f16 part and the f16 of what is left; returns nonzero when any remainder is
+__device__ __forceinline__ uint32_t split4(const float (&v)[4], uint32_t (&hi)[2], uint32_t (&lo)[2]) {
+    float r[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) r[j] = v[j] - round_half(v[j]);
+    hi[0] = pack_half2(v[0], v[1]), hi[1] = pack_half2(v[2], v[3]);
+    lo[0] = pack_half2(r[0], r[1]), lo[1] = pack_half2(r[2], r[3]);
+    return (lo[0] | lo[1]) & 0x7FFF7FFFu;
+}
+
+// H128 of the block whose values are `v` (v[i8] = elements 16 i8 + 4q .. + 3), any f32 values
+__device__ __forceinline__ void h128_split(const float (&v)[8][4], const HadB& hb, float (&out)[8][4]) {
+    uint32_t hi[8][2], lo[8][2], rest = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) rest |= split4(v[i], hi[i], lo[i]);
+    h128_mma(hi, lo, __any_sync(0xFFFFFFFFu, rest != 0u) != 0, hb, out);
+}
+
+// The output rotation of one block (format.finishOutput, format.zig:370-380): z and sv point at this lane's first
+// element (block start + 4q); out = f16(H128(z) / sqrt(128) * sv).
+__device__ __forceinline__ void finish_block_mma(const __half* z, const __half* sv, const HadB& hb, float (&out)[8][4]) {
+    uint32_t a[8][2];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint2 u = *reinterpret_cast<const uint2*>(z + 16 * i);
+        a[i][0] = u.x, a[i][1] = u.y;
+    }
+    h128_mma(a, a, false, hb, out);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float sc[4];
+        load_half4(sv + 16 * i, sc);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) out[i][e] = round_half(out[i][e] * kHadScale * sc[e]);
+    }
+}
+
+constexpr uint32_t kRowsPerCta = 64;  // 8 warps x 8 positions
+
+// how many CTAs share a position group's 128-blocks, so that small calls still fill the GPU
+uint32_t spread(uint32_t positions, uint32_t nblk) {
+    const uint32_t groups = (positions + kRowsPerCta - 1u) / kRowsPerCta;
+    const uint32_t want = (1184u + groups - 1u) / groups;
+    return want < 1u ? 1u : (want > nblk ? nblk : want);
+}
+
+// this lane's position in a warp's group of eight; returns false when the whole warp is past the end
+__device__ __forceinline__ bool my_position(uint32_t count, uint32_t lane, uint32_t& p, bool& live) {
+    const uint32_t first = (blockIdx.y * 8u + (threadIdx.x >> 5)) * 8u;
+    if (first >= count) return false;
+    const uint32_t mine = first + (lane >> 2);
+    live = mine < count;
+    p = live ? mine : count - 1u;
+    return true;
+}
+
+// grid (spread, ceil(P / 64)), 256 threads. Dense: position = row, suh shared. Routed: position p -> slot order[p] -> row
+// slot / topk, suh of the slot's expert; the second op (up) reuses the row with its own suh.
 struct PrepArgs {
     const void* x;
     int x_dt;
     const __half* suh[2];
-    uint32_t K, positions, topk, experts;
+    uint32_t K, positions, topk, experts, ops;
     const uint32_t *order, *inds;  // null for a dense linear
     __half* xp;                    // [ops][positions][K]
 };
 __global__ void __launch_bounds__(256) prep_rows_kernel(const PrepArgs a) {
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const uint32_t p = blockIdx.y * 8u + warp, blk = blockIdx.x, op = blockIdx.z;
-    if (p >= a.positions) return;
+    const uint32_t lane = threadIdx.x & 31u, q = lane & 3u;
+    uint32_t p;
+    bool live;
+    if (!my_position(a.positions, lane, p, live)) return;
     uint32_t row = p, e = 0;
     if (a.order) {
         const uint32_t slot = a.order[p];
         row = slot / a.topk;
         e = min(a.inds[slot], a.experts - 1u);
     }
-    const __half* suh = a.suh[op] + (size_t)e * a.K + blk * 128u;
-    float v[4], sc[4];
-    load_act4(a.x, a.x_dt, (size_t)row * a.K + blk * 128u + 4u * lane, v);
-    load_half4(suh + 4u * lane, sc);
+    const HadB hb = had_b(lane);
+    for (uint32_t blk = blockIdx.x; blk < (a.K >> 7); blk += gridDim.x) {
+        const uint32_t col = blk * 128u + 4u * q;
+        float xv[8][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = round_half(v[j]) * sc[j];
-    h128_warp_v4(v, lane);
+        for (int i = 0; i < 8; ++i) load_act4(a.x, a.x_dt, (size_t)row * a.K + col + 16u * i, xv[i]);
+        for (uint32_t op = 0; op < a.ops; ++op) {
+            const __half* suh = (op ? a.suh[1] : a.suh[0]) + (size_t)e * a.K + col;
+            float v[8][4], out[8][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] *= kHadScale;
-    store_act4(a.xp, kF16, ((size_t)op * a.positions + p) * a.K + blk * 128u + 4u * lane, v);
+            for (int i = 0; i < 8; ++i) {
+                float sc[4];
+                load_half4(suh + 16 * i, sc);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[i][j] = round_half(xv[i][j]) * sc[j];
+            }
+            h128_split(v, hb, out);
+            if (live) {
+                const size_t o = ((size_t)op * a.positions + p) * a.K + col;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) out[i][j] *= kHadScale;
+                    store_act4(a.xp, kF16, o + 16u * i, out[i]);
+                }
+            }
+        }
+    }
 }
 
-// the output rotation of a 128-block whose elements 4 L .. 4 L + 3 lane L holds (svh_blk: the block's first scale)
-__device__ __forceinline__ void finish4(float (&v)[4], const __half* svh_blk, uint32_t lane) {
-    float sc[4];
-    load_half4(svh_blk + 4u * lane, sc);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = round_half(v[j]);
-    h128_warp_v4(v, lane);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = round_half(v[j] * kHadScale * sc[j]);
-}
-
-// grid (out / 128, ceil(rows / 8)): the plain finish of a dense linear (format.finishOutput, format.zig:370-380)
+// grid (spread, ceil(rows / 64)): the plain finish of a dense linear
 struct FinishArgs {
     const __half* z;
     const __half* svh;
@@ -450,14 +582,19 @@ struct FinishArgs {
     uint32_t rows, out;
 };
 __global__ void __launch_bounds__(256) finish_rows_kernel(const FinishArgs a) {
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const uint32_t row = blockIdx.y * 8u + warp, blk = blockIdx.x;
-    if (row >= a.rows) return;
-    float v[4];
-    const size_t o = (size_t)row * a.out + blk * 128u + 4u * lane;
-    load_half4(a.z + o, v);
-    finish4(v, a.svh + blk * 128u, lane);
-    store_act4(a.y, a.y_dt, o, v);
+    const uint32_t lane = threadIdx.x & 31u, q = lane & 3u;
+    uint32_t row;
+    bool live;
+    if (!my_position(a.rows, lane, row, live)) return;
+    const HadB hb = had_b(lane);
+    for (uint32_t blk = blockIdx.x; blk < (a.out >> 7); blk += gridDim.x) {
+        const size_t o = (size_t)row * a.out + blk * 128u + 4u * q;
+        float v[8][4];
+        finish_block_mma(a.z + o, a.svh + blk * 128u + 4u * q, hb, v);
+        if (live)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) store_act4(a.y, a.y_dt, o + 16u * i, v[i]);
+    }
 }
 
 __device__ __forceinline__ float swiglu_f32(float g, float u, float limit, int clamp_at) {
@@ -470,7 +607,7 @@ __device__ __forceinline__ float swiglu_f32(float g, float u, float limit, int c
     return s * u;
 }
 
-// grid (inter / 128, ceil(P / 8)): gate and up finish, SwiGLU, the down projection's prepare, per sorted position
+// grid (spread, ceil(P / 64)): gate and up finish, SwiGLU, the down projection's prepare, per sorted position
 struct MidArgs {
     const __half* z;  // [2][P][inter]
     const __half *gate_svh, *up_svh, *down_suh;
@@ -481,27 +618,36 @@ struct MidArgs {
     __half* hd;  // [P][inter]
 };
 __global__ void __launch_bounds__(256) mid_kernel(const MidArgs a) {
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const uint32_t p = blockIdx.y * 8u + warp, blk = blockIdx.x;
-    if (p >= a.positions) return;
+    const uint32_t lane = threadIdx.x & 31u, q = lane & 3u;
+    uint32_t p;
+    bool live;
+    if (!my_position(a.positions, lane, p, live)) return;
     const uint32_t e = min(a.inds[a.order[p]], a.experts - 1u);
-    const size_t eo = (size_t)e * a.inter + blk * 128u, zo = (size_t)p * a.inter + blk * 128u + 4u * lane;
-    float g[4], u[4], sd[4];
-    load_half4(a.z + zo, g);
-    load_half4(a.z + (size_t)a.positions * a.inter + zo, u);
-    load_half4(a.down_suh + eo + 4u * lane, sd);
-    finish4(g, a.gate_svh + eo, lane);
-    finish4(u, a.up_svh + eo, lane);
-    float d[4];
+    const HadB hb = had_b(lane);
+    for (uint32_t blk = blockIdx.x; blk < (a.inter >> 7); blk += gridDim.x) {
+        const size_t eo = (size_t)e * a.inter + blk * 128u + 4u * q, zo = (size_t)p * a.inter + blk * 128u + 4u * q;
+        float g[8][4], u[8][4];
+        finish_block_mma(a.z + zo, a.gate_svh + eo, hb, g);
+        finish_block_mma(a.z + (size_t)a.positions * a.inter + zo, a.up_svh + eo, hb, u);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) d[j] = round_half(swiglu_f32(g[j], u[j], a.limit, a.clamp_at)) * sd[j];
-    h128_warp_v4(d, lane);
+        for (int i = 0; i < 8; ++i) {
+            float sd[4];
+            load_half4(a.down_suh + eo + 16 * i, sd);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) d[j] *= kHadScale;
-    store_act4(a.hd, kF16, zo, d);
+            for (int j = 0; j < 4; ++j) g[i][j] = round_half(swiglu_f32(g[i][j], u[i][j], a.limit, a.clamp_at)) * sd[j];
+        }
+        h128_split(g, hb, u);
+        if (live)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) u[i][j] *= kHadScale;
+                store_act4(a.hd, kF16, zo + 16u * i, u[i]);
+            }
+    }
 }
 
-// grid (hidden / 128, ceil(rows / 8)): per row, each slot's down finish (through inv) and the score-weighted sum in slot
+// grid (spread, ceil(rows / 64)): per row, each slot's down finish (through inv) and the score-weighted sum in slot
 // order, then the optional shared-expert add in the output dtype
 struct FinArgs {
     const __half* zd;  // [P][hidden]
@@ -515,30 +661,44 @@ struct FinArgs {
     uint32_t rows, hidden, topk, experts;
 };
 __global__ void __launch_bounds__(256) moe_fin_kernel(const FinArgs a) {
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const uint32_t row = blockIdx.y * 8u + warp, blk = blockIdx.x;
-    if (row >= a.rows) return;
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    for (uint32_t k = 0; k < a.topk; ++k) {
-        const size_t slot = (size_t)row * a.topk + k;
-        const uint32_t p = a.inv[slot], e = min(a.inds[slot], a.experts - 1u);
-        const float w = load_act(a.scores, a.score_dt, slot);
-        float v[4];
-        load_half4(a.zd + (size_t)p * a.hidden + blk * 128u + 4u * lane, v);
-        finish4(v, a.down_svh + (size_t)e * a.hidden + blk * 128u, lane);
+    const uint32_t lane = threadIdx.x & 31u, q = lane & 3u;
+    uint32_t row;
+    bool live;
+    if (!my_position(a.rows, lane, row, live)) return;
+    const HadB hb = had_b(lane);
+    for (uint32_t blk = blockIdx.x; blk < (a.hidden >> 7); blk += gridDim.x) {
+        const uint32_t col = blk * 128u + 4u * q;
+        float acc[8][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] = __fadd_rn(acc[j], __fmul_rn(w, v[j]));
-    }
-    const size_t o = (size_t)row * a.hidden + blk * 128u + 4u * lane;
-    if (a.shared) {
-        float t[4], sh[4];
-        store_act4(a.y, a.y_dt, o, acc);   // the routed output's rounding point
-        load_act4(a.y, a.y_dt, o, t);
-        load_act4(a.shared, a.y_dt, o, sh);
+        for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] = __fadd_rn(t[j], sh[j]);
+            for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+        for (uint32_t k = 0; k < a.topk; ++k) {
+            const size_t slot = (size_t)row * a.topk + k;
+            const uint32_t p = a.inv[slot], e = min(a.inds[slot], a.experts - 1u);
+            const float w = load_act(a.scores, a.score_dt, slot);
+            float v[8][4];
+            finish_block_mma(a.zd + (size_t)p * a.hidden + col, a.down_svh + (size_t)e * a.hidden + col, hb, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(w, v[i][j]));
+        }
+        if (!live) continue;
+        const size_t o = (size_t)row * a.hidden + col;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (a.shared) {
+                float t[4], sh[4];
+                store_act4(a.y, a.y_dt, o + 16u * i, acc[i]);  // the routed output's rounding point
+                load_act4(a.y, a.y_dt, o + 16u * i, t);
+                load_act4(a.shared, a.y_dt, o + 16u * i, sh);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = __fadd_rn(t[j], sh[j]);
+            }
+            store_act4(a.y, a.y_dt, o + 16u * i, acc[i]);
+        }
     }
-    store_act4(a.y, a.y_dt, o, acc);
 }
 
 // ---- host side -----------------------------------------------------------------------------------------------------
@@ -623,7 +783,8 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
     pa.topk = 1;
     pa.experts = 1;
     pa.xp = xp;
-    prep_rows_kernel<<<dim3(p.in / 128u, (p.rows + 7u) / 8u, 1), 256, 0, stream>>>(pa);
+    pa.ops = 1;
+    prep_rows_kernel<<<dim3(spread(p.rows, p.in / 128u), (p.rows + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(pa);
     CUtensorMap map;
     if (!make_a_map(&map, xp, p.rows, p.in, 256u)) return cudaErrorNotSupported;
     GemmArgs g = {};
@@ -639,7 +800,7 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
     cudaError_t rc = launch_gemm(map, g, (p.rows + 255u) / 256u, 256u, codebook, stream);
     if (rc != cudaSuccess) return rc;
     FinishArgs f = {z, static_cast<const __half*>(p.svh), p.y, p.x_dt, p.rows, p.out};
-    finish_rows_kernel<<<dim3(p.out / 128u, (p.rows + 7u) / 8u, 1), 256, 0, stream>>>(f);
+    finish_rows_kernel<<<dim3(spread(p.rows, p.out / 128u), (p.rows + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(f);
     *launches += 3;
     return cudaGetLastError();
 }
@@ -705,7 +866,8 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
     pa.order = w.order;
     pa.inds = inds;
     pa.xp = w.xp;
-    prep_rows_kernel<<<dim3(H / 128u, (S + 7u) / 8u, 2), 256, 0, stream>>>(pa);
+    pa.ops = 2;
+    prep_rows_kernel<<<dim3(spread(S, H / 128u), (S + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(pa);
 
     const uint32_t tile_bytes = 2u * a.n;
     CUtensorMap map_gu, map_d;
@@ -730,7 +892,7 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
 
     MidArgs m = {w.zgu, static_cast<const __half*>(a.gate_svh), static_cast<const __half*>(a.up_svh),
                  static_cast<const __half*>(a.down_suh), w.order, inds, S, I, a.experts, a.limit, a.clamp_at, w.hd};
-    mid_kernel<<<dim3(I / 128u, (S + 7u) / 8u, 1), 256, 0, stream>>>(m);
+    mid_kernel<<<dim3(spread(S, I / 128u), (S + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(m);
 
     GemmArgs d = {};
     d.trellis[0] = d.trellis[1] = a.down_t;
@@ -748,7 +910,7 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
 
     FinArgs f = {w.zd, static_cast<const __half*>(a.down_svh), w.inv, inds, a.scores, a.score_dt, a.shared, a.y, a.x_dt,
                  a.rows, H, a.topk, a.experts};
-    moe_fin_kernel<<<dim3(H / 128u, (a.rows + 7u) / 8u, 1), 256, 0, stream>>>(f);
+    moe_fin_kernel<<<dim3(spread(a.rows, H / 128u), (a.rows + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(f);
     *launches += 8;
     return cudaGetLastError();
 }
