@@ -102,3 +102,25 @@ def test_ep_and_column_shards_on_gloo_ranks(world):
         errors.append(fail.get())
     assert not errors, errors
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+
+
+def test_mixed_rate_buckets_route_every_slot_to_its_sub_bank():
+    """The mixed-rate layer's index arithmetic with host stand-ins for the engine: expert e scales its row by e + 1."""
+    from turboexl3_b200 import mixed
+    g = torch.Generator().manual_seed(5)
+    E, rows, topk, H = 11, 9, 3, 8
+    rates = [32, 48, 64, 48, 32, 32, 64, 48, 48, 64, 32]
+    b = mixed.bucket_by_rate(rates)
+    assert b.rates == [32, 48, 64]
+    assert b.members == [[0, 4, 5, 10], [1, 3, 7, 8], [2, 6, 9]]
+    for e in range(E):
+        assert b.members[int(b.bank_of[e])][int(b.local_of[e])] == e
+    x = torch.randn(rows, H, generator=g).half()
+    inds = torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(rows)]).to(torch.int32)
+    scores = torch.rand(rows, topk, generator=g)
+    banks = [torch.tensor(m) for m in b.members]  # a "bank" here is just its experts' ids
+    expert_fn = lambda xr, bank, er: (xr.float() * (bank[er.long()].float() + 1.0).unsqueeze(1)).half()
+    merge_fn = lambda v, sc: (v.float() * sc.unsqueeze(-1)).sum(1)
+    y = mixed.mixed_rate_moe(x, banks, b, inds, scores, None, expert_fn=expert_fn, merge_fn=merge_fn)
+    want = ((x.float().unsqueeze(1) * (inds.float() + 1.0).unsqueeze(-1)).half().float() * scores.unsqueeze(-1)).sum(1)
+    assert torch.allclose(y, want, rtol=0, atol=1e-6)

@@ -1,14 +1,16 @@
 // Prefill-row kernels (more than 32 activation rows): the trellis is decoded inside the weight loader of a tcgen05 GEMM.
 //
-//   route   : counting sort of the row-slots by expert + a table of 256-row M tiles (the reference's route:
+//   route   : counting sort of the row-slots by expert + a table of 128-row M tiles (the reference's route:
 //             src/core/kernels/prefill/froute_count.metal, table_2.metal; src/kernels/hip/prefill/prefill.hip:22-71)
 //   prep    : input rotation of every sorted row, f16, natural order (format.prepareInput, src/core/format.zig:334-345)
-//   gemm    : z = f16(xp W_hat), 256 x 128 output tile per CTA, K in stages of 64. Warp 0 streams the activation tile
-//             with TMA (128-byte swizzle), warps 2-9 decode the stage's 32 weight tiles in registers and store them as
-//             the K-major 128-byte-swizzled B operand, warp 1 issues tcgen05.mma (two M = 128 halves share each decoded
-//             B tile; f32 accumulators in tensor memory), then warps 2-9 read the accumulators back (tcgen05.ld), round
-//             to f16 and store. (The reference's GEMM with the decode in the loader: src/core/kernels/prefill/gemm_4.metal,
-//             src/kernels/hip/prefill/prefill.hip:125-216, on Apple / gfx11 matrix units.)
+//   gemm    : z = f16(xp W_hat), a 256 x 128 (dense) or 128 x 128 (routed experts, two CTAs a multiprocessor) output tile
+//             per CTA, K in stages of 64. One thread of warp 0 feeds two rings: the activation tile by TMA (tiled, 128-byte
+//             swizzle) and the stage's code words by bulk copies. Warps 2-17 decode the stage's 32 weight tiles in
+//             registers and store them as the K-major 128-byte-swizzled B operand; one thread of warp 1 issues tcgen05.mma
+//             (f32 accumulators in tensor memory; with 256 rows two M = 128 halves share each decoded B tile); then warps
+//             2-17 read the accumulators back (tcgen05.ld), round to f16 and store. (The reference's GEMM with the decode
+//             in the loader: src/core/kernels/prefill/gemm_4.metal, src/kernels/hip/prefill/prefill.hip:125-216, on
+//             Apple / gfx11 matrix units.)
 //   mid     : gate and up finish, SwiGLU, the down projection's prepare (src/kernels/hip/routed.hpp:64-112)
 //   fin     : per row, every slot's down finish and the score-weighted sum in slot order
 //             (src/kernels/hip/prefill/prefill.hip:243-264); dense linears use the plain finish.

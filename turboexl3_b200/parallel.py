@@ -93,16 +93,10 @@ def ep_moe_cuda(x: torch.Tensor, bank_local, inds: torch.Tensor, scores: torch.T
                 shared: Optional[torch.Tensor] = None, group=None) -> torch.Tensor:
     """ep_moe on the engine: x [rows, hidden] on this rank's GPU, bank_local = this rank's experts."""
     from . import api
+    from .mixed import expert_rows
 
     def expert_fn(xr: torch.Tensor, er: torch.Tensor) -> torch.Tensor:
-        r = xr.shape[0]
-        ones = torch.ones((1, r, 1), dtype=torch.float32, device=xr.device)
-        out = []
-        for r0 in range(0, r, 1 << 16):  # keep every call's row count inside the engine's limits
-            r1 = min(r, r0 + (1 << 16))
-            out.append(api.moe(xr[r0:r1].unsqueeze(0).contiguous(), bank_local, er[r0:r1].view(1, -1, 1).contiguous(),
-                               ones[:, r0:r1].contiguous(), dec).squeeze(0))
-        return torch.cat(out).to(torch.float16)
+        return expert_rows(xr, bank_local, er, dec)
 
     def merge_fn(v: torch.Tensor, sc: torch.Tensor) -> torch.Tensor:
         return api.moe_merge(v.contiguous(), sc.contiguous(), x.dtype, shared)
