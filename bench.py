@@ -242,6 +242,48 @@ def prefill_submetric(t3, synth, torch) -> dict:
     return out
 
 
+def sharded_submetric(t3, synth, torch, dist, rank: int, world: int) -> dict:
+    """The two sharded paths at N > 1 (every rank calls this): the config 4 routed layer expert-parallel, 4096 tokens a
+    rank (two all-to-alls a layer), and config 5's q_b projection column-sharded (one all-gather). Device time, max over
+    ranks."""
+    from turboexl3_b200 import parallel as par
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([time_us(fn, reps)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    out = {}
+    H, I, E, topk, n, rows = 2048, 512, 512, 10, 48, 4096
+    per = E // world
+    arrs = synth.bank(100 + rank, per, H, I, n)  # this rank's experts only
+    local = t3.Bank(t3.Proj(dev(arrs["gate_t"]), dev(arrs["gate_suh"]), dev(arrs["gate_svh"])),
+                    t3.Proj(dev(arrs["up_t"]), dev(arrs["up_suh"]), dev(arrs["up_svh"])),
+                    t3.Proj(dev(arrs["down_t"]), dev(arrs["down_suh"]), dev(arrs["down_svh"])))
+    inds, scores = synth.routing(200 + rank, rows, E, topk)
+    x, di, ds = dev(synth.activations(300 + rank, rows, H)), dev(inds), dev(scores)
+    us = timed(lambda: par.ep_moe_cuda(x, local, di, ds, E, t3.Decode.mul1), 3)
+    out["ep_moe_config4_K3"] = {"tokens_per_rank": rows, "us_per_layer": round(us, 1),
+                                "tokens_per_s": round(world * rows / us * 1e6),
+                                "TFLOPS": round(world * 2.0 * rows * topk * 3 * H * I / us / 1e6, 1),
+                                "exchange": "all_to_all_single x rows out, v rows back; merge at the home rank"}
+    in_dim, out_dim = 1536, 24576
+    trellis, suh, svh = synth.linear(400, in_dim, out_dim, 64)
+    t_sh, svh_sh = par.shard_columns(dev(trellis), dev(svh), rank, world)
+    suh_d = dev(suh)
+    for r in (1, 4096):
+        xr = dev(synth.activations(401 + r, r, in_dim))
+        us = timed(lambda: par.column_sharded_linear(xr, t_sh, suh_d, svh_sh, out_dim, t3.Decode.mul1), 5)
+        out[f"column_sharded_q_b_1536x24576_K4_rows{r}"] = {
+            "us": round(us, 1), "code_GBps": round(in_dim * out_dim * 0.5 / us / 1e3, 1),
+            "TFLOPS": round(2.0 * r * in_dim * out_dim / us / 1e6, 1), "exchange": "all_gather of y column shards"}
+    return out
+
+
 def run_case(args) -> None:
     """One named case run eagerly a few times (for profilers): prints a small JSON line, not the bench contract's."""
     import torch
@@ -434,6 +476,9 @@ def run_ours(args) -> None:
         extra["cases"] = cases
         extra["submetrics"] = {"moe_layer_decode_rows_config3": moe_submetric(t3, synth, torch),
                                "prefill": prefill_submetric(t3, synth, torch)}
+
+    if world > 1 and not args.quick:
+        extra.setdefault("submetrics", {})["sharded"] = sharded_submetric(t3, synth, torch, dist, rank, world)
 
     if t3.device_error() != 0:
         raise SystemExit("a kernel reported a bounded-wait failure; the numbers are void")

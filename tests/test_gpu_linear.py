@@ -166,3 +166,22 @@ def test_small_ring_recycles_stages():
     ref = ob.linear_rows_what(host_f32(x), what, suh, svh, 4096, 256)
     check(small, ref, "f16", "ring of one stage")
     assert t3.device_error() == 0
+
+
+@pytest.mark.parametrize("n,cb", [(48, t3.MUL1), (128, t3.MCG), (36, t3.MUL1)])
+def test_gemm_512_row_tiles(n, cb):
+    """Calls large enough to fill the GPU with 512-row tiles (four accumulators a decoded tile): a ragged last tile, rows
+    sampled in every quarter of a tile, and the same bytes as the 256-row-tile path gives the leading rows."""
+    in_dim, out_dim, rows = 512, 2560, 4100
+    trellis, suh, svh = synth.linear(600 + n, in_dim, out_dim, n, scaled=True)
+    x16 = synth.activations(601 + n, rows, in_dim)
+    dec = t3.Decode(cb, 16)
+    t, a, b, x = dev(trellis), dev(suh), dev(svh), dev(x16)
+    y = t3.linear(x, t, a, b, dec)
+    sample = [0, 127, 128, 255, 256, 383, 384, 511, 512, 1000, 2047, 2048, 3583, 4095, 4096, 4099]
+    what = ob.reconstruct_inner(trellis, in_dim, out_dim, n, cb, 16)
+    ref = ob.linear_rows_what(x16[sample].astype(np.float32), what, suh, svh, in_dim, out_dim)
+    check(host_f32(y)[sample], ref, "f16", ("512-row tiles", n))
+    small = t3.linear(x[:700].contiguous(), t, a, b, dec)  # 256-row tiles: the same K order a row
+    assert np.array_equal(bits16(y[:700]), bits16(small))
+    assert t3.device_error() == 0

@@ -31,18 +31,19 @@ constexpr uint32_t kGemmThreads = 32u * (2u + kDecodeWarps);
 constexpr uint32_t kMaxStages = 4;      // operand stages (A by TMA, B by the decode warps)
 constexpr uint32_t kMaxCodeStages = 8;  // stages of the code ring that feeds the decode warps
 
-// The two tile heights: 256 rows (two M = 128 accumulators share every decoded B tile; dense linears and full expert
-// tiles) and 128 rows (half the shared memory and tensor memory, so two CTAs fit a multiprocessor: routed experts, whose
-// tiles are mostly part-full and whose cost is the decode).
+// The tile heights: 512 rows (four M = 128 accumulators — all of tensor memory — share every decoded B tile, so a stage's
+// MMAs outlast its decode and the kernel is bound by the tensor pipe; two operand stages; large dense calls), 256 rows
+// (two accumulators, three stages; smaller dense calls) and 128 rows (half the shared memory and a quarter of tensor
+// memory, so two CTAs fit a multiprocessor: routed experts, whose tiles are mostly part-full and whose cost is the decode).
 template <int BM>
 struct Tile {
-    static_assert(BM == 128 || BM == 256, "tile height");
+    static_assert(BM == 128 || BM == 256 || BM == 512, "tile height");
     static constexpr uint32_t kABytes = BM * kBK * 2u;
     static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-    static constexpr uint32_t kStages = 3u;
-    static constexpr uint32_t kCodeStages = BM == 256 ? 6u : 3u;
-    static constexpr uint32_t kTmemCols = BM == 256 ? 256u : 128u;
-    static constexpr int kMinBlocks = BM == 256 ? 1 : 2;
+    static constexpr uint32_t kStages = BM == 512 ? 2u : 3u;
+    static constexpr uint32_t kCodeStages = BM == 256 ? 6u : (BM == 512 ? 4u : 3u);
+    static constexpr uint32_t kTmemCols = BM;  // one f32 column an output row block of 128 x 128
+    static constexpr int kMinBlocks = BM == 128 ? 2 : 1;
     // dynamic shared memory: operand stages, the code ring (4 tile rows of 16 n bytes a stage), barriers, alignment slack
     static constexpr uint32_t smem(uint32_t n) { return kStages * kStageBytes + kCodeStages * 64u * n + 1024u + 512u; }
 };
@@ -225,7 +226,10 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
                     const uint32_t s = ka % kStages, u = ka / kStages;
                     if (u == 0 || mbar_try(smem_addr(&empty[s]), (u - 1u) & 1u)) {
                         mbar_arrive_expect_tx(&full_a[s], kABytes);
-                        tma_load_2d(smem + s * kStageBytes, &tmap_a, (int)(ka * kBK), (int)(op * a.a_op_rows) + first, &full_a[s]);
+#pragma unroll
+                        for (uint32_t h = 0; h < BM; h += 256u)  // a TMA box holds at most 256 rows
+                            tma_load_2d(smem + s * kStageBytes + h * kBK * 2u, &tmap_a, (int)(ka * kBK),
+                                        (int)(op * a.a_op_rows) + first + (int)h, &full_a[s]);
                         ++ka;
                         moved = true;
                     }
@@ -249,7 +253,9 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
                 for (uint32_t kk = 0; kk < kBK / 16u; ++kk) {
                     const uint64_t bdesc = umma_desc(b_addr + kk * 32u);
                     umma_f16(tmem, umma_desc(a_addr + kk * 32u), bdesc, (ks | kk) != 0u);
-                    if (BM == 256) umma_f16(tmem + 128u, umma_desc(a_addr + 128u * 128u + kk * 32u), bdesc, (ks | kk) != 0u);
+#pragma unroll
+                    for (uint32_t h = 1; h < BM / 128u; ++h)
+                        umma_f16(tmem + h * 128u, umma_desc(a_addr + h * 128u * 128u + kk * 32u), bdesc, (ks | kk) != 0u);
                 }
                 umma_commit(&empty[s]);
             }
@@ -317,8 +323,9 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
         if (!mbar_wait(acc_full, 0u)) report(a.err, kErrMmaWait);
         tc_fence_after();
         const uint32_t quarter = warp & 3u, grp = dw >> 2;  // grp 0..3
-        const uint32_t half = BM == 256 ? (grp & 1u) : 0u;
-        const uint32_t col0 = BM == 256 ? (grp >> 1) * 64u : grp * 32u, ncols = BM == 256 ? 64u : 32u;
+        const uint32_t half = BM == 512 ? grp : (BM == 256 ? (grp & 1u) : 0u);
+        const uint32_t col0 = BM == 512 ? 0u : (BM == 256 ? (grp >> 1) * 64u : grp * 32u);
+        const uint32_t ncols = BM == 512 ? 128u : (BM == 256 ? 64u : 32u);
         const int r = (int)(half * 128u + quarter * 32u + lane);
         __half* zrow = a.z + op * a.z_op_stride + (size_t)(first + r) * a.N + nt * kBN + col0;
 #pragma unroll 1
@@ -755,6 +762,9 @@ cudaError_t launch_gemm_cb(const CUtensorMap& map, const GemmArgs& g, uint32_t m
 // bm: 256 (dense) or 128 (routed)
 cudaError_t launch_gemm(const CUtensorMap& map, const GemmArgs& g, uint32_t max_tiles, uint32_t bm, int codebook,
                         cudaStream_t stream) {
+    if (bm == 512u)
+        return codebook == kMcg ? launch_gemm_cb<kMcg, 512>(map, g, max_tiles, stream)
+                                : launch_gemm_cb<kMul1, 512>(map, g, max_tiles, stream);
     if (bm == 256u)
         return codebook == kMcg ? launch_gemm_cb<kMcg, 256>(map, g, max_tiles, stream)
                                 : launch_gemm_cb<kMul1, 256>(map, g, max_tiles, stream);
@@ -763,6 +773,17 @@ cudaError_t launch_gemm(const CUtensorMap& map, const GemmArgs& g, uint32_t max_
 }
 
 size_t up256(size_t v) { return (v + 255u) & ~(size_t)255u; }
+
+// multiprocessors of the current device (one 512- or 256-row CTA fits each)
+uint32_t one_wave_ctas() {
+    static int sms = [] {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            n = 148;
+        return n;
+    }();
+    return (uint32_t)sms;
+}
 
 }  // namespace
 
@@ -789,6 +810,8 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
     prep_rows_kernel<<<dim3(spread(p.rows, p.in / 128u), (p.rows + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(pa);
     CUtensorMap map;
     if (!make_a_map(&map, xp, p.rows, p.in, 256u)) return cudaErrorNotSupported;
+    // 512-row tiles once they fill the GPU: the decode of a B tile is then shared by four accumulators
+    const uint32_t bm = ((p.rows + 511u) / 512u) * (p.out / kBN) >= one_wave_ctas() ? 512u : 256u;
     GemmArgs g = {};
     g.trellis[0] = g.trellis[1] = p.trellis;
     g.K = p.in;
@@ -799,7 +822,7 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
     g.dense_rows = p.rows;
     g.z = z;
     g.err = p.err;
-    cudaError_t rc = launch_gemm(map, g, (p.rows + 255u) / 256u, 256u, codebook, stream);
+    cudaError_t rc = launch_gemm(map, g, (p.rows + bm - 1u) / bm, bm, codebook, stream);
     if (rc != cudaSuccess) return rc;
     FinishArgs f = {z, static_cast<const __half*>(p.svh), p.y, p.x_dt, p.rows, p.out};
     finish_rows_kernel<<<dim3(spread(p.rows, p.out / 128u), (p.rows + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(f);
