@@ -204,10 +204,20 @@ def moe_submetric(t3, synth, torch) -> dict:
                           dev(scores).view(1, rows, topk), dev(np.zeros((rows, 1), np.int32)).view(1, rows, 1),
                           dev(gate).view(1, rows, 1)))
 
+        side = torch.cuda.Stream()
+
         def layer_burst():
+            # the shared expert runs on a second stream beside the routed experts; only the routed call's last launch
+            # (the merge, which adds the shared output) waits for it
+            main = torch.cuda.current_stream()
             for (x, i_, s_, z_, g_) in calls:
-                sh = t3.moe(x, shared_bank, z_, g_)
-                t3.moe_with_shared(x, bank, i_, s_, t3.Decode.mul1, sh)
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    sh = t3.moe(x, shared_bank, z_, g_)
+                    ready = torch.cuda.Event()
+                    ready.record(side)
+                t3.moe_with_shared(x, bank, i_, s_, t3.Decode.mul1, sh, shared_ready=ready)
+                main.wait_stream(side)
 
         g = graph_of(layer_burst)
         us = time_us(g.replay, 10) / len(calls)

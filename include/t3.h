@@ -136,6 +136,15 @@ int t3_moe_with_shared(const void* x, int x_dtype, size_t rows, const t3_bank* b
                        const void* scores, int scores_dtype, int topk, t3_decode dec, const void* shared, void* y,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* t3_moe_with_shared for a shared-expert output that another stream is still computing: `shared_ready` is a cudaEvent_t
+ * recorded on that stream after `shared` was written. Only the call's last launch (the one that adds `shared`) waits for
+ * the event, so the routed experts' launches run beside the shared expert's. The reference's moeWithShared
+ * (src/root.zig:976-984) is moe followed by one add and leaves this overlap to MLX's graph scheduler; a stream-ordered C
+ * ABI has to be told. Works under stream capture (the event becomes a graph edge into the last node). */
+int t3_moe_with_shared_after(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds,
+                             const void* scores, int scores_dtype, int topk, t3_decode dec, const void* shared,
+                             void* shared_ready, void* y, void* workspace, size_t workspace_bytes, void* stream);
+
 /* The routed chain's last step on its own: y[row] = sum over the row's slots, in slot order, of score * v, in f32 with a
  * multiply and an add (ref.moeRow, src/core/ref.zig:106), stored in y_dtype, plus the optional shared-expert add.
  * v is f16 [rows * topk, hidden]: each row-slot's finished down projection, the unit an expert-parallel combine returns

@@ -239,3 +239,30 @@ def test_prefill_rows_do_not_depend_on_later_rows():
     full = bits16(t3.moe(x, bank, di, ds)).reshape(rows, H)
     part = bits16(t3.moe(x[:, :40].contiguous(), bank, di[:, :40].contiguous(), ds[:, :40].contiguous())).reshape(40, H)
     assert np.array_equal(full[:40], part)
+
+
+def test_shared_expert_on_a_second_stream():
+    """moe_with_shared told to wait for the shared output's event only at its last launch gives the bytes of the plain
+    call, at decode rows and at prefill rows."""
+    H, I, E, topk, n = 512, 256, 12, 4, 64
+    bank, _ = make_bank(91, E, H, I, n)
+    sbank, _ = make_bank(92, 1, H, I, n)
+    side = torch.cuda.Stream()
+    for rows in (3, 70):
+        inds, scores = synth.routing(93 + rows, rows, E, topk)
+        x = dev(synth.activations(94 + rows, rows, H)).view(1, rows, H)
+        di, ds = dev(inds).view(1, rows, topk), dev(scores).view(1, rows, topk)
+        zero, gate = dev(np.zeros((rows, 1), np.int32)).view(1, rows, 1), dev(np.full((rows, 1), 0.5, np.float32)).view(1, rows, 1)
+        sh = t3.moe(x, sbank, zero, gate)
+        want = bits16(t3.moe_with_shared(x, bank, di, ds, t3.Decode.mul1, sh))
+        torch.cuda.synchronize()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            sh2 = t3.moe(x, sbank, zero, gate)
+            ready = torch.cuda.Event()
+            ready.record(side)
+        got = t3.moe_with_shared(x, bank, di, ds, t3.Decode.mul1, sh2, shared_ready=ready)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        assert np.array_equal(bits16(got), want), rows
+    assert t3.device_error() == 0

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes as C
 import os
+from typing import Optional
 from dataclasses import dataclass
 
 import torch
@@ -75,6 +76,7 @@ SYMBOLS = {
     "t3_moe_swiglu": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _u32, _i, _vp, _vp, _sz, _vp]),
     "t3_moe_clamped": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _i, _vp, _vp, _sz, _vp]),
     "t3_moe_with_shared": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp, _vp, _sz, _vp]),
+    "t3_moe_with_shared_after": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp, _vp, _vp, _sz, _vp]),
     "t3_moe_merge": (_i, [_vp, _vp, _i, _sz, _i, _i, _vp, _vp, _i, _vp]),
     "t3_moe_noalloc": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp]),
     "t3_set_trace": (None, [_vp]),
@@ -251,7 +253,7 @@ def _bank_c(bank: Bank, hidden: int) -> _Bank:
                  d.trellis.shape[3])
 
 
-def _moe(x, bank, inds, scores, dec, limit, clamp_at, shared, entry: str):
+def _moe(x, bank, inds, scores, dec, limit, clamp_at, shared, entry: str, shared_ready=None):
     _need_cuda(x, inds, scores)
     if x.dim() != 3 or inds.dim() != 3 or x.shape[:2] != inds.shape[:2] or inds.shape != scores.shape:
         raise Exl3Error(1, "BadExl3Shape")  # root.validateCall, src/root.zig:128-141
@@ -280,6 +282,8 @@ def _moe(x, bank, inds, scores, dec, limit, clamp_at, shared, entry: str):
         _check(L.t3_moe_swiglu(*common, limit, clamp_at, *tail))
     elif entry == "clamped":
         _check(L.t3_moe_clamped(*common, limit, *tail))
+    elif shared_ready is not None:
+        _check(L.t3_moe_with_shared_after(*common, shared.data_ptr(), shared_ready.cuda_event, *tail))
     else:
         _check(L.t3_moe_with_shared(*common, shared.data_ptr(), *tail))
     return y
@@ -315,7 +319,8 @@ def moe_clamped(x, bank: Bank, inds, scores, dec: Decode, limit: int) -> torch.T
 
 
 def moe_with_shared(x, bank: Bank, inds, scores, dec: Decode, shared: torch.Tensor,
-                    verify_rows: bool = False) -> torch.Tensor:
-    """root.moeWithShared (src/root.zig:976-984)."""
+                    verify_rows: bool = False, shared_ready: Optional[torch.cuda.Event] = None) -> torch.Tensor:
+    """root.moeWithShared (src/root.zig:976-984). shared_ready: an event recorded on the stream that computes `shared`;
+    only the call's last launch waits for it (t3_moe_with_shared_after)."""
     del verify_rows
-    return _moe(x, bank, inds, scores, dec, 0, CLAMP_GATE_IN, shared, "shared")
+    return _moe(x, bank, inds, scores, dec, 0, CLAMP_GATE_IN, shared, "shared", shared_ready)

@@ -407,7 +407,7 @@ size_t align256(size_t v) { return (v + 255u) & ~(size_t)255u; }
 
 int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds, const void* scores,
              int scores_dtype, int topk, t3_decode dec, uint32_t limit, int clamp_at, const void* shared, void* y,
-             void* workspace, size_t workspace_bytes, void* stream) {
+             void* workspace, size_t workspace_bytes, void* stream, void* shared_ready = nullptr) {
     if (!x || !inds || !scores || !y) return T3_NULL_POINTER;
     if (rows < 1 || rows > (size_t)1 << 30 || topk <= 0) return T3_BAD_EXL3_SHAPE;
     if (topk > T3_REDUCE_MAX_TOPK) return T3_BAD_EXL3_SHAPE;  // validateCall, src/root.zig:131
@@ -453,6 +453,7 @@ int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const
     const size_t slots = rows * (size_t)topk;
     a.y = y;
     a.shared = shared;
+    a.shared_ready = shared_ready;
     a.err = dev_error_ptr();
     if (rows > T3_DECODE_ROWS_MAX) {
         int launches = 0;
@@ -488,6 +489,8 @@ int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const
     if (int rc = cuda_status(launch_moe_gate_up(a, dec.codebook, s))) return rc;
     if (int rc = cuda_status(launch_moe_down(a, dec.codebook, s))) return rc;
     g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (shared_ready)  // only the merge reads `shared`: the two GEMV launches above do not wait for it
+        if (int rc = cuda_status(cudaStreamWaitEvent(s, static_cast<cudaEvent_t>(shared_ready), 0))) return rc;
     return cuda_status(launch_moe_merge(a, s));
 }
 
@@ -549,6 +552,14 @@ int t3_moe_with_shared(const void* x, int x_dtype, size_t rows, const t3_bank* b
     if (!shared) return T3_NULL_POINTER;
     return moe_call(x, x_dtype, rows, bank, inds, scores, scores_dtype, topk, dec, 0, T3_CLAMP_GATE_IN, shared, y,
                     workspace, workspace_bytes, stream);
+}
+
+int t3_moe_with_shared_after(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds,
+                             const void* scores, int scores_dtype, int topk, t3_decode dec, const void* shared,
+                             void* shared_ready, void* y, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!shared || !shared_ready) return T3_NULL_POINTER;
+    return moe_call(x, x_dtype, rows, bank, inds, scores, scores_dtype, topk, dec, 0, T3_CLAMP_GATE_IN, shared, y,
+                    workspace, workspace_bytes, stream, shared_ready);
 }
 
 }  // extern "C"

@@ -182,6 +182,12 @@ __device__ __forceinline__ void named_sync(uint32_t id, uint32_t threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// asks L2 for `bytes` starting at p (lanes 0 .. bytes / 128 of the calling warp, one 128-byte line each): for small
+// weight-side vectors whose first use sits behind a wait, so that the use finds them in L2 and not in DRAM
+__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes, uint32_t lane) {
+    if (lane * 128u < bytes) asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const uint8_t*>(p) + lane * 128u));
+}
+
 static __device__ __noinline__ void report(uint32_t* err, uint32_t bit) {
     if (err) atomicOr(err, bit);
 }

@@ -105,6 +105,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) dense_gemv_kernel(const Dense
     } else {
         pdl_trigger();
         load_scales(static_cast<const __half*>(a.svh) + blk * 128u, lane, sv);  // weights-side: ahead of the wait
+        if (warp == 0) prefetch_l2(static_cast<const __half*>(a.suh) + b0 * 128u, nblk * 256u, lane);
         pdl_wait();  // x may be the previous kernel's output
         for (uint32_t task = warp; task < a.rows * nblk; task += kConsumerWarps) {
             const uint32_t row = task / nblk, b = task - row * nblk;
@@ -222,6 +223,13 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_gate_up_kernel(const MoeA
     const size_t expert_bytes = (size_t)(H / 16u) * out_tiles * tile_bytes;
     const uint8_t* wsrc = (proj ? a.up_t : a.gate_t) + e * expert_bytes + ((size_t)(b0 * 8u) * out_tiles + ib * 8u) * tile_bytes;
     const __half* suh = static_cast<const __half*>(proj ? a.up_suh : a.gate_suh) + (size_t)e * H;
+    if (warp == 0) {  // the expert's scale vectors are first used behind the weight stream and the cluster barrier
+        const size_t eo = (size_t)e * I + ib * 128u;
+        prefetch_l2(suh + b0 * 128u, nblk * 256u, lane);
+        prefetch_l2(static_cast<const __half*>(a.gate_svh) + eo, 256u, lane);
+        prefetch_l2(static_cast<const __half*>(a.up_svh) + eo, 256u, lane);
+        prefetch_l2(static_cast<const __half*>(a.down_suh) + eo, 256u, lane);
+    }
     const uint32_t owned = rows_owned(RM, csize);
     RingPos pos;
     for (uint32_t m0 = 0; m0 < mem.count; m0 += RM) {
@@ -299,6 +307,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs
 
     const size_t expert_bytes = (size_t)(I / 16u) * out_tiles * tile_bytes;
     const uint8_t* wsrc = a.down_t + e * expert_bytes + ((size_t)(b0 * 8u) * out_tiles + hb * 8u) * tile_bytes;
+    if (warp == 0) prefetch_l2(static_cast<const __half*>(a.down_svh) + (size_t)e * H + hb * 128u, 256u, lane);
     const uint32_t owned = rows_owned(RM, csize);
     RingPos pos;
     for (uint32_t m0 = 0; m0 < mem.count; m0 += RM) {

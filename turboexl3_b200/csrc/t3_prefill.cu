@@ -935,6 +935,10 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
 
     FinArgs f = {w.zd, static_cast<const __half*>(a.down_svh), w.inv, inds, a.scores, a.score_dt, a.shared, a.y, a.x_dt,
                  a.rows, H, a.topk, a.experts};
+    if (a.shared_ready) {  // only this launch reads `shared`
+        rc = cudaStreamWaitEvent(stream, static_cast<cudaEvent_t>(a.shared_ready), 0);
+        if (rc != cudaSuccess) return rc;
+    }
     moe_fin_kernel<<<dim3(spread(a.rows, H / 128u), (a.rows + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(f);
     *launches += 8;
     return cudaGetLastError();
