@@ -266,3 +266,22 @@ def test_shared_expert_on_a_second_stream():
         torch.cuda.synchronize()
         assert np.array_equal(bits16(got), want), rows
     assert t3.device_error() == 0
+
+
+def test_expert_with_more_members_than_a_pass_serves():
+    """With many experts the row capacity of a pass is sized for a few rows an expert; a routing that sends every row to
+    one expert makes that expert take several passes over its weights."""
+    H, I, E, topk, n = 512, 256, 96, 2, 48
+    bank, obank = make_bank(95, E, H, I, n)
+    for rows in (20, 32):
+        inds, scores = synth.routing(96 + rows, rows, E, topk)
+        inds[:, 0] = 5                                   # every row's first slot: expert 5
+        inds[:, 1] = np.where(inds[:, 1] == 5, 6, inds[:, 1])
+        x16 = synth.activations(97 + rows, rows, H)
+        x = dev(x16).view(1, rows, H)
+        y = t3.moe(x, bank, dev(inds).view(1, rows, topk), dev(scores).view(1, rows, topk))
+        ref = ob.moe_rows(obank, x16.astype(np.float32), inds, scores)
+        check_moe(host_f32(y).reshape(rows, H), ref, "f16", ("many members", rows))
+        alone = t3.moe(x[:, 7:8].contiguous(), bank, dev(inds[7:8]).view(1, 1, topk), dev(scores[7:8]).view(1, 1, topk))
+        assert np.array_equal(bits16(alone).reshape(-1), bits16(y).reshape(rows, H)[7])
+    assert t3.device_error() == 0

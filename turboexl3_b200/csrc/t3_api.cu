@@ -463,7 +463,13 @@ int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const
     }
     a.hd = workspace;
     a.v = static_cast<uint8_t*>(workspace) + align256(slots * a.inter * 2u);
-    const uint32_t rm = row_cap_for(a.rows);
+    // Rows one pass over an expert's weights serves. Sized from the geometry's expected members an expert (rows * topk /
+    // experts, with headroom), not from the row count: with many experts a 32-row call still has one or two rows an
+    // expert, and a 32-row pass would pay four times the shared memory and twice the tensor-core steps for nothing. An
+    // expert with more members than this takes further passes over its weights. A row's bytes do not depend on it.
+    const uint32_t expect = (uint32_t)((4u * slots + a.experts - 1u) / a.experts) + 4u;
+    const uint32_t rm = row_cap_for(expect < a.rows ? expect : a.rows);
+    a.row_cap = rm;
     a.overlap = !cfg.no_overlap;
     // The K splits depend on the geometry only (sized for one row's slots), never on the row count: a row's summation
     // order, hence its bytes, is the same alone and in a batch.

@@ -443,14 +443,14 @@ cudaError_t T3_CAT(launch_dense_gemv_cb, T3_CB)(const DenseArgs& a, cudaStream_t
 }
 
 cudaError_t T3_CAT(launch_moe_gate_up_cb, T3_CB)(const MoeArgs& a, cudaStream_t stream) {
-    const uint32_t rm = row_cap_for(a.rows);
+    const uint32_t rm = a.row_cap;
     KernelFn<MoeArgs> fn = T3_PICK(moe_gate_up_kernel, a.n, rm);
     return launch_cluster(fn, a, dim3(2u * a.split_gu, a.inter / 128u, a.rows * a.topk), 2u * a.split_gu,
                           gemv_smem_bytes(rm, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu), a.overlap != 0, stream);
 }
 
 cudaError_t T3_CAT(launch_moe_down_cb, T3_CB)(const MoeArgs& a, cudaStream_t stream) {
-    const uint32_t rm = row_cap_for(a.rows);
+    const uint32_t rm = a.row_cap;
     KernelFn<MoeArgs> fn = T3_PICK(moe_down_kernel, a.n, rm);
     return launch_cluster(fn, a, dim3(a.split_d, a.hidden / 128u, a.rows * a.topk), a.split_d,
                           gemv_smem_bytes(rm, a.slice_max_d, a.split_d, a.n, a.ring_d), a.overlap != 0, stream);

@@ -45,6 +45,7 @@ struct MoeArgs {
     void* y;                  // [rows, hidden], dtype x_dt
     const void* shared;       // optional [rows, hidden] dtype x_dt added at y's rounding point, or null
     void* shared_ready;       // host side only: an event the last launch (the one that reads `shared`) waits for, or null
+    uint32_t row_cap;                  // rows one pass over an expert's weights serves (8, 16 or 32): experts with more members take more passes
     uint32_t split_gu, slice_max_gu;   // K slices of gate|up (cluster = 2 * split_gu), largest slice
     uint32_t split_d, slice_max_d;     // K slices of down
     RingPlan ring_gu, ring_d;
