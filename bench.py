@@ -133,6 +133,21 @@ def cpu_sample(threads: int) -> dict:
     return {"seconds_per_pass": dt, "value": STEP_BYTES / dt / 1e9}
 
 
+def cpu_single_thread() -> dict:
+    """The same oracle on ONE host thread, as the reference's own format.project runs (it is scalar and single-threaded),
+    over the sweep's three K = 4 linears."""
+    from oracle import binding as ob
+    from turboexl3_b200 import synth
+    ops = [op for op in host_operands(0) if op[2] == 64]
+    xs = {i: synth.activations(7, 1, i).astype(np.float32) for i in (2048, 6144)}
+    t0 = time.perf_counter()
+    for (i, o, n, trellis, suh, svh) in ops:
+        ob.linear_rows(xs[i], trellis, suh, svh, i, o, n, ob.MUL1, 16, threads=1)
+    dt = time.perf_counter() - t0
+    byts = sum(code_bytes(i, o, n // 16) for (i, o, n, _, _, _) in ops)
+    return {"value": byts / dt / 1e9, "unit": UNIT, "cores": 1, "sample": "the sweep's three K = 4 linears, one row each"}
+
+
 def run_reference(args) -> None:
     if int(os.environ.get("RANK", "0")) != 0:
         return
@@ -530,7 +545,8 @@ def run_ours(args) -> None:
                      "frac": achieved / peaks["hbm"], "traffic": traffic, "peak_kind": peaks["kind"],
                      "kernel": "dense_gemv_kernel (21 launches a step; bytes and time are the step's, per launch)"},
         "cpu_baseline": {"value": cpu["value"], "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": "one full pass of the 21-linear sweep, format.project decoding every tile per call"},
+                         "sample": "one full pass of the 21-linear sweep, format.project decoding every tile per call",
+                         "single_thread": cpu_single_thread()},
         "e2e": {"value": world * STEP_BYTES / (e2e_ms_per_step * 1e-3) / 1e9, "unit": UNIT,
                 "h2d_bytes_per_step": sum(i * 2 for (i, o) in SHAPES for _ in KS),
                 "d2h_bytes_per_step": sum(o * 2 for (i, o) in SHAPES for _ in KS),

@@ -170,6 +170,17 @@ int t3_moe_noalloc(const void* x, int x_dtype, size_t rows, const t3_bank* bank,
  * pushed, [5] cluster reduce complete, [6] outputs stored. Null switches it off. */
 void t3_set_trace(void* device_u64x8);
 
+/* root.enginesHeld / root.releaseEngines (src/root.zig:1148-1192). The reference caches a compiled engine per geometry and
+ * frees them on request; here kernels are compiled ahead and a plan is recomputed per call, so an "engine" is only the
+ * record that a geometry was served on a path. The counts are distinct geometries since the last release. */
+typedef struct t3_engines {
+    size_t decode;  /* routed GEMV chains (rows <= 32) */
+    size_t dense;   /* dense linears at decode rows */
+    size_t prefill; /* dense and routed calls past 32 rows */
+} t3_engines;
+void t3_engines_held(t3_engines* out);
+void t3_release_engines(void);
+
 /* Kernels this library launched since the process started (for benches that must report their launch count). */
 uint64_t t3_launch_count(void);
 

@@ -128,3 +128,9 @@ def test_configure_validates():  # src/core/config.zig:139
     with pytest.raises(t3.Exl3Error):
         t3.configure(ring_bytes=100)
     t3.configure()
+
+
+def test_release_engines_is_a_no_op_on_empty_caches():
+    """src/root.zig:1194-1199: releaseEngines empties every cache; on empty ones it does nothing."""
+    api.release_engines()
+    assert api.engines_held() == {"decode": 0, "dense": 0, "prefill": 0}

@@ -185,3 +185,14 @@ def test_gemm_512_row_tiles(n, cb):
     small = t3.linear(x[:700].contiguous(), t, a, b, dec)  # 256-row tiles: the same K order a row
     assert np.array_equal(bits16(y[:700]), bits16(small))
     assert t3.device_error() == 0
+
+
+def test_engines_held_counts_geometries_and_release_empties_them():
+    t3.release_engines()
+    trellis, suh, svh = synth.linear(700, 256, 128, 32, scaled=True)
+    t, a, b = dev(trellis), dev(suh), dev(svh)
+    for rows in (1, 5, 40, 50):
+        t3.linear(dev(synth.activations(701, rows, 256)), t, a, b)
+    assert t3.engines_held() == {"decode": 0, "dense": 1, "prefill": 1}
+    t3.release_engines()
+    assert t3.engines_held() == {"decode": 0, "dense": 0, "prefill": 0}

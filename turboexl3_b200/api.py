@@ -81,6 +81,8 @@ SYMBOLS = {
     "t3_moe_noalloc": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp]),
     "t3_set_trace": (None, [_vp]),
     "t3_launch_count": (C.c_uint64, []),
+    "t3_engines_held": (None, [_vp]),
+    "t3_release_engines": (None, []),
 }
 
 _lib = None
@@ -172,6 +174,18 @@ def device_error(clear: bool = True) -> int:
 
 def launch_count() -> int:
     return int(lib().t3_launch_count())
+
+
+def engines_held() -> dict:
+    """root.enginesHeld (src/root.zig:1183-1192): distinct geometries served per path since the last release."""
+    out = (C.c_size_t * 3)()
+    lib().t3_engines_held(out)
+    return {"decode": int(out[0]), "dense": int(out[1]), "prefill": int(out[2])}
+
+
+def release_engines() -> None:
+    """root.releaseEngines (src/root.zig:1148-1181)."""
+    lib().t3_release_engines()
 
 
 def parse_expert_quant(json_text: str) -> dict:

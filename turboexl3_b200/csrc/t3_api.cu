@@ -5,6 +5,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <unordered_set>
 #include <string>
 
 #include "../../include/t3.h"
@@ -23,6 +24,17 @@ cudaError_t launch_moe_down_cb1(const MoeArgs&, cudaStream_t);
 namespace {
 
 std::atomic<uint64_t> g_launches{0};
+
+// The geometries served since the last t3_release_engines, by path: what the reference's engine caches would hold
+// (src/root.zig:1183-1192). Nothing heavier hangs off an entry here: kernels are compiled ahead and plans are recomputed
+// per call, so an entry is a key, not device memory.
+std::mutex g_engines_mu;
+std::unordered_set<uint64_t> g_engines[3];  // decode (routed GEMV chain), dense, prefill
+void note_engine(int kind, uint64_t a, uint64_t b, uint64_t c, uint64_t d) {
+    const uint64_t key = (a * 0x9E3779B97F4A7C15ull) ^ (b * 0xC2B2AE3D27D4EB4Full) ^ (c * 0x165667B19E3779F9ull) ^ (d << 48);
+    std::lock_guard<std::mutex> lock(g_engines_mu);
+    g_engines[kind].insert(key);
+}
 
 __device__ uint32_t g_dev_error_word;
 
@@ -304,6 +316,19 @@ void t3_set_trace(void* device_u64x8) {
 
 uint64_t t3_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+void t3_engines_held(t3_engines* out) {
+    if (!out) return;
+    std::lock_guard<std::mutex> lock(g_engines_mu);
+    out->decode = g_engines[0].size();
+    out->dense = g_engines[1].size();
+    out->prefill = g_engines[2].size();
+}
+
+void t3_release_engines(void) {
+    std::lock_guard<std::mutex> lock(g_engines_mu);
+    for (auto& e : g_engines) e.clear();
+}
+
 // ---- W_hat ----------------------------------------------------------------------------------------------------------
 
 int t3_dequant(const void* trellis, int in_dim, int out_dim, int n, t3_decode dec, void* w_hat, void* stream) {
@@ -353,6 +378,7 @@ int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, cons
         if (!workspace || workspace_bytes < t3_linear_workspace_bytes(rows, in_dim, out_dim, n)) return T3_WORKSPACE_TOO_SMALL;
         PrefillLinearArgs p = {x, y, static_cast<const uint8_t*>(trellis), suh, svh, (uint32_t)rows, (uint32_t)in_dim,
                                (uint32_t)out_dim, (uint32_t)n, mask, x_dtype, workspace, dev_error_ptr()};
+        note_engine(2, (uint64_t)in_dim, (uint64_t)out_dim, (uint64_t)n, 0);
         int launches = 0;
         const cudaError_t rc = launch_prefill_linear(p, dec.codebook, static_cast<cudaStream_t>(stream), &launches);
         g_launches.fetch_add((uint64_t)launches, std::memory_order_relaxed);
@@ -368,6 +394,7 @@ int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, cons
     a.n = (uint32_t)n;
     a.mask = mask;
     a.x_dt = x_dtype;
+    note_engine(1, (uint64_t)in_dim, (uint64_t)out_dim, (uint64_t)n, 0);
     const uint32_t nb = a.in / 128u;
     a.split = cfg.dense_split ? pow2_at_most(nb, cfg.dense_split) : pick_split(nb, a.out / 128u, 1u, 8u);
     a.overlap = !cfg.no_overlap;
@@ -455,6 +482,7 @@ int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const
     a.shared = shared;
     a.shared_ready = shared_ready;
     a.err = dev_error_ptr();
+    note_engine(rows > T3_DECODE_ROWS_MAX ? 2 : 0, ((uint64_t)a.hidden << 32) | a.inter, a.experts, a.n, a.topk);
     if (rows > T3_DECODE_ROWS_MAX) {
         int launches = 0;
         const cudaError_t rc = launch_prefill_moe(a, workspace, dec.codebook, static_cast<cudaStream_t>(stream), &launches);
