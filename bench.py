@@ -251,6 +251,11 @@ def prefill_submetric(t3, synth, torch) -> dict:
         t3.linear(x, *w)
         us = time_us(lambda: t3.linear(x, *w), 5)
         out[f"dense_{i}x{o}_K{k}_rows{rows}"] = {"us": round(us, 1), "TFLOPS": round(2.0 * rows * i * o / us / 1e6, 1)}
+        if rows >= 4096:  # the same call on a kept W_hat (the resident trunk: 2 bytes a weight held, nothing decoded)
+            w_t = t3.resident_build(w[0])
+            t3.linear_resident(x, w_t, w[1], w[2])
+            us = time_us(lambda: t3.linear_resident(x, w_t, w[1], w[2]), 5)
+            out[f"resident_{i}x{o}_rows{rows}"] = {"us": round(us, 1), "TFLOPS": round(2.0 * rows * i * o / us / 1e6, 1)}
     H, I, E, topk, n = 2048, 512, 512, 10, 48
     arrs = synth.bank(3, E, H, I, n)
     bank = t3.Bank(t3.Proj(dev(arrs["gate_t"]), dev(arrs["gate_suh"]), dev(arrs["gate_svh"])),
@@ -335,7 +340,11 @@ def run_case(args) -> None:
     else:
         w = tuple(dev(a) for a in synth.linear(5, 2048, 6144, 64))
         x = dev(synth.activations(1, max(args.rows, 33), 2048))
-        run = lambda: t3.linear(x, *w)
+        if args.case == "resident_prefill":
+            w_t = t3.resident_build(w[0])
+            run = lambda: t3.linear_resident(x, w_t, w[1], w[2])
+        else:
+            run = lambda: t3.linear(x, *w)
         per = 1
     run()
     us = time_us(run, reps) / per
@@ -568,7 +577,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--quick", action="store_true", help="headline and e2e only (no per-linear table, no submetrics)")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of replaying CUDA graphs")
-    ap.add_argument("--case", default=None, choices=["moe_decode", "moe_prefill", "dense_prefill"],
+    ap.add_argument("--case", default=None, choices=["moe_decode", "moe_prefill", "dense_prefill", "resident_prefill"],
                     help="run one case eagerly --steps times and exit (for profilers)")
     ap.add_argument("--rows", type=int, default=1, help="rows of --case")
     args = ap.parse_args()

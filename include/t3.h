@@ -170,6 +170,17 @@ int t3_moe_noalloc(const void* x, int x_dtype, size_t rows, const t3_bank* bank,
  * pushed, [5] cluster reduce complete, [6] outputs stored. Null switches it off. */
 void t3_set_trace(void* device_u64x8);
 
+/* The resident trunk (src/core/dense.zig:1323-1530: "memory for compute; a host's opt-in"): a trunk linear's W_hat decoded
+ * once and kept, so calls past 32 rows run a plain tensor-core GEMM instead of decoding every tile again. The caller owns
+ * the memory: t3_resident_bytes (dense.residentBytesOf, src/core/dense.zig:1342-1345: 2 bytes a weight) sizes it,
+ * t3_resident_build fills it — W_hat TRANSPOSED, f16 [out, in], so both GEMM operands stream by TMA as K-major tiles —
+ * and t3_linear_resident is t3_linear on it. As in the reference the kept weight is the per-call one bit for bit, and so
+ * is every output. Decode rows (<= 32) read the codes, never W_hat: Exl3EngineNotImplemented here, use t3_linear. */
+size_t t3_resident_bytes(int in_dim, int out_dim);
+int t3_resident_build(const void* trellis, int in_dim, int out_dim, int n, t3_decode dec, void* w_hat_t, void* stream);
+int t3_linear_resident(const void* x, int x_dtype, size_t rows, const void* w_hat_t, const void* suh, const void* svh,
+                       int in_dim, int out_dim, void* y, void* workspace, size_t workspace_bytes, void* stream);
+
 /* root.enginesHeld / root.releaseEngines (src/root.zig:1148-1192). The reference caches a compiled engine per geometry and
  * frees them on request; here kernels are compiled ahead and a plan is recomputed per call, so an "engine" is only the
  * record that a geometry was served on a path. The counts are distinct geometries since the last release. */

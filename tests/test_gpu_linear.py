@@ -196,3 +196,28 @@ def test_engines_held_counts_geometries_and_release_empties_them():
     assert t3.engines_held() == {"decode": 0, "dense": 1, "prefill": 1}
     t3.release_engines()
     assert t3.engines_held() == {"decode": 0, "dense": 0, "prefill": 0}
+
+
+@pytest.mark.parametrize("case", [(512, 2560, 48, t3.MUL1), (640, 256, 128, t3.MCG), (2048, 2048, 36, t3.MUL1)])
+def test_resident_trunk_gives_the_per_call_bytes(case):
+    """src/core/dense.zig:1323-1530: a kept W_hat is the per-call one bit for bit, and so is every output; decode rows never
+    touch it."""
+    from turboexl3_b200.resident import ResidentTable
+    in_dim, out_dim, n, cb = case
+    trellis, suh, svh = synth.linear(800 + n, in_dim, out_dim, n, scaled=True)
+    dec = t3.Decode(cb, 16)
+    t, a, b = dev(trellis), dev(suh), dev(svh)
+    w_t = t3.resident_build(t, dec)
+    what = ob.reconstruct_inner(trellis, in_dim, out_dim, n, cb, 16)
+    assert np.array_equal(bits16(w_t), np.ascontiguousarray(what.T).view(np.uint16))
+    table = ResidentTable()
+    table.arm([t])
+    assert table.pending() == in_dim * out_dim * 2 and not table.keeps(t)
+    for rows in (1, 33, 300, 4100):
+        x = dev(synth.activations(801 + rows, rows, in_dim))
+        assert np.array_equal(bits16(table.linear(x, t, a, b, dec)), bits16(t3.linear(x, t, a, b, dec))), rows
+        assert table.keeps(t) == (rows > 32)
+    assert table.pending() == 0 and table.stats()["kept_bytes"] == in_dim * out_dim * 2
+    table.release()
+    assert table.stats() == {"admitted": 0, "kept": 0, "kept_bytes": 0}
+    assert t3.device_error() == 0

@@ -81,6 +81,9 @@ SYMBOLS = {
     "t3_moe_noalloc": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp]),
     "t3_set_trace": (None, [_vp]),
     "t3_launch_count": (C.c_uint64, []),
+    "t3_resident_bytes": (_sz, [_i, _i]),
+    "t3_resident_build": (_i, [_vp, _i, _i, _i, _Decode, _vp, _vp]),
+    "t3_linear_resident": (_i, [_vp, _i, _sz, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp]),
     "t3_engines_held": (None, [_vp]),
     "t3_release_engines": (None, []),
 }
@@ -242,6 +245,42 @@ def linear(x: torch.Tensor, trellis: torch.Tensor, suh: torch.Tensor, svh: torch
     _check(L.t3_linear(x.data_ptr(), _DTYPES[x.dtype], rows, trellis.data_ptr(), suh.data_ptr(), svh.data_ptr(),
                        in_dim, out_dim, n, dec._c(), y.data_ptr(), ws.data_ptr() if ws is not None else None,
                        ws_bytes, _stream_ptr(x)))
+    return y
+
+
+def resident_build(trellis: torch.Tensor, dec: Decode = Decode.mul1) -> torch.Tensor:
+    """The kept weight of a trunk linear (t3_resident_build): W_hat transposed, f16 [out, in], decoded once."""
+    _need_cuda(trellis)
+    if trellis.dim() != 3:
+        raise Exl3Error(1, "BadExl3Shape")
+    if not _trellis_ok(trellis):
+        raise Exl3Error(2, "BadExl3Dtype")
+    in_dim, out_dim, n = trellis.shape[0] * 16, trellis.shape[1] * 16, trellis.shape[2]
+    L = lib()
+    if L.t3_resident_bytes(in_dim, out_dim) != in_dim * out_dim * 2:
+        raise Exl3Error(1, "BadExl3Shape")
+    w_t = torch.empty((out_dim, in_dim), dtype=torch.float16, device=trellis.device)
+    _check(L.t3_resident_build(trellis.data_ptr(), in_dim, out_dim, n, dec._c(), w_t.data_ptr(), _stream_ptr(trellis)))
+    return w_t
+
+
+def linear_resident(x: torch.Tensor, w_hat_t: torch.Tensor, suh: torch.Tensor, svh: torch.Tensor) -> torch.Tensor:
+    """linear on a kept weight (t3_linear_resident), more than 32 rows: the same bytes as `linear` on the trellis."""
+    _need_cuda(x, w_hat_t, suh, svh)
+    if x.dim() < 1 or w_hat_t.dim() != 2:
+        raise Exl3Error(1, "BadExl3Shape")
+    out_dim, in_dim = w_hat_t.shape
+    if x.shape[-1] != in_dim or suh.numel() != in_dim or svh.numel() != out_dim or not w_hat_t.is_contiguous():
+        raise Exl3Error(1, "BadExl3Shape")
+    if x.dtype not in _DTYPES or w_hat_t.dtype != torch.float16 or suh.dtype != torch.float16 or svh.dtype != torch.float16:
+        raise Exl3Error(2, "BadExl3Dtype")
+    rows = x.numel() // in_dim
+    y = torch.empty(x.shape[:-1] + (out_dim,), dtype=x.dtype, device=x.device)
+    L = lib()
+    ws_bytes = L.t3_linear_workspace_bytes(max(rows, 33), in_dim, out_dim, 16)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x.device)
+    _check(L.t3_linear_resident(x.data_ptr(), _DTYPES[x.dtype], rows, w_hat_t.data_ptr(), suh.data_ptr(), svh.data_ptr(),
+                                in_dim, out_dim, y.data_ptr(), ws.data_ptr(), ws_bytes, _stream_ptr(x)))
     return y
 
 

@@ -338,7 +338,40 @@ int t3_dequant(const void* trellis, int in_dim, int out_dim, int n, t3_decode de
     if (int rc = decode_mask(dec, mask)) return rc;
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return cuda_status(launch_dequant(static_cast<const uint8_t*>(trellis), (uint32_t)in_dim, (uint32_t)out_dim,
-                                      (uint32_t)n, mask, dec.codebook, w_hat, static_cast<cudaStream_t>(stream)));
+                                      (uint32_t)n, mask, dec.codebook, 0, w_hat, static_cast<cudaStream_t>(stream)));
+}
+
+size_t t3_resident_bytes(int in_dim, int out_dim) {
+    if (in_dim <= 0 || out_dim <= 0 || in_dim % 128 != 0 || out_dim % 128 != 0) return 0;
+    return (size_t)in_dim * (size_t)out_dim * 2u;
+}
+
+int t3_resident_build(const void* trellis, int in_dim, int out_dim, int n, t3_decode dec, void* w_hat_t, void* stream) {
+    if (!trellis || !w_hat_t) return T3_NULL_POINTER;
+    if (in_dim <= 0 || out_dim <= 0 || in_dim % 128 != 0 || out_dim % 128 != 0 || !rate_ok(n)) return T3_BAD_EXL3_SHAPE;
+    uint32_t mask;
+    if (int rc = decode_mask(dec, mask)) return rc;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cuda_status(launch_dequant(static_cast<const uint8_t*>(trellis), (uint32_t)in_dim, (uint32_t)out_dim,
+                                      (uint32_t)n, mask, dec.codebook, 1, w_hat_t, static_cast<cudaStream_t>(stream)));
+}
+
+int t3_linear_resident(const void* x, int x_dtype, size_t rows, const void* w_hat_t, const void* suh, const void* svh,
+                       int in_dim, int out_dim, void* y, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!x || !w_hat_t || !suh || !svh || !y) return T3_NULL_POINTER;
+    if (in_dim <= 0 || out_dim <= 0 || in_dim % 128 != 0 || out_dim % 128 != 0 || rows < 1 || rows > (size_t)1 << 30)
+        return T3_BAD_EXL3_SHAPE;
+    if (!dtype_ok(x_dtype)) return T3_BAD_EXL3_DTYPE;
+    if (rows <= T3_DECODE_ROWS_MAX) return T3_ENGINE_NOT_IMPLEMENTED;  // decode rows read the codes, never W_hat
+    if (rows > 0x7FFFFFFFu / (size_t)(in_dim > out_dim ? in_dim : out_dim)) return T3_BAD_EXL3_SHAPE;
+    if (!workspace || workspace_bytes < t3_linear_workspace_bytes(rows, in_dim, out_dim, 16)) return T3_WORKSPACE_TOO_SMALL;
+    PrefillLinearArgs p = {x, y, nullptr, w_hat_t, suh, svh, (uint32_t)rows, (uint32_t)in_dim, (uint32_t)out_dim, 16u, 0xFFFFu,
+                           x_dtype, workspace, dev_error_ptr()};
+    note_engine(2, (uint64_t)in_dim, (uint64_t)out_dim, 0, 1);
+    int launches = 0;
+    const cudaError_t rc = launch_prefill_linear(p, kMul1, static_cast<cudaStream_t>(stream), &launches);
+    g_launches.fetch_add((uint64_t)launches, std::memory_order_relaxed);
+    return cuda_status(rc);
 }
 
 int t3_codebook_table(t3_decode dec, void* out, void* stream) {
@@ -376,7 +409,7 @@ int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, cons
         if (!cfg.prefill) return T3_ENGINE_NOT_IMPLEMENTED;
         if (rows > 0x7FFFFFFFu / (size_t)(in_dim > out_dim ? in_dim : out_dim)) return T3_BAD_EXL3_SHAPE;
         if (!workspace || workspace_bytes < t3_linear_workspace_bytes(rows, in_dim, out_dim, n)) return T3_WORKSPACE_TOO_SMALL;
-        PrefillLinearArgs p = {x, y, static_cast<const uint8_t*>(trellis), suh, svh, (uint32_t)rows, (uint32_t)in_dim,
+        PrefillLinearArgs p = {x, y, static_cast<const uint8_t*>(trellis), nullptr, suh, svh, (uint32_t)rows, (uint32_t)in_dim,
                                (uint32_t)out_dim, (uint32_t)n, mask, x_dtype, workspace, dev_error_ptr()};
         note_engine(2, (uint64_t)in_dim, (uint64_t)out_dim, (uint64_t)n, 0);
         int launches = 0;

@@ -13,8 +13,8 @@ namespace {
 constexpr uint32_t kStripStride = 128 + 8;  // halfs per strip row (padding spreads the 2-byte scatter over banks)
 
 template <int N, int CB>
-__global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict__ trellis, uint32_t out, uint32_t n,
-                                                      uint32_t mask, __half* __restrict__ what) {
+__global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict__ trellis, uint32_t in, uint32_t out,
+                                                      uint32_t n, uint32_t mask, int transposed, __half* __restrict__ what) {
     __shared__ __align__(16) uint16_t strip[16 * kStripStride];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t tk = blockIdx.y, tn = blockIdx.x * 8u + warp, out_tiles = out / 16u;
@@ -31,9 +31,19 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
     for (uint32_t m = 0; m < 8u; ++m)
         strip[tile_row(lane, m) * kStripStride + warp * 16u + tile_col(lane, m)] = (uint16_t)(b[m >> 1] >> ((m & 1u) * 16u));
     __syncthreads();
-    const uint32_t r = tid >> 4, c = (tid & 15u) * 8u;  // 16 rows x 16 chunks of 8 halfs
-    const uint4 v = *reinterpret_cast<const uint4*>(&strip[r * kStripStride + c]);
-    *reinterpret_cast<uint4*>(what + ((size_t)tk * 16u + r) * out + blockIdx.x * 128u + c) = v;
+    if (!transposed) {
+        const uint32_t r = tid >> 4, c = (tid & 15u) * 8u;  // 16 rows x 16 chunks of 8 halfs
+        const uint4 v = *reinterpret_cast<const uint4*>(&strip[r * kStripStride + c]);
+        *reinterpret_cast<uint4*>(what + ((size_t)tk * 16u + r) * out + blockIdx.x * 128u + c) = v;
+    } else {
+        // [out, in]: output column c's 16 inputs of this tile row are 32 contiguous bytes; a thread writes half of them
+        const uint32_t c = tid >> 1, r0 = (tid & 1u) * 8u;
+        uint32_t w[4];
+#pragma unroll
+        for (uint32_t i = 0; i < 4u; ++i)
+            w[i] = (uint32_t)strip[(r0 + 2u * i) * kStripStride + c] | ((uint32_t)strip[(r0 + 2u * i + 1u) * kStripStride + c] << 16);
+        *reinterpret_cast<uint4*>(what + (size_t)(blockIdx.x * 128u + c) * in + tk * 16u + r0) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
 }
 
 template <int CB>
@@ -46,16 +56,16 @@ __global__ void codebook_table_kernel(uint32_t mask, uint16_t* out) {
 }
 
 template <int CB>
-cudaError_t launch_dequant_cb(const uint8_t* trellis, uint32_t in, uint32_t out, uint32_t n, uint32_t mask, void* what,
-                              cudaStream_t stream) {
+cudaError_t launch_dequant_cb(const uint8_t* trellis, uint32_t in, uint32_t out, uint32_t n, uint32_t mask, int transposed,
+                              void* what, cudaStream_t stream) {
     const dim3 grid(out / 128u, in / 16u, 1);
     __half* w = static_cast<__half*>(what);
     switch (n) {
 #define T3_CASE(NN) \
-    case NN: dequant_kernel<NN, CB><<<grid, 256, 0, stream>>>(trellis, out, n, mask, w); break;
+    case NN: dequant_kernel<NN, CB><<<grid, 256, 0, stream>>>(trellis, in, out, n, mask, transposed, w); break;
         T3_CASE(16) T3_CASE(32) T3_CASE(48) T3_CASE(64) T3_CASE(80) T3_CASE(96) T3_CASE(112) T3_CASE(128)
 #undef T3_CASE
-        default: dequant_kernel<0, CB><<<grid, 256, 0, stream>>>(trellis, out, n, mask, w); break;
+        default: dequant_kernel<0, CB><<<grid, 256, 0, stream>>>(trellis, in, out, n, mask, transposed, w); break;
     }
     return cudaGetLastError();
 }
@@ -63,9 +73,9 @@ cudaError_t launch_dequant_cb(const uint8_t* trellis, uint32_t in, uint32_t out,
 }  // namespace
 
 cudaError_t launch_dequant(const uint8_t* trellis, uint32_t in, uint32_t out, uint32_t n, uint32_t mask, int codebook,
-                           void* what, cudaStream_t stream) {
-    return codebook == kMcg ? launch_dequant_cb<kMcg>(trellis, in, out, n, mask, what, stream)
-                            : launch_dequant_cb<kMul1>(trellis, in, out, n, mask, what, stream);
+                           int transposed, void* what, cudaStream_t stream) {
+    return codebook == kMcg ? launch_dequant_cb<kMcg>(trellis, in, out, n, mask, transposed, what, stream)
+                            : launch_dequant_cb<kMul1>(trellis, in, out, n, mask, transposed, what, stream);
 }
 
 cudaError_t launch_codebook_table(int codebook, uint32_t mask, uint16_t* out, cudaStream_t stream) {

@@ -69,6 +69,7 @@ struct PrefillLinearArgs {
     const void* x;
     void* y;
     const uint8_t* trellis;
+    const void* resident;  // W_hat transposed, f16 [out, in], kept by the caller: the GEMM loads it instead of decoding; or null
     const void* suh;
     const void* svh;
     uint32_t rows, in, out, n, mask;
@@ -82,9 +83,9 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
 size_t prefill_moe_workspace(size_t rows, uint32_t topk, uint32_t experts, uint32_t hidden, uint32_t inter);
 cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, cudaStream_t stream, int* launches);
 
-// W_hat [in, out] f16 from the trellis
+// W_hat f16 from the trellis: [in, out], or transposed [out, in]
 cudaError_t launch_dequant(const uint8_t* trellis, uint32_t in, uint32_t out, uint32_t n, uint32_t mask, int codebook,
-                           void* what, cudaStream_t stream);
+                           int transposed, void* what, cudaStream_t stream);
 // all 65,536 codewords through the kernels' decoders: out[cw] = f16 bits (test hook)
 cudaError_t launch_codebook_table(int codebook, uint32_t mask, uint16_t* out, cudaStream_t stream);
 

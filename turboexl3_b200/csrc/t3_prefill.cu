@@ -145,9 +145,10 @@ struct GemmArgs {
     uint32_t* err;
 };
 
-template <int NN, int CB, int BM>
+// RES: the B operand is a kept W_hat (transposed, [N, K] f16) loaded by TMA like A; nothing is decoded.
+template <int NN, int CB, int BM, bool RES = false>
 __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
-    gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmArgs a) {
+    gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs a) {
     using T = Tile<BM>;
     constexpr uint32_t kStages = T::kStages, kStageBytes = T::kStageBytes, kABytes = T::kABytes;
     int e = 0, first = 0, rows = 0;
@@ -207,7 +208,7 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
             const uint8_t* src = (op ? a.trellis[1] : a.trellis[0]) + (size_t)e * a.expert_bytes + (size_t)(nt * 8u) * tile_bytes;
             const size_t tk_stride = (size_t)out_tiles * tile_bytes;
             const uint32_t row_bytes = 8u * tile_bytes;
-            uint32_t ka = 0, kc = 0, idle = 0;
+            uint32_t ka = 0, kc = RES ? ksteps : 0u, idle = 0;
             while (ka < ksteps || kc < ksteps) {
                 bool moved = false;
                 if (kc < ksteps) {
@@ -225,7 +226,8 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
                 if (ka < ksteps) {
                     const uint32_t s = ka % kStages, u = ka / kStages;
                     if (u == 0 || mbar_try(smem_addr(&empty[s]), (u - 1u) & 1u)) {
-                        mbar_arrive_expect_tx(&full_a[s], kABytes);
+                        mbar_arrive_expect_tx(&full_a[s], RES ? kStageBytes : kABytes);
+                        if (RES) tma_load_2d(smem + s * kStageBytes + kABytes, &tmap_b, (int)(ka * kBK), (int)(nt * kBN), &full_a[s]);
 #pragma unroll
                         for (uint32_t h = 0; h < BM; h += 256u)  // a TMA box holds at most 256 rows
                             tma_load_2d(smem + s * kStageBytes + h * kBK * 2u, &tmap_a, (int)(ka * kBK),
@@ -246,7 +248,7 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
             for (uint32_t ks = 0; ks < ksteps; ++ks) {
                 const uint32_t s = ks % kStages, u = ks / kStages;
                 if (!mbar_wait(&full_a[s], u & 1u)) report(a.err, kErrFullWait);
-                if (!mbar_wait(&full_b[s], u & 1u)) report(a.err, kErrFullWait);
+                if (!RES && !mbar_wait(&full_b[s], u & 1u)) report(a.err, kErrFullWait);
                 tc_fence_after();
                 const uint32_t a_addr = smem_addr(smem + s * kStageBytes), b_addr = a_addr + kABytes;
 #pragma unroll
@@ -284,7 +286,7 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
             boff[i][0] = row0 + ((2u * (tk0 + i)) ^ g) * 16u;
             boff[i][1] = row0 + ((2u * (tk0 + i) + 1u) ^ g) * 16u;
         }
-        for (uint32_t ks = 0; ks < ksteps; ++ks) {
+        for (uint32_t ks = RES ? ksteps : 0u; ks < ksteps; ++ks) {
             const uint32_t s = ks % kStages, u = ks / kStages, cs = ks % kCodeStages, uc = ks / kCodeStages;
             if (!mbar_wait(&full_c[cs], uc & 1u)) report(a.err, kErrFullWait);
             const uint8_t* cst = codes + cs * code_stage_bytes;
@@ -741,9 +743,22 @@ bool make_a_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, u
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// the resident GEMM: both operands by TMA
+template <int BM>
+cudaError_t launch_gemm_resident(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& g, uint32_t max_tiles,
+                                 cudaStream_t stream) {
+    void (*fn)(const CUtensorMap, const CUtensorMap, const GemmArgs) = gemm_decode_kernel<0, 0, BM, true>;
+    const uint32_t smem_bytes = Tile<BM>::smem(0);
+    cudaError_t rc = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)smem_bytes);
+    if (rc != cudaSuccess) return rc;
+    fn<<<dim3(g.N / kBN, max_tiles, 1), kGemmThreads, smem_bytes, stream>>>(map_a, map_b, g);
+    return cudaGetLastError();
+}
+
 template <int CB, int BM>
 cudaError_t launch_gemm_cb(const CUtensorMap& map, const GemmArgs& g, uint32_t max_tiles, cudaStream_t stream) {
-    void (*fn)(const CUtensorMap, const GemmArgs) = nullptr;
+    void (*fn)(const CUtensorMap, const CUtensorMap, const GemmArgs) = nullptr;
     switch (g.n) {
 #define T3_CASE(NN) \
     case NN: fn = gemm_decode_kernel<NN, CB, BM>; break;
@@ -755,7 +770,7 @@ cudaError_t launch_gemm_cb(const CUtensorMap& map, const GemmArgs& g, uint32_t m
     cudaError_t rc = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)Tile<BM>::smem(128u));
     if (rc != cudaSuccess) return rc;
-    fn<<<dim3(g.ops * g.N / kBN, max_tiles, 1), kGemmThreads, smem_bytes, stream>>>(map, g);
+    fn<<<dim3(g.ops * g.N / kBN, max_tiles, 1), kGemmThreads, smem_bytes, stream>>>(map, map, g);
     return cudaGetLastError();
 }
 
@@ -816,13 +831,21 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
     g.trellis[0] = g.trellis[1] = p.trellis;
     g.K = p.in;
     g.N = p.out;
-    g.n = p.n;
+    g.n = p.resident ? 0u : p.n;  // no code ring beside a kept weight: the barriers follow the operand stages directly
     g.mask = p.mask;
     g.ops = 1;
     g.dense_rows = p.rows;
     g.z = z;
     g.err = p.err;
-    cudaError_t rc = launch_gemm(map, g, (p.rows + bm - 1u) / bm, bm, codebook, stream);
+    cudaError_t rc;
+    if (p.resident) {
+        CUtensorMap map_b;  // W_hat transposed [out, in]: boxes of 64 inputs x 128 outputs, the decoded B tile's layout
+        if (!make_a_map(&map_b, p.resident, p.out, p.in, kBN)) return cudaErrorNotSupported;
+        rc = bm == 512u ? launch_gemm_resident<512>(map, map_b, g, (p.rows + bm - 1u) / bm, stream)
+                        : launch_gemm_resident<256>(map, map_b, g, (p.rows + bm - 1u) / bm, stream);
+    } else {
+        rc = launch_gemm(map, g, (p.rows + bm - 1u) / bm, bm, codebook, stream);
+    }
     if (rc != cudaSuccess) return rc;
     FinishArgs f = {z, static_cast<const __half*>(p.svh), p.y, p.x_dt, p.rows, p.out};
     finish_rows_kernel<<<dim3(spread(p.rows, p.out / 128u), (p.rows + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(f);
