@@ -41,8 +41,9 @@ struct Tile {
     static constexpr uint32_t kABytes = BM * kBK * 2u;
     static constexpr uint32_t kStageBytes = kABytes + kBBytes;
     static constexpr uint32_t kStages = BM == 512 ? 2u : 3u;
+    static constexpr uint32_t kBoxRows = BM % 256u == 0u ? 256u : 128u;  // rows of one TMA box of the activation tile
     static constexpr uint32_t kCodeStages = BM == 256 ? 6u : (BM == 512 ? 4u : 3u);
-    static constexpr uint32_t kTmemCols = BM;  // one f32 column an output row block of 128 x 128
+    static constexpr uint32_t kTmemCols = BM;  // 128 f32 columns an accumulator
     static constexpr int kMinBlocks = BM == 128 ? 2 : 1;
     // dynamic shared memory: operand stages, the code ring (4 tile rows of 16 n bytes a stage), barriers, alignment slack
     static constexpr uint32_t smem(uint32_t n) { return kStages * kStageBytes + kCodeStages * 64u * n + 1024u + 512u; }
@@ -229,7 +230,7 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
                         mbar_arrive_expect_tx(&full_a[s], RES ? kStageBytes : kABytes);
                         if (RES) tma_load_2d(smem + s * kStageBytes + kABytes, &tmap_b, (int)(ka * kBK), (int)(nt * kBN), &full_a[s]);
 #pragma unroll
-                        for (uint32_t h = 0; h < BM; h += 256u)  // a TMA box holds at most 256 rows
+                        for (uint32_t h = 0; h < BM; h += T::kBoxRows)  // a TMA box holds at most 256 rows
                             tma_load_2d(smem + s * kStageBytes + h * kBK * 2u, &tmap_a, (int)(ka * kBK),
                                         (int)(op * a.a_op_rows) + first + (int)h, &full_a[s]);
                         ++ka;
@@ -324,14 +325,14 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
         // accumulator halves (BM = 256) and the columns between them
         if (!mbar_wait(acc_full, 0u)) report(a.err, kErrMmaWait);
         tc_fence_after();
+        // every accumulator's lane quarter `quarter`, columns 32 grp .. + 31 of its 128
         const uint32_t quarter = warp & 3u, grp = dw >> 2;  // grp 0..3
-        const uint32_t half = BM == 512 ? grp : (BM == 256 ? (grp & 1u) : 0u);
-        const uint32_t col0 = BM == 512 ? 0u : (BM == 256 ? (grp >> 1) * 64u : grp * 32u);
-        const uint32_t ncols = BM == 512 ? 128u : (BM == 256 ? 64u : 32u);
-        const int r = (int)(half * 128u + quarter * 32u + lane);
-        __half* zrow = a.z + op * a.z_op_stride + (size_t)(first + r) * a.N + nt * kBN + col0;
+        const uint32_t col0 = grp * 32u;
 #pragma unroll 1
-        for (uint32_t c = 0; c < ncols; c += 16u) {
+        for (uint32_t hc = 0; hc < (BM / 128u) * 2u; ++hc) {
+            const uint32_t half = hc >> 1, c = (hc & 1u) * 16u;
+            const int r = (int)(half * 128u + quarter * 32u + lane);
+            __half* zrow = a.z + op * a.z_op_stride + (size_t)(first + r) * a.N + nt * kBN + col0;
             uint32_t v[16];
             tmem_ld16(tmem + ((quarter * 32u) << 16) + half * 128u + col0 + c, v);
             if (r < rows) {
@@ -823,10 +824,11 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
     pa.xp = xp;
     pa.ops = 1;
     prep_rows_kernel<<<dim3(spread(p.rows, p.in / 128u), (p.rows + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(pa);
+    // 512-row tiles once they fill the GPU: the decode of a B tile is then shared by four accumulators
+    // (three accumulators and three stages, or two accumulators, measured no faster on calls this size)
+    const uint32_t bm = ((p.rows + 511u) / 512u) * (p.out / kBN) >= one_wave_ctas() ? 512u : 256u;
     CUtensorMap map;
     if (!make_a_map(&map, xp, p.rows, p.in, 256u)) return cudaErrorNotSupported;
-    // 512-row tiles once they fill the GPU: the decode of a B tile is then shared by four accumulators
-    const uint32_t bm = ((p.rows + 511u) / 512u) * (p.out / kBN) >= one_wave_ctas() ? 512u : 256u;
     GemmArgs g = {};
     g.trellis[0] = g.trellis[1] = p.trellis;
     g.K = p.in;
