@@ -78,3 +78,25 @@ def test_swiglu_host_arrays():
         tb.table().release(C.byref(w))
     blk.close()
     assert t3.device_error() == 0
+
+
+def test_pack_file_to_table_to_matmul(tmp_path):
+    """A trunk linear from a safetensors shard (the reference's affine names, i16 trellis) through the table's loader."""
+    from turboexl3_b200 import pack
+    in_dim, out_dim, n = 512, 256, 80
+    trellis, suh, svh = synth.linear(81, in_dim, out_dim, n, scaled=True)
+    pack.write_safetensors(str(tmp_path / "shard.safetensors"),
+                           {"attn.o.weight": trellis.view(np.int16), "attn.o.scales": suh, "attn.o.biases": svh})
+    pk = pack.Pack.open_dir(str(tmp_path))
+    blk = tb.Block(TRUNK)
+    v, w = blk.load_tensor(*pk.trunk("attn.o"), in_dim)
+    assert v.ok, v.why
+    x = synth.activations(82, 9, in_dim)
+    v, y = tb.matmul(w, x)
+    assert v.ok
+    want = t3.linear(torch.from_numpy(x).cuda(), torch.from_numpy(trellis).cuda(), torch.from_numpy(suh).cuda(),
+                     torch.from_numpy(svh).cuda())
+    assert np.array_equal(y.view(np.uint16), want.cpu().numpy().view(np.uint16))
+    tb.table().release(C.byref(w))
+    blk.close()
+    pk.close()
