@@ -136,6 +136,16 @@ int t3_moe_with_shared(const void* x, int x_dtype, size_t rows, const t3_bank* b
                        const void* scores, int scores_dtype, int topk, t3_decode dec, const void* shared, void* y,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* root.moeSwigluRows / moeClampedRows (src/root.zig:1007-1094): the routed chain at top-1 over GATHERED rows, for an expert
+ * streamer's prompt calls over its slot bank. Row-slot p reads x's row row_map[p] (x [x_rows, hidden]; row_map u32 [slots],
+ * each below x_rows: the caller's routing, not checked), runs the expert at slot inds[p] at weight scores[p], and y
+ * [slots, hidden] in y_dtype holds its output at row p. No gathered copy of x is made. Row p is, bit for bit, row p of
+ * t3_moe_swiglu at top-1 over the gathered rows, y rounded once to y_dtype. More than 32 row-slots (a caller pads a smaller
+ * call), else Exl3EngineNotImplemented; limit 0 (none) .. 128, else InvalidExl3Clamp. Workspace: t3_moe_workspace_bytes(slots, 1, bank). */
+int t3_moe_swiglu_rows(const void* x, int x_dtype, size_t x_rows, const void* row_map, size_t slots, const t3_bank* bank,
+                       const void* inds, const void* scores, int scores_dtype, t3_decode dec, int limit, int clamp_at,
+                       void* y, int y_dtype, void* workspace, size_t workspace_bytes, void* stream);
+
 /* t3_moe_with_shared for a shared-expert output that another stream is still computing: `shared_ready` is a cudaEvent_t
  * recorded on that stream after `shared` was written. Only the call's last launch (the one that adds `shared`) waits for
  * the event, so the routed experts' launches run beside the shared expert's. The reference's moeWithShared

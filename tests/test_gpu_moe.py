@@ -285,3 +285,32 @@ def test_expert_with_more_members_than_a_pass_serves():
         alone = t3.moe(x[:, 7:8].contiguous(), bank, dev(inds[7:8]).view(1, 1, topk), dev(scores[7:8]).view(1, 1, topk))
         assert np.array_equal(bits16(alone).reshape(-1), bits16(y).reshape(rows, H)[7])
     assert t3.device_error() == 0
+
+
+@pytest.mark.parametrize("xdt,ydt", [("f16", "f16"), ("bf16", "f32"), ("f32", "bf16")])
+def test_gathered_rows_chain_is_the_top1_chain_over_taken_rows(xdt, ydt):
+    """src/root.zig:1007-1019: row p of moeSwigluRows is, bit for bit, row p of moeSwiglu at top-1 over take(x, rows) in any
+    float dtype holding the same values, its y rounded once to out_dtype; here also against the oracle."""
+    H, I, E, n, S, N = 512, 256, 12, 64, 300, 40
+    bank, obank = make_bank(98, E, H, I, n)
+    rng = np.random.default_rng(99)
+    rows = rng.integers(0, N, S).astype(np.int32)
+    inds = rng.integers(0, E, S).astype(np.int32)
+    scores = rng.random(S).astype(np.float32) + 0.25
+    x16 = synth.activations(100, N, H)
+    x = x_as(x16, xdt)
+    for limit, clamp_at in ((0, t3.CLAMP_GATE_IN), (7, t3.CLAMP_GATE_IN), (7, t3.CLAMP_SILU_OUT)):
+        y = t3.moe_swiglu_rows(x, dev(rows), bank, dev(inds), dev(scores), t3.Decode.mul1, limit, clamp_at, TORCH_DT[ydt])
+        assert y.shape == (S, H) and y.dtype == TORCH_DT[ydt]
+        taken = x.float()[torch.from_numpy(rows).long().cuda()].view(1, S, H)  # f32 holds every dtype's values exactly
+        top1 = t3.moe_swiglu(taken, bank, dev(inds).view(1, S, 1), dev(scores).view(1, S, 1), t3.Decode.mul1, limit, clamp_at)
+        assert torch.equal(y, top1.view(S, H).to(TORCH_DT[ydt])), (limit, clamp_at)
+        sample = [0, 1, 150, 299]
+        ref = ob.moe_rows(obank, host_f32(x)[rows[sample]], inds[sample, None], scores[sample, None], ob.MUL1, 16,
+                          float(limit), clamp_at)
+        check_moe(host_f32(y)[sample], ref, ydt, ("rows chain", xdt, ydt, limit))
+    with pytest.raises(t3.Exl3Error, match="Exl3EngineNotImplemented"):
+        t3.moe_swiglu_rows(x, dev(rows[:20]), bank, dev(inds[:20]), dev(scores[:20]))
+    with pytest.raises(t3.Exl3Error, match="InvalidExl3Clamp"):
+        t3.moe_swiglu_rows(x, dev(rows), bank, dev(inds), dev(scores), t3.Decode.mul1, 129)
+    assert t3.device_error() == 0

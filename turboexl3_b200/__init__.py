@@ -6,11 +6,11 @@ been built (`python -m turboexl3_b200.build`).
 """
 from .api import (CLAMP_GATE_IN, CLAMP_SILU_OUT, DECODE_ROWS_MAX, MCG, MUL1, REDUCE_MAX_TOPK, Bank, Decode, Exl3Error,
                   Proj, codebook_table, configure, dequantize, device_error, engines_held, launch_count, lib, linear, linear_resident, moe,
-                  moe_clamped, moe_merge, moe_swiglu, moe_with_shared, parse_expert_quant, release_engines, resident_build,
+                  moe_clamped, moe_merge, moe_swiglu, moe_swiglu_rows, moe_with_shared, parse_expert_quant, release_engines, resident_build,
                   status_name, trellis_admitted)
 
 __all__ = ["CLAMP_GATE_IN", "CLAMP_SILU_OUT", "DECODE_ROWS_MAX", "MCG", "MUL1", "REDUCE_MAX_TOPK", "Bank", "Decode",
            "Exl3Error", "Proj", "codebook_table", "configure", "dequantize", "device_error", "engines_held", "launch_count", "lib", "linear_resident", "resident_build",
-           "linear", "moe", "moe_clamped", "moe_merge", "moe_swiglu", "moe_with_shared", "parse_expert_quant", "release_engines",
+           "linear", "moe", "moe_clamped", "moe_merge", "moe_swiglu", "moe_swiglu_rows", "moe_with_shared", "parse_expert_quant", "release_engines",
            "status_name",
            "trellis_admitted"]

@@ -76,6 +76,7 @@ SYMBOLS = {
     "t3_moe_swiglu": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _u32, _i, _vp, _vp, _sz, _vp]),
     "t3_moe_clamped": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _i, _vp, _vp, _sz, _vp]),
     "t3_moe_with_shared": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp, _vp, _sz, _vp]),
+    "t3_moe_swiglu_rows": (_i, [_vp, _i, _sz, _vp, _sz, C.POINTER(_Bank), _vp, _vp, _i, _Decode, _i, _i, _vp, _i, _vp, _sz, _vp]),
     "t3_moe_with_shared_after": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp, _vp, _vp, _sz, _vp]),
     "t3_moe_merge": (_i, [_vp, _vp, _i, _sz, _i, _i, _vp, _vp, _i, _vp]),
     "t3_moe_noalloc": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp]),
@@ -346,6 +347,30 @@ def moe(x, bank: Bank, inds, scores, dec: Decode = Decode.mul1, verify_rows: boo
     """root.moe (src/root.zig:822-825): x [B, S, D], inds/scores [B, S, K]; y in x's shape and dtype."""
     del verify_rows  # accepted and ignored, as the reference does
     return _moe(x, bank, inds, scores, dec, 0, CLAMP_GATE_IN, None, "moe")
+
+
+def moe_swiglu_rows(x: torch.Tensor, rows: torch.Tensor, bank: Bank, inds: torch.Tensor, scores: torch.Tensor,
+                    dec: Decode = Decode.mul1, limit: int = 0, clamp_at: int = CLAMP_GATE_IN,
+                    out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """root.moeSwigluRows (src/root.zig:1007-1021; moeClampedRows at limit 1..128): x [n, hidden], rows u32/i32 [S], inds
+    [S], scores [S]; y [S, hidden] in out_dtype (default x's)."""
+    _need_cuda(x, rows, inds, scores)
+    if x.dim() != 2 or rows.dim() != 1 or rows.shape != inds.shape or rows.shape != scores.shape or x.shape[1] % 128:
+        raise Exl3Error(1, "BadExl3Shape")
+    out_dtype = out_dtype or x.dtype
+    if (x.dtype not in _DTYPES or out_dtype not in _DTYPES or rows.dtype not in (torch.int32, torch.uint32)
+            or inds.dtype not in (torch.int32, torch.uint32) or scores.dtype not in _DTYPES):
+        raise Exl3Error(2, "BadExl3Dtype")
+    cb = _bank_c(bank, x.shape[1])
+    S = rows.shape[0]
+    L = lib()
+    ws_bytes = L.t3_moe_workspace_bytes(S, 1, C.byref(cb))
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x.device)
+    y = torch.empty((S, x.shape[1]), dtype=out_dtype, device=x.device)
+    _check(L.t3_moe_swiglu_rows(x.data_ptr(), _DTYPES[x.dtype], x.shape[0], rows.data_ptr(), S, C.byref(cb), inds.data_ptr(),
+                                scores.data_ptr(), _DTYPES[scores.dtype], dec._c(), limit, clamp_at, y.data_ptr(),
+                                _DTYPES[out_dtype], ws.data_ptr(), ws_bytes, _stream_ptr(x)))
+    return y
 
 
 def moe_merge(v: torch.Tensor, scores: torch.Tensor, out_dtype: torch.dtype, shared=None) -> torch.Tensor:

@@ -513,6 +513,7 @@ int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const
     const size_t slots = rows * (size_t)topk;
     a.y = y;
     a.shared = shared;
+    a.y_dt = x_dtype;
     a.shared_ready = shared_ready;
     a.err = dev_error_ptr();
     note_engine(rows > T3_DECODE_ROWS_MAX ? 2 : 0, ((uint64_t)a.hidden << 32) | a.inter, a.experts, a.n, a.topk);
@@ -619,6 +620,61 @@ int t3_moe_with_shared(const void* x, int x_dtype, size_t rows, const t3_bank* b
     if (!shared) return T3_NULL_POINTER;
     return moe_call(x, x_dtype, rows, bank, inds, scores, scores_dtype, topk, dec, 0, T3_CLAMP_GATE_IN, shared, y,
                     workspace, workspace_bytes, stream);
+}
+
+int t3_moe_swiglu_rows(const void* x, int x_dtype, size_t x_rows, const void* row_map, size_t slots, const t3_bank* bank,
+                       const void* inds, const void* scores, int scores_dtype, t3_decode dec, int limit, int clamp_at,
+                       void* y, int y_dtype, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!x || !row_map || !inds || !scores || !y) return T3_NULL_POINTER;
+    if (limit < 0 || limit > 128) return T3_INVALID_CLAMP;                       // src/root.zig:1058
+    if (clamp_at != T3_CLAMP_GATE_IN && clamp_at != T3_CLAMP_SILU_OUT) return T3_INVALID_CLAMP;
+    if (x_rows < 1 || slots < 1 || slots > (size_t)1 << 30) return T3_BAD_EXL3_SHAPE;
+    if (int rc = validate_bank(bank, bank ? bank->hidden : 0)) return rc;
+    if (!dtype_ok(x_dtype) || !dtype_ok(scores_dtype) || !dtype_ok(y_dtype)) return T3_BAD_EXL3_DTYPE;
+    t3_config cfg;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        cfg = g_cfg;
+    }
+    if (!cfg.prefill || slots <= T3_DECODE_ROWS_MAX) return T3_ENGINE_NOT_IMPLEMENTED;  // src/root.zig:1059,1066
+    if (bank->n_gate != bank->n_down) return T3_ENGINE_NOT_IMPLEMENTED;                 // src/root.zig:1074
+    if (slots > 0x7FFFFFFFu / (size_t)(bank->hidden > bank->inter ? bank->hidden : bank->inter)) return T3_BAD_EXL3_SHAPE;
+    uint32_t mask;
+    if (int rc = decode_mask(dec, mask)) return rc;
+    if (!workspace || workspace_bytes < t3_moe_workspace_bytes(slots, 1, bank)) return T3_WORKSPACE_TOO_SMALL;
+    MoeArgs a = {};
+    a.x = x;
+    a.x_dt = x_dtype;
+    a.inds = inds;
+    a.scores = scores;
+    a.score_dt = scores_dtype;
+    a.gate_t = static_cast<const uint8_t*>(bank->gate.trellis);
+    a.up_t = static_cast<const uint8_t*>(bank->up.trellis);
+    a.down_t = static_cast<const uint8_t*>(bank->down.trellis);
+    a.gate_suh = bank->gate.suh;
+    a.gate_svh = bank->gate.svh;
+    a.up_suh = bank->up.suh;
+    a.up_svh = bank->up.svh;
+    a.down_suh = bank->down.suh;
+    a.down_svh = bank->down.svh;
+    a.experts = (uint32_t)bank->experts;
+    a.hidden = (uint32_t)bank->hidden;
+    a.inter = (uint32_t)bank->inter;
+    a.topk = 1;
+    a.rows = (uint32_t)slots;
+    a.n = (uint32_t)bank->n_gate;
+    a.mask = mask;
+    a.limit = (float)limit;
+    a.clamp_at = clamp_at;
+    a.y = y;
+    a.y_dt = y_dtype;
+    a.row_map = static_cast<const uint32_t*>(row_map);
+    a.err = dev_error_ptr();
+    note_engine(2, ((uint64_t)a.hidden << 32) | a.inter, a.experts, a.n, 1);
+    int launches = 0;
+    const cudaError_t rc = launch_prefill_moe(a, workspace, dec.codebook, static_cast<cudaStream_t>(stream), &launches);
+    g_launches.fetch_add((uint64_t)launches, std::memory_order_relaxed);
+    return cuda_status(rc);
 }
 
 int t3_moe_with_shared_after(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds,

@@ -44,6 +44,8 @@ struct MoeArgs {
     void* v;                  // scratch f16 [rows * topk, hidden]: each row-slot's finished down output
     void* y;                  // [rows, hidden], dtype x_dt
     const void* shared;       // optional [rows, hidden] dtype x_dt added at y's rounding point, or null
+    const uint32_t* row_map;  // prefill rows only: row-slot p reads x's row row_map[p] (top-1 over gathered rows), or null
+    int y_dt;                 // prefill rows only: y's dtype (the decode-row chain stores y in x_dt)
     void* shared_ready;       // host side only: an event the last launch (the one that reads `shared`) waits for, or null
     uint32_t row_cap;                  // rows one pass over an expert's weights serves (8, 16 or 32): experts with more members take more passes
     uint32_t split_gu, slice_max_gu;   // K slices of gate|up (cluster = 2 * split_gu), largest slice

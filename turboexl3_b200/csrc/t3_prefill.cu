@@ -542,6 +542,7 @@ struct PrepArgs {
     const __half* suh[2];
     uint32_t K, positions, topk, experts, ops;
     const uint32_t *order, *inds;  // null for a dense linear
+    const uint32_t* row_map;       // routed: the x row of each row-slot when the call gathers rows, else slot / topk
     __half* xp;                    // [ops][positions][K]
 };
 __global__ void __launch_bounds__(256) prep_rows_kernel(const PrepArgs a) {
@@ -552,7 +553,7 @@ __global__ void __launch_bounds__(256) prep_rows_kernel(const PrepArgs a) {
     uint32_t row = p, e = 0;
     if (a.order) {
         const uint32_t slot = a.order[p];
-        row = slot / a.topk;
+        row = a.row_map ? a.row_map[slot] : slot / a.topk;
         e = min(a.inds[slot], a.experts - 1u);
     }
     const HadB hb = had_b(lane);
@@ -915,6 +916,7 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
     pa.experts = a.experts;
     pa.order = w.order;
     pa.inds = inds;
+    pa.row_map = a.row_map;
     pa.xp = w.xp;
     pa.ops = 2;
     prep_rows_kernel<<<dim3(spread(S, H / 128u), (S + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(pa);
@@ -958,7 +960,7 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
     rc = launch_gemm(map_d, d, w.max_tiles, kMoeBM, codebook, stream);
     if (rc != cudaSuccess) return rc;
 
-    FinArgs f = {w.zd, static_cast<const __half*>(a.down_svh), w.inv, inds, a.scores, a.score_dt, a.shared, a.y, a.x_dt,
+    FinArgs f = {w.zd, static_cast<const __half*>(a.down_svh), w.inv, inds, a.scores, a.score_dt, a.shared, a.y, a.y_dt,
                  a.rows, H, a.topk, a.experts};
     if (a.shared_ready) {  // only this launch reads `shared`
         rc = cudaStreamWaitEvent(stream, static_cast<cudaEvent_t>(a.shared_ready), 0);
