@@ -13,7 +13,7 @@
 //             Apple / gfx11 matrix units.)
 //   mid     : gate and up finish, SwiGLU, the down projection's prepare (src/kernels/hip/routed.hpp:64-112)
 //   fin     : per row, every slot's down finish and the score-weighted sum in slot order
-//             (src/kernels/hip/prefill/prefill.hip:243-264); dense linears use the plain finish.
+//             (src/kernels/hip/prefill/prefill.hip:243-264); a dense linear's finish runs in its GEMM's epilogue.
 // Every wait is bounded: a wait that runs out sets a bit of the device error word and the kernel walks to its exit,
 // freeing its tensor memory on the way.
 #include <cuda.h>
@@ -131,6 +131,110 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- the 128-point Hadamard on tensor cores (prepare / mid / finish kernels and the dense GEMM's epilogue) --------------------
+//
+// The 128-point Hadamards of these kernels run on the tensor cores. The sign of entry (i, j) of H128 is the parity of
+// popcount(i & j), which splits over the bit fields of i = 16 i8 + i16, so H128 = H8 (x) H16 and a block viewed as an
+// 8 x 16 matrix X becomes H8 . X . H16: X . H16 is m16n8k16 steps against a constant +-1 fragment, H8 a three-level
+// butterfly over values one thread already holds. A warp works on EIGHT positions at a time, one 128-block each: quad g
+// (lanes 4g .. 4g + 3) owns position g, and lane q of the quad holds, for every i8, the four elements 16 i8 + 4q .. + 3:
+// one 8-byte (f16) or 16-byte (f32) access per i8 on the way in and on the way out. The butterfly on a warp costs twenty
+// shuffles per block, and the shuffle unit (one warp instruction per SM per cycle) bounded these kernels; this form has none.
+// f32 accumulation of +-1 products is exact per term, so the result differs from the butterfly (and from the oracle's
+// dense sum) only in summation order, as before.
+
+struct HadB {
+    uint32_t b[2][2];  // the +-1 H16 fragment of each 8-column half (t): {k 0-7 part, k 8-15 part}
+};
+
+// Matrix index <-> element maps (both free to choose): A/B index k of thread q covers elements 4q, 4q+1 (k = 2q, 2q+1) and
+// 4q+2, 4q+3 (k = 2q+8, 2q+9); output column n = 2q+b of half t is element 4q + 2t + b. So a thread's inputs and outputs
+// are the same four consecutive elements.
+__device__ __forceinline__ HadB had_b(uint32_t lane) {
+    const uint32_t g = lane >> 2, q = lane & 3u;
+    HadB h;
+#pragma unroll
+    for (uint32_t t = 0; t < 2u; ++t) {
+        const uint32_t en = 4u * (g >> 1) + 2u * t + (g & 1u);
+        uint32_t s[4];
+#pragma unroll
+        for (uint32_t b = 0; b < 4u; ++b) s[b] = (__popc((4u * q + b) & en) & 1) ? 0xBC00u : 0x3C00u;
+        h.b[t][0] = s[0] | (s[1] << 16);
+        h.b[t][1] = s[2] | (s[3] << 16);
+    }
+    return h;
+}
+
+// out[i8][e] = sum over the block of sign * value, for the position this quad owns. a[i8] = the four f16 values
+// {16 i8 + 4q .. + 3} as two packed pairs; a second set (the f16 remainders of values that are not f16 themselves) is
+// accumulated into the same sums when `use_lo` is set.
+__device__ __forceinline__ void h128_mma(const uint32_t (&a)[8][2], const uint32_t (&lo)[8][2], bool use_lo,
+                                         const HadB& hb, float (&out)[8][4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            mma16816(c, a[2 * j][0], a[2 * j + 1][0], a[2 * j][1], a[2 * j + 1][1], hb.b[t][0], hb.b[t][1]);
+            if (use_lo) mma16816(c, lo[2 * j][0], lo[2 * j + 1][0], lo[2 * j][1], lo[2 * j + 1][1], hb.b[t][0], hb.b[t][1]);
+            out[2 * j][2 * t] = c[0], out[2 * j][2 * t + 1] = c[1];
+            out[2 * j + 1][2 * t] = c[2], out[2 * j + 1][2 * t + 1] = c[3];
+        }
+#pragma unroll
+    for (int bit = 1; bit < 8; bit <<= 1)
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (!(i & bit))
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float lo_v = out[i][e], hi_v = out[i | bit][e];
+                    out[i][e] = lo_v + hi_v;
+                    out[i | bit][e] = lo_v - hi_v;
+                }
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// v (f32 values, not necessarily f16) as an f16 part and the f16 of what is left; returns nonzero when any remainder is
+__device__ __forceinline__ uint32_t split4(const float (&v)[4], uint32_t (&hi)[2], uint32_t (&lo)[2]) {
+    float r[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) r[j] = v[j] - round_half(v[j]);
+    hi[0] = pack_half2(v[0], v[1]), hi[1] = pack_half2(v[2], v[3]);
+    lo[0] = pack_half2(r[0], r[1]), lo[1] = pack_half2(r[2], r[3]);
+    return (lo[0] | lo[1]) & 0x7FFF7FFFu;
+}
+
+// H128 of the block whose values are `v` (v[i8] = elements 16 i8 + 4q .. + 3), any f32 values
+__device__ __forceinline__ void h128_split(const float (&v)[8][4], const HadB& hb, float (&out)[8][4]) {
+    uint32_t hi[8][2], lo[8][2], rest = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) rest |= split4(v[i], hi[i], lo[i]);
+    h128_mma(hi, lo, __any_sync(0xFFFFFFFFu, rest != 0u) != 0, hb, out);
+}
+
+// The output rotation of one block (format.finishOutput, format.zig:370-380): z and sv point at this lane's first
+// element (block start + 4q); out = f16(H128(z) / sqrt(128) * sv).
+__device__ __forceinline__ void finish_block_mma(const __half* z, const __half* sv, const HadB& hb, float (&out)[8][4]) {
+    uint32_t a[8][2];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint2 u = *reinterpret_cast<const uint2*>(z + 16 * i);
+        a[i][0] = u.x, a[i][1] = u.y;
+    }
+    h128_mma(a, a, false, hb, out);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float sc[4];
+        load_half4(sv + 16 * i, sc);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) out[i][e] = round_half(out[i][e] * kHadScale * sc[e]);
+    }
+}
+
 // ---- the GEMM ------------------------------------------------------------------------------------------------------
 
 struct GemmArgs {
@@ -143,6 +247,9 @@ struct GemmArgs {
     uint32_t dense_rows;
     __half* z;                  // [ops][z_rows][N]
     size_t z_op_stride;         // elements between the ops' outputs
+    const __half* svh;          // dense linears: finish in the epilogue (the CTA's 128 columns are one rotation block) into y
+    void* y;                    // [rows][N], dtype y_dt; z is not written then
+    int y_dt;
     uint32_t* err;
 };
 
@@ -328,6 +435,45 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
         // every accumulator's lane quarter `quarter`, columns 32 grp .. + 31 of its 128
         const uint32_t quarter = warp & 3u, grp = dw >> 2;  // grp 0..3
         const uint32_t col0 = grp * 32u;
+        if (BM >= 256 && a.svh != nullptr) {
+            // Fused finish (format.finishOutput): the accumulators go to shared memory as f16 (the operand stages are
+            // free: every MMA and every copy has completed), then a warp takes eight rows at a time through the
+            // tensor-core Hadamard, scales by svh, rounds and stores y.
+            constexpr uint32_t kZStride = 128u + 8u;  // halfs a row: 16-byte aligned rows, staggered over the banks
+            __half* ztile = reinterpret_cast<__half*>(smem);
+#pragma unroll 1
+            for (uint32_t hc = 0; hc < (BM / 128u) * 2u; ++hc) {
+                const uint32_t half = hc >> 1, c = (hc & 1u) * 16u;
+                const uint32_t r = half * 128u + quarter * 32u + lane;
+                uint32_t v[16];
+                tmem_ld16(tmem + ((quarter * 32u) << 16) + half * 128u + col0 + c, v);
+                uint32_t packed[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const __half2 h = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                    packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(ztile + r * kZStride + col0 + c);
+                dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            }
+            tc_fence_before();
+            named_sync(2, kDecodeWarps * 32u);
+            const HadB hb = had_b(lane);
+            const uint32_t pg = lane >> 2, pq = lane & 3u;
+            const __half* sv = a.svh + nt * kBN + 4u * pq;
+#pragma unroll 1
+            for (uint32_t g8 = dw; g8 < BM / 8u; g8 += kDecodeWarps) {
+                const uint32_t r = g8 * 8u + pg;
+                float out[8][4];
+                finish_block_mma(ztile + r * kZStride + 4u * pq, sv, hb, out);
+                if ((int)r < rows) {
+                    const size_t o = (size_t)(first + (int)r) * a.N + nt * kBN + 4u * pq;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) store_act4(a.y, a.y_dt, o + 16u * i, out[i]);
+                }
+            }
+        } else
 #pragma unroll 1
         for (uint32_t hc = 0; hc < (BM / 128u) * 2u; ++hc) {
             const uint32_t half = hc >> 1, c = (hc & 1u) * 16u;
@@ -412,108 +558,6 @@ __global__ void route_scatter_kernel(const uint32_t* inds, uint32_t slots, uint3
 }
 
 // ---- prepare / mid / finish ------------------------------------------------------------------------------------------
-//
-// The 128-point Hadamards of these kernels run on the tensor cores. The sign of entry (i, j) of H128 is the parity of
-// popcount(i & j), which splits over the bit fields of i = 16 i8 + i16, so H128 = H8 (x) H16 and a block viewed as an
-// 8 x 16 matrix X becomes H8 . X . H16: X . H16 is m16n8k16 steps against a constant +-1 fragment, H8 a three-level
-// butterfly over values one thread already holds. A warp works on EIGHT positions at a time, one 128-block each: quad g
-// (lanes 4g .. 4g + 3) owns position g, and lane q of the quad holds, for every i8, the four elements 16 i8 + 4q .. + 3:
-// one 8-byte (f16) or 16-byte (f32) access per i8 on the way in and on the way out. The butterfly on a warp costs twenty
-// shuffles per block, and the shuffle unit (one warp instruction per SM per cycle) bounded these kernels; this form has none.
-// f32 accumulation of +-1 products is exact per term, so the result differs from the butterfly (and from the oracle's
-// dense sum) only in summation order, as before.
-
-struct HadB {
-    uint32_t b[2][2];  // the +-1 H16 fragment of each 8-column half (t): {k 0-7 part, k 8-15 part}
-};
-
-// Matrix index <-> element maps (both free to choose): A/B index k of thread q covers elements 4q, 4q+1 (k = 2q, 2q+1) and
-// 4q+2, 4q+3 (k = 2q+8, 2q+9); output column n = 2q+b of half t is element 4q + 2t + b. So a thread's inputs and outputs
-// are the same four consecutive elements.
-__device__ __forceinline__ HadB had_b(uint32_t lane) {
-    const uint32_t g = lane >> 2, q = lane & 3u;
-    HadB h;
-#pragma unroll
-    for (uint32_t t = 0; t < 2u; ++t) {
-        const uint32_t en = 4u * (g >> 1) + 2u * t + (g & 1u);
-        uint32_t s[4];
-#pragma unroll
-        for (uint32_t b = 0; b < 4u; ++b) s[b] = (__popc((4u * q + b) & en) & 1) ? 0xBC00u : 0x3C00u;
-        h.b[t][0] = s[0] | (s[1] << 16);
-        h.b[t][1] = s[2] | (s[3] << 16);
-    }
-    return h;
-}
-
-// out[i8][e] = sum over the block of sign * value, for the position this quad owns. a[i8] = the four f16 values
-// {16 i8 + 4q .. + 3} as two packed pairs; a second set (the f16 remainders of values that are not f16 themselves) is
-// accumulated into the same sums when `use_lo` is set.
-__device__ __forceinline__ void h128_mma(const uint32_t (&a)[8][2], const uint32_t (&lo)[8][2], bool use_lo,
-                                         const HadB& hb, float (&out)[8][4]) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            mma16816(c, a[2 * j][0], a[2 * j + 1][0], a[2 * j][1], a[2 * j + 1][1], hb.b[t][0], hb.b[t][1]);
-            if (use_lo) mma16816(c, lo[2 * j][0], lo[2 * j + 1][0], lo[2 * j][1], lo[2 * j + 1][1], hb.b[t][0], hb.b[t][1]);
-            out[2 * j][2 * t] = c[0], out[2 * j][2 * t + 1] = c[1];
-            out[2 * j + 1][2 * t] = c[2], out[2 * j + 1][2 * t + 1] = c[3];
-        }
-#pragma unroll
-    for (int bit = 1; bit < 8; bit <<= 1)
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-            if (!(i & bit))
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float lo_v = out[i][e], hi_v = out[i | bit][e];
-                    out[i][e] = lo_v + hi_v;
-                    out[i | bit][e] = lo_v - hi_v;
-                }
-}
-
-__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
-    const __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<const uint32_t*>(&h);
-}
-
-// v (f32 values, not necessarily f16) as an f16 part and the f16 of what is left; returns nonzero when any remainder is
-__device__ __forceinline__ uint32_t split4(const float (&v)[4], uint32_t (&hi)[2], uint32_t (&lo)[2]) {
-    float r[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) r[j] = v[j] - round_half(v[j]);
-    hi[0] = pack_half2(v[0], v[1]), hi[1] = pack_half2(v[2], v[3]);
-    lo[0] = pack_half2(r[0], r[1]), lo[1] = pack_half2(r[2], r[3]);
-    return (lo[0] | lo[1]) & 0x7FFF7FFFu;
-}
-
-// H128 of the block whose values are `v` (v[i8] = elements 16 i8 + 4q .. + 3), any f32 values
-__device__ __forceinline__ void h128_split(const float (&v)[8][4], const HadB& hb, float (&out)[8][4]) {
-    uint32_t hi[8][2], lo[8][2], rest = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) rest |= split4(v[i], hi[i], lo[i]);
-    h128_mma(hi, lo, __any_sync(0xFFFFFFFFu, rest != 0u) != 0, hb, out);
-}
-
-// The output rotation of one block (format.finishOutput, format.zig:370-380): z and sv point at this lane's first
-// element (block start + 4q); out = f16(H128(z) / sqrt(128) * sv).
-__device__ __forceinline__ void finish_block_mma(const __half* z, const __half* sv, const HadB& hb, float (&out)[8][4]) {
-    uint32_t a[8][2];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint2 u = *reinterpret_cast<const uint2*>(z + 16 * i);
-        a[i][0] = u.x, a[i][1] = u.y;
-    }
-    h128_mma(a, a, false, hb, out);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        float sc[4];
-        load_half4(sv + 16 * i, sc);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) out[i][e] = round_half(out[i][e] * kHadScale * sc[e]);
-    }
-}
 
 constexpr uint32_t kRowsPerCta = 64;  // 8 warps x 8 positions
 
@@ -583,30 +627,6 @@ __global__ void __launch_bounds__(256) prep_rows_kernel(const PrepArgs a) {
                 }
             }
         }
-    }
-}
-
-// grid (spread, ceil(rows / 64)): the plain finish of a dense linear
-struct FinishArgs {
-    const __half* z;
-    const __half* svh;
-    void* y;
-    int y_dt;
-    uint32_t rows, out;
-};
-__global__ void __launch_bounds__(256) finish_rows_kernel(const FinishArgs a) {
-    const uint32_t lane = threadIdx.x & 31u, q = lane & 3u;
-    uint32_t row;
-    bool live;
-    if (!my_position(a.rows, lane, row, live)) return;
-    const HadB hb = had_b(lane);
-    for (uint32_t blk = blockIdx.x; blk < (a.out >> 7); blk += gridDim.x) {
-        const size_t o = (size_t)row * a.out + blk * 128u + 4u * q;
-        float v[8][4];
-        finish_block_mma(a.z + o, a.svh + blk * 128u + 4u * q, hb, v);
-        if (live)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) store_act4(a.y, a.y_dt, o + 16u * i, v[i]);
     }
 }
 
@@ -839,6 +859,9 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
     g.ops = 1;
     g.dense_rows = p.rows;
     g.z = z;
+    g.svh = static_cast<const __half*>(p.svh);
+    g.y = p.y;
+    g.y_dt = p.x_dt;
     g.err = p.err;
     cudaError_t rc;
     if (p.resident) {
@@ -850,9 +873,7 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
         rc = launch_gemm(map, g, (p.rows + bm - 1u) / bm, bm, codebook, stream);
     }
     if (rc != cudaSuccess) return rc;
-    FinishArgs f = {z, static_cast<const __half*>(p.svh), p.y, p.x_dt, p.rows, p.out};
-    finish_rows_kernel<<<dim3(spread(p.rows, p.out / 128u), (p.rows + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(f);
-    *launches += 3;
+    *launches += 2;  // the output rotation runs in the GEMM's epilogue
     return cudaGetLastError();
 }
 
