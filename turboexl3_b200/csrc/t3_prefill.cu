@@ -247,8 +247,12 @@ struct GemmArgs {
     uint32_t dense_rows;
     __half* z;                  // [ops][z_rows][N]
     size_t z_op_stride;         // elements between the ops' outputs
-    const __half* svh;          // dense linears: finish in the epilogue (the CTA's 128 columns are one rotation block) into y
-    void* y;                    // [rows][N], dtype y_dt; z is not written then
+    // The output rotation in the epilogue (the CTA's 128 columns are one rotation block): svh[op] + expert * svh_stride is
+    // the op's scale vector; the finished values go to y (dtype y_dt) when it is given, else to z as f16. Null svh[0]: the raw
+    // inner products go to z.
+    const __half* svh[2];
+    size_t svh_stride;
+    void* y;                    // [rows][N], one op
     int y_dt;
     uint32_t* err;
 };
@@ -435,7 +439,7 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
         // every accumulator's lane quarter `quarter`, columns 32 grp .. + 31 of its 128
         const uint32_t quarter = warp & 3u, grp = dw >> 2;  // grp 0..3
         const uint32_t col0 = grp * 32u;
-        if (BM >= 256 && a.svh != nullptr) {
+        if (a.svh[0] != nullptr) {
             // Fused finish (format.finishOutput): the accumulators go to shared memory as f16 (the operand stages are
             // free: every MMA and every copy has completed), then a warp takes eight rows at a time through the
             // tensor-core Hadamard, scales by svh, rounds and stores y.
@@ -461,16 +465,18 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
             named_sync(2, kDecodeWarps * 32u);
             const HadB hb = had_b(lane);
             const uint32_t pg = lane >> 2, pq = lane & 3u;
-            const __half* sv = a.svh + nt * kBN + 4u * pq;
+            const __half* sv = (op ? a.svh[1] : a.svh[0]) + (size_t)e * a.svh_stride + nt * kBN + 4u * pq;
+            void* const dst = a.y ? a.y : static_cast<void*>(a.z);
+            const int dst_dt = a.y ? a.y_dt : (int)kF16;
 #pragma unroll 1
             for (uint32_t g8 = dw; g8 < BM / 8u; g8 += kDecodeWarps) {
                 const uint32_t r = g8 * 8u + pg;
                 float out[8][4];
                 finish_block_mma(ztile + r * kZStride + 4u * pq, sv, hb, out);
                 if ((int)r < rows) {
-                    const size_t o = (size_t)(first + (int)r) * a.N + nt * kBN + 4u * pq;
+                    const size_t o = op * a.z_op_stride + (size_t)(first + (int)r) * a.N + nt * kBN + 4u * pq;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) store_act4(a.y, a.y_dt, o + 16u * i, out[i]);
+                    for (int i = 0; i < 8; ++i) store_act4(dst, dst_dt, o + 16u * i, out[i]);
                 }
             }
         } else
@@ -640,10 +646,11 @@ __device__ __forceinline__ float swiglu_f32(float g, float u, float limit, int c
     return s * u;
 }
 
-// grid (spread, ceil(P / 64)): gate and up finish, SwiGLU, the down projection's prepare, per sorted position
+// grid (spread, ceil(P / 64)): SwiGLU of the finished gate and up values (the GEMM's epilogue finished them) and the
+// down projection's prepare, per sorted position
 struct MidArgs {
-    const __half* z;  // [2][P][inter]
-    const __half *gate_svh, *up_svh, *down_suh;
+    const __half* z;  // [2][P][inter]: finished gate, finished up
+    const __half* down_suh;
     const uint32_t *order, *inds;
     uint32_t positions, inter, experts;
     float limit;
@@ -660,8 +667,11 @@ __global__ void __launch_bounds__(256) mid_kernel(const MidArgs a) {
     for (uint32_t blk = blockIdx.x; blk < (a.inter >> 7); blk += gridDim.x) {
         const size_t eo = (size_t)e * a.inter + blk * 128u + 4u * q, zo = (size_t)p * a.inter + blk * 128u + 4u * q;
         float g[8][4], u[8][4];
-        finish_block_mma(a.z + zo, a.gate_svh + eo, hb, g);
-        finish_block_mma(a.z + (size_t)a.positions * a.inter + zo, a.up_svh + eo, hb, u);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            load_half4(a.z + zo + 16 * i, g[i]);
+            load_half4(a.z + (size_t)a.positions * a.inter + zo + 16 * i, u[i]);
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             float sd[4];
@@ -680,57 +690,51 @@ __global__ void __launch_bounds__(256) mid_kernel(const MidArgs a) {
     }
 }
 
-// grid (spread, ceil(rows / 64)): per row, each slot's down finish (through inv) and the score-weighted sum in slot
-// order, then the optional shared-expert add in the output dtype
+// grid (spread, ceil(rows / 64)): per row, the score-weighted sum of its slots' finished down outputs (through inv) in
+// slot order, then the optional shared-expert add in the output dtype
 struct FinArgs {
-    const __half* zd;  // [P][hidden]
-    const __half* down_svh;
-    const uint32_t *inv, *inds;
+    const __half* zd;  // [P][hidden]: each sorted position's finished down output (the per-slot v)
+    const uint32_t* inv;
     const void* scores;
     int score_dt;
     const void* shared;
     void* y;
     int y_dt;
-    uint32_t rows, hidden, topk, experts;
+    uint32_t rows, hidden, topk;
 };
 __global__ void __launch_bounds__(256) moe_fin_kernel(const FinArgs a) {
-    const uint32_t lane = threadIdx.x & 31u, q = lane & 3u;
-    uint32_t row;
-    bool live;
-    if (!my_position(a.rows, lane, row, live)) return;
-    const HadB hb = had_b(lane);
+    // a warp a row, a lane four consecutive elements of a 128-block: every slot's 256 bytes are one coalesced read
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t row = blockIdx.y * 8u + warp;
+    if (row >= a.rows) return;
     for (uint32_t blk = blockIdx.x; blk < (a.hidden >> 7); blk += gridDim.x) {
-        const uint32_t col = blk * 128u + 4u * q;
-        float acc[8][4];
+        const uint32_t col = blk * 128u + 4u * lane;
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (uint32_t k0 = 0; k0 < a.topk; k0 += 4u) {  // four slots' loads in flight, the sum still in slot order
+            float w[4], v[4][4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
-        for (uint32_t k = 0; k < a.topk; ++k) {
-            const size_t slot = (size_t)row * a.topk + k;
-            const uint32_t p = a.inv[slot], e = min(a.inds[slot], a.experts - 1u);
-            const float w = load_act(a.scores, a.score_dt, slot);
-            float v[8][4];
-            finish_block_mma(a.zd + (size_t)p * a.hidden + col, a.down_svh + (size_t)e * a.hidden + col, hb, v);
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(w, v[i][j]));
-        }
-        if (!live) continue;
-        const size_t o = (size_t)row * a.hidden + col;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            if (a.shared) {
-                float t[4], sh[4];
-                store_act4(a.y, a.y_dt, o + 16u * i, acc[i]);  // the routed output's rounding point
-                load_act4(a.y, a.y_dt, o + 16u * i, t);
-                load_act4(a.shared, a.y_dt, o + 16u * i, sh);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = __fadd_rn(t[j], sh[j]);
+            for (uint32_t i = 0; i < 4u; ++i) {
+                const uint32_t k = k0 + i < a.topk ? k0 + i : a.topk - 1u;
+                const size_t slot = (size_t)row * a.topk + k;
+                w[i] = load_act(a.scores, a.score_dt, slot);
+                load_half4(a.zd + (size_t)a.inv[slot] * a.hidden + col, v[i]);
             }
-            store_act4(a.y, a.y_dt, o + 16u * i, acc[i]);
+#pragma unroll
+            for (uint32_t i = 0; i < 4u; ++i)
+                if (k0 + i < a.topk)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[j] = __fadd_rn(acc[j], __fmul_rn(w[i], v[i][j]));
         }
+        const size_t o = (size_t)row * a.hidden + col;
+        if (a.shared) {
+            float t[4], sh[4];
+            store_act4(a.y, a.y_dt, o, acc);  // the routed output's rounding point
+            load_act4(a.y, a.y_dt, o, t);
+            load_act4(a.shared, a.y_dt, o, sh);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[j] = __fadd_rn(t[j], sh[j]);
+        }
+        store_act4(a.y, a.y_dt, o, acc);
     }
 }
 
@@ -859,7 +863,7 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
     g.ops = 1;
     g.dense_rows = p.rows;
     g.z = z;
-    g.svh = static_cast<const __half*>(p.svh);
+    g.svh[0] = g.svh[1] = static_cast<const __half*>(p.svh);
     g.y = p.y;
     g.y_dt = p.x_dt;
     g.err = p.err;
@@ -959,12 +963,14 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
     g.tiles = w.tiles;
     g.z = w.zgu;
     g.z_op_stride = slots * I;
+    g.svh[0] = static_cast<const __half*>(a.gate_svh);  // the epilogue finishes gate and up with the tile's expert's scales
+    g.svh[1] = static_cast<const __half*>(a.up_svh);
+    g.svh_stride = I;
     g.err = a.err;
     rc = launch_gemm(map_gu, g, w.max_tiles, kMoeBM, codebook, stream);
     if (rc != cudaSuccess) return rc;
 
-    MidArgs m = {w.zgu, static_cast<const __half*>(a.gate_svh), static_cast<const __half*>(a.up_svh),
-                 static_cast<const __half*>(a.down_suh), w.order, inds, S, I, a.experts, a.limit, a.clamp_at, w.hd};
+    MidArgs m = {w.zgu, static_cast<const __half*>(a.down_suh), w.order, inds, S, I, a.experts, a.limit, a.clamp_at, w.hd};
     mid_kernel<<<dim3(spread(S, I / 128u), (S + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(m);
 
     GemmArgs d = {};
@@ -977,17 +983,19 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
     d.ops = 1;
     d.tiles = w.tiles;
     d.z = w.zd;
+    d.svh[0] = d.svh[1] = static_cast<const __half*>(a.down_svh);  // each slot's finished down output, the per-slot v
+    d.svh_stride = H;
     d.err = a.err;
     rc = launch_gemm(map_d, d, w.max_tiles, kMoeBM, codebook, stream);
     if (rc != cudaSuccess) return rc;
 
-    FinArgs f = {w.zd, static_cast<const __half*>(a.down_svh), w.inv, inds, a.scores, a.score_dt, a.shared, a.y, a.y_dt,
-                 a.rows, H, a.topk, a.experts};
+    FinArgs f = {w.zd, w.inv, a.scores, a.score_dt, a.shared, a.y, a.y_dt, a.rows, H, a.topk};
     if (a.shared_ready) {  // only this launch reads `shared`
         rc = cudaStreamWaitEvent(stream, static_cast<cudaEvent_t>(a.shared_ready), 0);
         if (rc != cudaSuccess) return rc;
     }
-    moe_fin_kernel<<<dim3(spread(a.rows, H / 128u), (a.rows + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(f);
+    const uint32_t fin_groups = (a.rows + 7u) / 8u, fin_want = (1184u + fin_groups - 1u) / fin_groups;
+    moe_fin_kernel<<<dim3(fin_want < H / 128u ? fin_want : H / 128u, fin_groups), 256, 0, stream>>>(f);
     *launches += 8;
     return cudaGetLastError();
 }
