@@ -306,6 +306,10 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
         mbar_init(acc_full, 1u);
         mbar_init_fence();
     }
+    // the tile's 128 output scales, fetched now so that the epilogue finds them in shared memory
+    __half* svh_s = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(bars) + 256u);
+    if (a.svh[0] != nullptr && tid >= 64u && tid < 64u + kBN)
+        svh_s[tid - 64u] = (op ? a.svh[1] : a.svh[0])[(size_t)e * a.svh_stride + nt * kBN + (tid - 64u)];
     if (warp == 1) tmem_alloc(tmem_slot, T::kTmemCols);
     tc_fence_before();
     __syncthreads();
@@ -465,7 +469,7 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
             named_sync(2, kDecodeWarps * 32u);
             const HadB hb = had_b(lane);
             const uint32_t pg = lane >> 2, pq = lane & 3u;
-            const __half* sv = (op ? a.svh[1] : a.svh[0]) + (size_t)e * a.svh_stride + nt * kBN + 4u * pq;
+            const __half* sv = svh_s + 4u * pq;
             void* const dst = a.y ? a.y : static_cast<void*>(a.z);
             const int dst_dt = a.y ? a.y_dt : (int)kF16;
 #pragma unroll 1
@@ -849,11 +853,19 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
     pa.xp = xp;
     pa.ops = 1;
     prep_rows_kernel<<<dim3(spread(p.rows, p.in / 128u), (p.rows + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(pa);
-    // 512-row tiles once they fill the GPU: the decode of a B tile is then shared by four accumulators
-    // (three accumulators and three stages, or two accumulators, measured no faster on calls this size)
-    const uint32_t bm = ((p.rows + 511u) / 512u) * (p.out / kBN) >= one_wave_ctas() ? 512u : 256u;
+    // Tile height: the one whose rounds of CTAs take the least time, a round of BM-row tiles costing about BM (two
+    // 128-row CTAs share a multiprocessor, so a full round of those costs 256); ties go to the taller tile, whose decoded
+    // B tile serves more rows. (Three accumulators with three stages measured no faster than four with two.)
+    const uint32_t sms = one_wave_ctas(), ncol = p.out / kBN;
+    uint32_t bm = 512u, best = ~0u;
+    for (uint32_t cand : {512u, 256u, 128u}) {
+        const uint32_t ctas = ((p.rows + cand - 1u) / cand) * ncol;
+        const uint32_t cost = cand == 128u ? (ctas <= sms ? 128u : ((ctas + 2u * sms - 1u) / (2u * sms)) * 256u)
+                                           : ((ctas + sms - 1u) / sms) * cand;
+        if (cost < best) best = cost, bm = cand;
+    }
     CUtensorMap map;
-    if (!make_a_map(&map, xp, p.rows, p.in, 256u)) return cudaErrorNotSupported;
+    if (!make_a_map(&map, xp, p.rows, p.in, bm == 128u ? 128u : 256u)) return cudaErrorNotSupported;
     GemmArgs g = {};
     g.trellis[0] = g.trellis[1] = p.trellis;
     g.K = p.in;
@@ -871,8 +883,9 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
     if (p.resident) {
         CUtensorMap map_b;  // W_hat transposed [out, in]: boxes of 64 inputs x 128 outputs, the decoded B tile's layout
         if (!make_a_map(&map_b, p.resident, p.out, p.in, kBN)) return cudaErrorNotSupported;
-        rc = bm == 512u ? launch_gemm_resident<512>(map, map_b, g, (p.rows + bm - 1u) / bm, stream)
-                        : launch_gemm_resident<256>(map, map_b, g, (p.rows + bm - 1u) / bm, stream);
+        rc = bm == 512u   ? launch_gemm_resident<512>(map, map_b, g, (p.rows + bm - 1u) / bm, stream)
+             : bm == 256u ? launch_gemm_resident<256>(map, map_b, g, (p.rows + bm - 1u) / bm, stream)
+                          : launch_gemm_resident<128>(map, map_b, g, (p.rows + bm - 1u) / bm, stream);
     } else {
         rc = launch_gemm(map, g, (p.rows + bm - 1u) / bm, bm, codebook, stream);
     }
