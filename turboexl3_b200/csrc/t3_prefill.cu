@@ -853,15 +853,16 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
     pa.xp = xp;
     pa.ops = 1;
     prep_rows_kernel<<<dim3(spread(p.rows, p.in / 128u), (p.rows + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(pa);
-    // Tile height: the one whose rounds of CTAs take the least time, a round of BM-row tiles costing about BM (two
-    // 128-row CTAs share a multiprocessor, so a full round of those costs 256); ties go to the taller tile, whose decoded
-    // B tile serves more rows. (Three accumulators with three stages measured no faster than four with two.)
+    // Tile height: the one whose rounds of CTAs take the least time, a round of BM-row tiles costing about BM + 128 (a CTA's
+    // fixed part: set-up, first loads, epilogue; and a shorter tile amortises its decoded B tile over fewer rows). Two
+    // 128-row CTAs share a multiprocessor, so a full round of those costs twice one. Ties go to the taller tile. (Three
+    // accumulators with three stages measured no faster than four with two.)
     const uint32_t sms = one_wave_ctas(), ncol = p.out / kBN;
     uint32_t bm = 512u, best = ~0u;
     for (uint32_t cand : {512u, 256u, 128u}) {
         const uint32_t ctas = ((p.rows + cand - 1u) / cand) * ncol;
-        const uint32_t cost = cand == 128u ? (ctas <= sms ? 128u : ((ctas + 2u * sms - 1u) / (2u * sms)) * 256u)
-                                           : ((ctas + sms - 1u) / sms) * cand;
+        const uint32_t cost = cand == 128u ? (ctas <= sms ? 256u : ((ctas + 2u * sms - 1u) / (2u * sms)) * 512u)
+                                           : ((ctas + sms - 1u) / sms) * (cand + 128u);
         if (cost < best) best = cost, bm = cand;
     }
     CUtensorMap map;
