@@ -460,9 +460,14 @@ def run_ours(args) -> None:
     y_arr = {o: tb.host_array(v) for o, v in y_np.items()}
     stream_ptr = torch.cuda.current_stream().cuda_stream
 
+    x_ref = {i: C.byref(v) for i, v in x_arr.items()}
+    y_ref = {o: C.byref(v) for o, v in y_arr.items()}
+    calls = [[(C.byref(w), x_ref[w.in_dim], y_ref[w.out_dim]) for w in ws] for ws in table_sets]
+    matmul = tab.matmul
+
     def step_e2e(s: int):
-        for w in table_sets[s % COPIES]:
-            v = tab.matmul(C.byref(w), C.byref(x_arr[w.in_dim]), stream_ptr, C.byref(y_arr[w.out_dim]))
+        for (w_ref, xr, yr) in calls[s % COPIES]:
+            v = matmul(w_ref, xr, stream_ptr, yr)
             if v.kind != 0:
                 raise SystemExit(f"table matmul refused: {v.reason}")
 
