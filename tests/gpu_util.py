@@ -41,7 +41,9 @@ def report(got: np.ndarray, ref: np.ndarray, dt: str) -> dict:
     exact f16 weights, so it differs from the oracle only through f32 summation order (the Hadamard butterflies and the
     tensor-core accumulation): a few percent of the f16 roundings inside a projection land on the other side, and each
     moves the outputs of its 128-block by a fraction of an ulp."""
-    half = HALF_ULP_BF16 if dt == "bf16" else (HALF_ULP_F16 if dt == "f16" else 0.0)
+    # an f32 activation still carries an f16-rounded y (the projection rounds y to f16 before the output dtype,
+    # docs/core/format.md:27-31), so its rounding allowance is f16's
+    half = HALF_ULP_BF16 if dt == "bf16" else HALF_ULP_F16
     ref_r = round_to(ref, dt) if dt != "f32" else ref
     return {
         "compare": ob.compare(got, ref)["max_ratio"],

@@ -221,3 +221,21 @@ def test_resident_trunk_gives_the_per_call_bytes(case):
     table.release()
     assert table.stats() == {"admitted": 0, "kept": 0, "kept_bytes": 0}
     assert t3.device_error() == 0
+
+
+def test_scales_that_are_not_signs():
+    """suh / svh with magnitudes in [0.5, 1.5] (the reference's synthetic scales, src/core/ref.zig:66-73): x * suh is then not
+    an f16 value, and the prepare's tensor-core Hadamard takes its two-part path."""
+    rng = np.random.default_rng(900)
+    in_dim, out_dim, n = 1024, 384, 64
+    trellis, suh, svh = synth.linear(901, in_dim, out_dim, n)
+    suh = (suh.astype(np.float32) * rng.uniform(0.5, 1.5, in_dim)).astype(np.float16)
+    svh = (svh.astype(np.float32) * rng.uniform(0.5, 1.5, out_dim) / 32.0).astype(np.float16)
+    what = ob.reconstruct_inner(trellis, in_dim, out_dim, n, t3.MUL1, 16)
+    t, a, b = dev(trellis), dev(suh), dev(svh)
+    for rows, dt in ((1, "f16"), (32, "f16"), (33, "f16"), (300, "f32"), (600, "bf16")):
+        x = x_as(synth.activations(902 + rows, rows, in_dim), dt)
+        y = t3.linear(x, t, a, b)
+        ref = ob.linear_rows_what(host_f32(x), what, suh, svh, in_dim, out_dim)
+        check(host_f32(y), ref, dt, ("general scales", rows, dt))
+    assert t3.device_error() == 0

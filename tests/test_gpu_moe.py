@@ -36,7 +36,7 @@ def check_moe(got, ref, dt, what, terms=1.0):
     """compareRounded always; `compare` at the reference's bar for outputs up to the size of the reference's own largest
     decode test (16 rows x 2560), 1.5 x that beyond: it is a maximum over the outputs, and one output rounding flip on a
     5-sigma value (seen once in ~10^5 outputs) is already 4.9e-3 of the RMS."""
-    half = HALF_ULP_BF16 if dt == "bf16" else (HALF_ULP_F16 if dt == "f16" else 0.0)
+    half = HALF_ULP_BF16 if dt == "bf16" else HALF_ULP_F16  # every per-slot v is f16-rounded whatever y's dtype
     assert np.all(np.isfinite(ref)) and np.all(np.isfinite(got)), what
     c = ob.compare(got, ref)["max_ratio"]
     r = ob.compare(got, ref, half)["max_ratio"]
@@ -313,4 +313,28 @@ def test_gathered_rows_chain_is_the_top1_chain_over_taken_rows(xdt, ydt):
         t3.moe_swiglu_rows(x, dev(rows[:20]), bank, dev(inds[:20]), dev(scores[:20]))
     with pytest.raises(t3.Exl3Error, match="InvalidExl3Clamp"):
         t3.moe_swiglu_rows(x, dev(rows), bank, dev(inds), dev(scores), t3.Decode.mul1, 129)
+    assert t3.device_error() == 0
+
+
+def test_bank_scales_that_are_not_signs():
+    """Every scale vector of the bank with magnitudes in [0.5, 1.5] times its sign (src/core/ref.zig:66-73), decode rows and
+    prefill rows: the prepares' two-part Hadamard path."""
+    H, I, E, topk, n = 512, 256, 10, 4, 48
+    rng = np.random.default_rng(910)
+    arrs = synth.bank(911, E, H, I, n)
+    for k in list(arrs):
+        if not k.endswith("_t"):
+            arrs[k] = (arrs[k].astype(np.float32) * rng.uniform(0.5, 1.5, arrs[k].shape)).astype(np.float16)
+    d = {k: dev(v) for k, v in arrs.items()}
+    bank = t3.Bank(t3.Proj(d["gate_t"], d["gate_suh"], d["gate_svh"]), t3.Proj(d["up_t"], d["up_suh"], d["up_svh"]),
+                   t3.Proj(d["down_t"], d["down_suh"], d["down_svh"]))
+    obank = ob.Bank(E, H, I, n, *[arrs[k] for k in ("gate_t", "gate_suh", "gate_svh", "up_t", "up_suh", "up_svh",
+                                                     "down_t", "down_suh", "down_svh")])
+    for rows in (3, 150):
+        inds, scores = synth.routing(912 + rows, rows, E, topk)
+        x16 = synth.activations(913 + rows, rows, H)
+        y = t3.moe(dev(x16).view(1, rows, H), bank, dev(inds).view(1, rows, topk), dev(scores).view(1, rows, topk))
+        sample = sorted({0, rows // 2, rows - 1})
+        ref = ob.moe_rows(obank, x16[sample].astype(np.float32), inds[sample], scores[sample])
+        check_moe(host_f32(y).reshape(rows, H)[sample], ref, "f16", ("general scales", rows))
     assert t3.device_error() == 0

@@ -208,12 +208,25 @@ __device__ __forceinline__ uint32_t split4(const float (&v)[4], uint32_t (&hi)[2
     return (lo[0] | lo[1]) & 0x7FFF7FFFu;
 }
 
-// H128 of the block whose values are `v` (v[i8] = elements 16 i8 + 4q .. + 3), any f32 values
-__device__ __forceinline__ void h128_split(const float (&v)[8][4], const HadB& hb, float (&out)[8][4]) {
+// H128 of the block whose values are `v` (v[i8] = elements 16 i8 + 4q .. + 3), any f32 values. `unit_scales`: the caller
+// knows (for the whole warp) that every v is an f16 value times +-1 — sign vectors, the usual suh — so v is an f16 value
+// itself and there are no remainders to compute.
+__device__ __forceinline__ void h128_split(const float (&v)[8][4], bool unit_scales, const HadB& hb, float (&out)[8][4]) {
     uint32_t hi[8][2], lo[8][2], rest = 0;
+    if (unit_scales) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) hi[i][0] = pack_half2(v[i][0], v[i][1]), hi[i][1] = pack_half2(v[i][2], v[i][3]);
+        h128_mma(hi, hi, false, hb, out);
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) rest |= split4(v[i], hi[i], lo[i]);
     h128_mma(hi, lo, __any_sync(0xFFFFFFFFu, rest != 0u) != 0, hb, out);
+}
+
+// whether four scales are all +1 or -1 (as f32 values converted from f16)
+__device__ __forceinline__ bool all_unit(const float (&sc)[4]) {
+    return fabsf(sc[0]) == 1.0f && fabsf(sc[1]) == 1.0f && fabsf(sc[2]) == 1.0f && fabsf(sc[3]) == 1.0f;
 }
 
 // The output rotation of one block (format.finishOutput, format.zig:370-380): z and sv point at this lane's first
@@ -619,14 +632,16 @@ __global__ void __launch_bounds__(256) prep_rows_kernel(const PrepArgs a) {
         for (uint32_t op = 0; op < a.ops; ++op) {
             const __half* suh = (op ? a.suh[1] : a.suh[0]) + (size_t)e * a.K + col;
             float v[8][4], out[8][4];
+            bool unit = true;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 float sc[4];
                 load_half4(suh + 16 * i, sc);
+                unit = unit && all_unit(sc);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) v[i][j] = round_half(xv[i][j]) * sc[j];
             }
-            h128_split(v, hb, out);
+            h128_split(v, __all_sync(0xFFFFFFFFu, unit) != 0, hb, out);
             if (live) {
                 const size_t o = ((size_t)op * a.positions + p) * a.K + col;
 #pragma unroll
@@ -676,14 +691,16 @@ __global__ void __launch_bounds__(256) mid_kernel(const MidArgs a) {
             load_half4(a.z + zo + 16 * i, g[i]);
             load_half4(a.z + (size_t)a.positions * a.inter + zo + 16 * i, u[i]);
         }
+        bool unit = true;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             float sd[4];
             load_half4(a.down_suh + eo + 16 * i, sd);
+            unit = unit && all_unit(sd);
 #pragma unroll
             for (int j = 0; j < 4; ++j) g[i][j] = round_half(swiglu_f32(g[i][j], u[i][j], a.limit, a.clamp_at)) * sd[j];
         }
-        h128_split(g, hb, u);
+        h128_split(g, __all_sync(0xFFFFFFFFu, unit) != 0, hb, u);
         if (live)
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
