@@ -261,7 +261,7 @@ def prefill_submetric(t3, synth, torch) -> dict:
     bank = t3.Bank(t3.Proj(dev(arrs["gate_t"]), dev(arrs["gate_suh"]), dev(arrs["gate_svh"])),
                    t3.Proj(dev(arrs["up_t"]), dev(arrs["up_suh"]), dev(arrs["up_svh"])),
                    t3.Proj(dev(arrs["down_t"]), dev(arrs["down_suh"]), dev(arrs["down_svh"])))
-    for rows in (4096,):
+    for rows in (4096, 16384):
         inds, scores = synth.routing(77, rows, E, topk)
         x = dev(synth.activations(5, rows, H)).view(1, rows, H)
         di, ds = dev(inds).view(1, rows, topk), dev(scores).view(1, rows, topk)
@@ -534,6 +534,22 @@ def run_ours(args) -> None:
                 cases[f"{i}x{o}_K{n // 16}"] = {"us": round(us, 2), "GBps": round(code_bytes(i, o, n // 16) / us / 1e3, 1)}
             return cases
         extra["cases"] = guarded(per_linear)
+
+        def per_rows():
+            """config 2's other in-register row counts on one linear (2048 x 6144, K = 4): the bytes do not grow with rows"""
+            idx = next(j for j, (i, o, n, _, _, _) in enumerate(sets[0]) if (i, o, n) == (2048, 6144, 64))
+            out = {}
+            for rows in (1, 8, 17, 32):
+                xr = torch.from_numpy(synth.activations(9, rows, 2048)).cuda()
+
+                def burst():
+                    for c in range(COPIES):
+                        t3.linear(xr, *sets[c][idx][3:], dec)
+                g = graph_of(burst) if graphs else None
+                us = time_us(g.replay if g is not None else burst, 10) / COPIES
+                out[f"rows{rows}"] = {"us": round(us, 2), "GBps": round(code_bytes(2048, 6144, 4) / us / 1e3, 1)}
+            return out
+        extra["rows_2048x6144_K4"] = guarded(per_rows)
         extra["submetrics"] = {"moe_layer_decode_rows_config3": guarded(lambda: moe_submetric(t3, synth, torch)),
                                "prefill": guarded(lambda: prefill_submetric(t3, synth, torch))}
 
