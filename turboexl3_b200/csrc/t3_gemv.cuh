@@ -225,10 +225,21 @@ __device__ __forceinline__ void gather_owned(const float* recv, uint32_t owned, 
                                              uint32_t step, uint32_t count, uint32_t lane, float (&v)[4]) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) v[j] = 0.0f;
-    for (uint32_t i = 0; i < count; ++i) {
-        const float* rp = recv + ((first + i * step) * owned + slot) * kPartialStride + lane;
+    // up to 16 ranks; the loads of four ranks are issued together, the sum stays in rank order
+    for (uint32_t i0 = 0; i0 < count; i0 += 4u) {
+        float t[4][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] = (i == 0) ? rp[32 * j] : v[j] + rp[32 * j];
+        for (uint32_t k = 0; k < 4u; ++k) {
+            const uint32_t i = i0 + k < count ? i0 + k : count - 1u;
+            const float* rp = recv + ((first + i * step) * owned + slot) * kPartialStride + lane;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) t[k][j] = rp[32 * j];
+        }
+#pragma unroll
+        for (uint32_t k = 0; k < 4u; ++k)
+            if (i0 + k < count)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] = (i0 + k == 0u) ? t[k][j] : v[j] + t[k][j];
     }
 }
 

@@ -612,7 +612,7 @@ struct PrepArgs {
     const uint32_t* row_map;       // routed: the x row of each row-slot when the call gathers rows, else slot / topk
     __half* xp;                    // [ops][positions][K]
 };
-__global__ void __launch_bounds__(256) prep_rows_kernel(const PrepArgs a) {
+__global__ void __launch_bounds__(256, 3) prep_rows_kernel(const PrepArgs a) {
     const uint32_t lane = threadIdx.x & 31u, q = lane & 3u;
     uint32_t p;
     bool live;
@@ -676,7 +676,7 @@ struct MidArgs {
     int clamp_at;
     __half* hd;  // [P][inter]
 };
-__global__ void __launch_bounds__(256) mid_kernel(const MidArgs a) {
+__global__ void __launch_bounds__(256, 3) mid_kernel(const MidArgs a) {
     const uint32_t lane = threadIdx.x & 31u, q = lane & 3u;
     uint32_t p;
     bool live;
