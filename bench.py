@@ -379,6 +379,8 @@ def run_ours(args) -> None:
             os.dup2(keep, 1)
             os.close(keep)
     t3.lib()
+    if args.dense_split:
+        t3.configure(dense_split=args.dense_split)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -611,6 +613,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--quick", action="store_true", help="headline and e2e only (no per-linear table, no submetrics)")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of replaying CUDA graphs")
+    ap.add_argument("--dense-split", type=int, default=0, help="force the dense GEMV's K split (t3_configure; 0 = the library's choice)")
     ap.add_argument("--case", default=None, choices=["moe_decode", "moe_prefill", "dense_prefill", "resident_prefill"],
                     help="run one case eagerly --steps times and exit (for profilers)")
     ap.add_argument("--rows", type=int, default=1, help="rows of --case")
