@@ -2,6 +2,7 @@
 """Bench of the EXL3 projection hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--quick] [--eager] [--dense-split S] [--case NAME --rows R]
 
 Headline workload (BASELINE.json configs[1], decode rows): the dense trunk sweep, shapes 2048x2048, 2048x6144 and
 6144x2048 at K in {1,2,3,4,5,6,8} bits, one f16 activation row each: 21 linears a step, 106.4 MB of trellis code bytes.
@@ -11,11 +12,18 @@ A step is ONE stream of 21 launches replayed from a CUDA graph (a dependent chai
 its weights while its predecessor finishes, nothing else overlaps).
 
 The JSON line also carries: `e2e` (the same step through the quant-plugin table with HOST arrays: copy in, run, copy
-out, every call), `roofline`, `cpu_baseline` (the oracle's format.project on the host cores), `submetrics` (the other two
-parts of BASELINE's metric: us per MoE layer at decode rows on config 3, prefill TFLOP/s on configs 2 and 4 shapes) and
-`concurrent` (the 21 independent linears as parallel graph branches: what the device sustains when nothing orders them).
+out, every call), `roofline`, `cpu_baseline` (the oracle's format.project on the host cores, all threads and one), `submetrics`
+(the other two parts of BASELINE's metric: us per MoE layer at decode rows on config 3, prefill TFLOP/s on configs 2 and 4
+shapes, per-call and on a kept W_hat), `cases` (every linear of the sweep), `rows_2048x6144_K4` (config 2's other row counts)
+and `concurrent` (the 21 independent linears as parallel graph branches: what the device sustains when nothing orders them).
+Optional measurements that fail are reported in place and never void the line.
+
+At N > 1 (torchrun) every rank runs the sweep on its own weight copies (replicas, no collective) and `submetrics.sharded`
+adds the two sharded paths: the routed layer expert-parallel and a trunk linear column-sharded.
 
 `--impl reference` times the CPU restatement of the reference's host implementation (format.project) instead.
+`--quick`: headline and e2e only. `--eager`: eager launches instead of graph replay (for profilers). `--case`: one named case
+run eagerly a few times (moe_decode, moe_prefill, dense_prefill, resident_prefill), printing a small JSON line of its own.
 """
 from __future__ import annotations
 
