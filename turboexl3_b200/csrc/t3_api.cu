@@ -555,6 +555,12 @@ int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const
     a.err = dev_error_ptr();
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (int rc = cuda_status(launch_moe_gate_up(a, dec.codebook, s))) return rc;
+    if (a.topk == 1u) {
+        // one slot a row: the down launch stores y itself (and adds `shared`), there is nothing to merge
+        if (shared_ready)
+            if (int rc = cuda_status(cudaStreamWaitEvent(s, static_cast<cudaEvent_t>(shared_ready), 0))) return rc;
+        return cuda_status(launch_moe_down(a, dec.codebook, s));
+    }
     if (int rc = cuda_status(launch_moe_down(a, dec.codebook, s))) return rc;
     g_launches.fetch_add(1, std::memory_order_relaxed);
     if (shared_ready)  // only the merge reads `shared`: the two GEMV launches above do not wait for it

@@ -343,7 +343,24 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs
                 load_scales(static_cast<const __half*>(a.down_svh) + (size_t)e * H + hb * 128u, lane, sv);
                 gather_owned(c.recv, owned, i, 0, 1, csize, lane, v);
                 finish_block(v, sv, lane);
-                __half* vo = static_cast<__half*>(a.v) + (size_t)s_members[m0 + m] * H + hb * 128u;
+                const uint32_t slot = s_members[m0 + m];
+                if (a.topk == 1u) {
+                    // One slot a row: the merge has nothing to gather, so the weighted value (and the shared-expert add)
+                    // is stored here and the merge launch is skipped. The arithmetic is moe_merge_kernel's, 0 + w v included.
+                    const float w = load_act(a.scores, a.score_dt, slot);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const size_t o = (size_t)slot * H + hb * 128u + lane + 32u * q;
+                        float acc = __fadd_rn(0.0f, __fmul_rn(w, v[q]));
+                        if (a.shared) {
+                            store_act(a.y, a.x_dt, o, acc);
+                            acc = __fadd_rn(load_act(a.y, a.x_dt, o), load_act(a.shared, a.x_dt, o));
+                        }
+                        store_act(a.y, a.x_dt, o, acc);
+                    }
+                    continue;
+                }
+                __half* vo = static_cast<__half*>(a.v) + (size_t)slot * H + hb * 128u;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) vo[lane + 32u * q] = __float2half_rn(v[q]);
             }
