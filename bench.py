@@ -28,6 +28,7 @@ run eagerly a few times (moe_decode, moe_prefill, dense_prefill, resident_prefil
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -379,7 +380,7 @@ def run_ours(args) -> None:
         keep = os.dup(1)
         os.dup2(2, 1)
         try:
-            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=180))
             dist.barrier()
             torch.cuda.synchronize()
         finally:
