@@ -76,12 +76,16 @@ uint32_t one_wave() {
     return ctas;
 }
 
-// K slices for `units` independent (output block, job) pairs over nb 128-blocks of K: the largest power of two, at most
-// `cap`, that keeps the whole grid (units x slices x `fan` CTAs a slice) inside one wave; 1 when even that does not fit.
+// K slices for `units` independent (output block, job) pairs over nb 128-blocks of K: the smallest power of two, at most
+// `cap`, that brings the grid (units x slices x `fan` CTAs a slice) to `target` CTAs, never past one wave. A dense linear
+// aims at one CTA a multiprocessor (a second slot stays free for the next launch to start under this one); a routed call
+// aims at an eighth of a wave for a nominal row's slots, because its grid grows with the rows and longer CTAs amortise
+// their fixed part (measured on config 3: split 1 instead of 2 is as fast at 1 and 4 rows and 10 % faster at 16 and 32).
 // (Other counts work too, slices may differ by a block, but measured slower than the nearest power of two below them.)
-uint32_t pick_split(uint32_t nb, uint32_t units, uint32_t fan, uint32_t cap) {
+uint32_t pick_split(uint32_t nb, uint32_t units, uint32_t fan, uint32_t cap, uint32_t target) {
     uint32_t s = 1;
-    while (s * 2u <= nb && s * 2u <= cap && (uint64_t)units * fan * s * 2u <= one_wave()) s *= 2u;
+    while (s * 2u <= nb && s * 2u <= cap && (uint64_t)units * fan * s < target && (uint64_t)units * fan * s * 2u <= one_wave())
+        s *= 2u;
     return s;
 }
 
@@ -429,7 +433,7 @@ int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, cons
     a.x_dt = x_dtype;
     note_engine(1, (uint64_t)in_dim, (uint64_t)out_dim, (uint64_t)n, 0);
     const uint32_t nb = a.in / 128u;
-    a.split = cfg.dense_split ? pow2_at_most(nb, cfg.dense_split) : pick_split(nb, a.out / 128u, 1u, 8u);
+    a.split = cfg.dense_split ? pow2_at_most(nb, cfg.dense_split) : pick_split(nb, a.out / 128u, 1u, 8u, one_wave() / 2u);
     a.overlap = !cfg.no_overlap;
     a.slice_max = largest_slice(nb, a.split);
     a.err = dev_error_ptr();
@@ -533,11 +537,15 @@ int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const
     const uint32_t rm = row_cap_for(expect < a.rows ? expect : a.rows);
     a.row_cap = rm;
     a.overlap = !cfg.no_overlap;
-    // The K splits depend on the geometry only (sized for one row's slots), never on the row count: a row's summation
-    // order, hence its bytes, is the same alone and in a batch.
-    a.split_gu = pick_split(a.hidden / 128u, (a.inter / 128u) * a.topk, 2u, 4u);
+    // The K splits depend on hidden and inter only (sized as if a row had eight slots), never on the row count, the top-k
+    // or the bank's size: a row-slot's summation order, hence its bytes, is the same alone and in a batch, and the same in
+    // a one-expert bank (a shared expert, an expert-parallel rank's share) as in the whole bank. A shared expert's chain,
+    // run on a second stream beside the routed chain, then launches the same cluster shapes as the routed one (measured:
+    // a 2-CTA-cluster launch beside 4- or 8-CTA-cluster launches costs a 1-row layer 7 us).
+    constexpr uint32_t kNominalSlots = 8;
+    a.split_gu = pick_split(a.hidden / 128u, (a.inter / 128u) * kNominalSlots, 2u, 4u, one_wave() / 8u);
     a.slice_max_gu = largest_slice(a.hidden / 128u, a.split_gu);
-    a.split_d = pick_split(a.inter / 128u, (a.hidden / 128u) * a.topk, 1u, 8u);
+    a.split_d = pick_split(a.inter / 128u, (a.hidden / 128u) * kNominalSlots, 1u, 8u, one_wave() / 8u);
     a.slice_max_d = largest_slice(a.inter / 128u, a.split_d);
     // sized for the widest row capacity so the split does not move with the rows either
     while (!plan_ring(32u, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu)) {
