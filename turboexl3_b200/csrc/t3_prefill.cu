@@ -116,104 +116,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// ---- the 128-point Hadamard on tensor cores (prepare / mid / finish kernels and the dense GEMM's epilogue) --------------------
-//
-// The 128-point Hadamards of these kernels run on the tensor cores. The sign of entry (i, j) of H128 is the parity of
-// popcount(i & j), which splits over the bit fields of i = 16 i8 + i16, so H128 = H8 (x) H16 and a block viewed as an
-// 8 x 16 matrix X becomes H8 . X . H16: X . H16 is m16n8k16 steps against a constant +-1 fragment, H8 a three-level
-// butterfly over values one thread already holds. A warp works on EIGHT positions at a time, one 128-block each: quad g
-// (lanes 4g .. 4g + 3) owns position g, and lane q of the quad holds, for every i8, the four elements 16 i8 + 4q .. + 3:
-// one 8-byte (f16) or 16-byte (f32) access per i8 on the way in and on the way out. The butterfly on a warp costs twenty
-// shuffles per block, and the shuffle unit (one warp instruction per SM per cycle) bounded these kernels; this form has none.
-// f32 accumulation of +-1 products is exact per term, so the result differs from the butterfly (and from the oracle's
-// dense sum) only in summation order, as before.
-
-struct HadB {
-    uint32_t b[2][2];  // the +-1 H16 fragment of each 8-column half (t): {k 0-7 part, k 8-15 part}
-};
-
-// Matrix index <-> element maps (both free to choose): A/B index k of thread q covers elements 4q, 4q+1 (k = 2q, 2q+1) and
-// 4q+2, 4q+3 (k = 2q+8, 2q+9); output column n = 2q+b of half t is element 4q + 2t + b. So a thread's inputs and outputs
-// are the same four consecutive elements.
-__device__ __forceinline__ HadB had_b(uint32_t lane) {
-    const uint32_t g = lane >> 2, q = lane & 3u;
-    HadB h;
-#pragma unroll
-    for (uint32_t t = 0; t < 2u; ++t) {
-        const uint32_t en = 4u * (g >> 1) + 2u * t + (g & 1u);
-        uint32_t s[4];
-#pragma unroll
-        for (uint32_t b = 0; b < 4u; ++b) s[b] = (__popc((4u * q + b) & en) & 1) ? 0xBC00u : 0x3C00u;
-        h.b[t][0] = s[0] | (s[1] << 16);
-        h.b[t][1] = s[2] | (s[3] << 16);
-    }
-    return h;
-}
-
-// out[i8][e] = sum over the block of sign * value, for the position this quad owns. a[i8] = the four f16 values
-// {16 i8 + 4q .. + 3} as two packed pairs; a second set (the f16 remainders of values that are not f16 themselves) is
-// accumulated into the same sums when `use_lo` is set.
-__device__ __forceinline__ void h128_mma(const uint32_t (&a)[8][2], const uint32_t (&lo)[8][2], bool use_lo,
-                                         const HadB& hb, float (&out)[8][4]) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            mma16816(c, a[2 * j][0], a[2 * j + 1][0], a[2 * j][1], a[2 * j + 1][1], hb.b[t][0], hb.b[t][1]);
-            if (use_lo) mma16816(c, lo[2 * j][0], lo[2 * j + 1][0], lo[2 * j][1], lo[2 * j + 1][1], hb.b[t][0], hb.b[t][1]);
-            out[2 * j][2 * t] = c[0], out[2 * j][2 * t + 1] = c[1];
-            out[2 * j + 1][2 * t] = c[2], out[2 * j + 1][2 * t + 1] = c[3];
-        }
-#pragma unroll
-    for (int bit = 1; bit < 8; bit <<= 1)
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-            if (!(i & bit))
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float lo_v = out[i][e], hi_v = out[i | bit][e];
-                    out[i][e] = lo_v + hi_v;
-                    out[i | bit][e] = lo_v - hi_v;
-                }
-}
-
-__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
-    const __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<const uint32_t*>(&h);
-}
-
-// v (f32 values, not necessarily f16) as an f16 part and the f16 of what is left; returns nonzero when any remainder is
-__device__ __forceinline__ uint32_t split4(const float (&v)[4], uint32_t (&hi)[2], uint32_t (&lo)[2]) {
-    float r[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) r[j] = v[j] - round_half(v[j]);
-    hi[0] = pack_half2(v[0], v[1]), hi[1] = pack_half2(v[2], v[3]);
-    lo[0] = pack_half2(r[0], r[1]), lo[1] = pack_half2(r[2], r[3]);
-    return (lo[0] | lo[1]) & 0x7FFF7FFFu;
-}
-
-// H128 of the block whose values are `v` (v[i8] = elements 16 i8 + 4q .. + 3), any f32 values. `unit_scales`: the caller
-// knows (for the whole warp) that every v is an f16 value times +-1 — sign vectors, the usual suh — so v is an f16 value
-// itself and there are no remainders to compute.
-__device__ __forceinline__ void h128_split(const float (&v)[8][4], bool unit_scales, const HadB& hb, float (&out)[8][4]) {
-    uint32_t hi[8][2], lo[8][2], rest = 0;
-    if (unit_scales) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) hi[i][0] = pack_half2(v[i][0], v[i][1]), hi[i][1] = pack_half2(v[i][2], v[i][3]);
-        h128_mma(hi, hi, false, hb, out);
-        return;
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) rest |= split4(v[i], hi[i], lo[i]);
-    h128_mma(hi, lo, __any_sync(0xFFFFFFFFu, rest != 0u) != 0, hb, out);
-}
-
-// whether four scales are all +1 or -1 (as f32 values converted from f16)
-__device__ __forceinline__ bool all_unit(const float (&sc)[4]) {
-    return fabsf(sc[0]) == 1.0f && fabsf(sc[1]) == 1.0f && fabsf(sc[2]) == 1.0f && fabsf(sc[3]) == 1.0f;
-}
-
 // The output rotation of one block (format.finishOutput, format.zig:370-380): z and sv point at this lane's first
 // element (block start + 4q); out = f16(H128(z) / sqrt(128) * sv).
 __device__ __forceinline__ void finish_block_mma(const __half* z, const __half* sv, const HadB& hb, float (&out)[8][4]) {
