@@ -323,6 +323,32 @@ def sharded_submetric(t3, synth, torch, dist, rank: int, world: int) -> dict:
     return out
 
 
+def trunk_submetric(t3, synth, torch) -> dict:
+    """BASELINE config 5's MLA trunk projections (K = 4) at one row: larger linears than the sweep's, where bytes start to
+    matter. Each linear runs over enough distinct weight copies (slices of one 288 MB buffer of random codes) to stream
+    from HBM, one graph of launches a shape."""
+    n = 64
+    pool = torch.randint(0, 2 ** 31 - 1, (288 * 1024 * 1024 // 4,), dtype=torch.int32, device="cuda").view(torch.int16)
+    out = {}
+    for name, i, o in (("q_a", 7168, 1536), ("q_b", 1536, 24576), ("kv_a", 7168, 640), ("kv_b", 512, 32768), ("o", 16384, 7168)):
+        halfs = (i // 16) * (o // 16) * n
+        copies = max(3, min(48, pool.numel() // halfs))
+        ws = [pool[c * halfs:(c + 1) * halfs].view(i // 16, o // 16, n) for c in range(copies)]
+        _, suh, svh = synth.linear(7, i, 128, 16)
+        suh_d = torch.from_numpy(suh).cuda()
+        svh_d = torch.from_numpy(np.where(np.random.default_rng(8).random(o) < 0.5, -1.0, 1.0).astype(np.float16)).cuda()
+        x = torch.from_numpy(synth.activations(9, 1, i)).cuda()
+
+        def burst():
+            for w in ws:
+                t3.linear(x, w, suh_d, svh_d)
+        g = graph_of(burst)
+        us = time_us(g.replay, 5) / copies
+        byts = i * o * n // 128
+        out[f"{name}_{i}x{o}"] = {"us": round(us, 2), "GBps": round(byts / us / 1e3, 1), "MB": round(byts / 1e6, 1)}
+    return out
+
+
 def run_case(args) -> None:
     """One named case run eagerly a few times (for profilers): prints a small JSON line, not the bench contract's."""
     import torch
@@ -561,6 +587,7 @@ def run_ours(args) -> None:
                 out[f"rows{rows}"] = {"us": round(us, 2), "GBps": round(code_bytes(2048, 6144, 4) / us / 1e3, 1)}
             return out
         extra["rows_2048x6144_K4"] = guarded(per_rows)
+        extra["trunk_config5_K4_rows1"] = guarded(lambda: trunk_submetric(t3, synth, torch))
         extra["submetrics"] = {"moe_layer_decode_rows_config3": guarded(lambda: moe_submetric(t3, synth, torch)),
                                "prefill": guarded(lambda: prefill_submetric(t3, synth, torch))}
 
