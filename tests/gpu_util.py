@@ -58,8 +58,16 @@ COMPARE_BAR = {"f32": 5e-3, "f16": 5e-3, "bf16": 2.5e-2}
 ROUNDED_BAR = 3e-3
 
 
+ACHIEVED = []  # every checked case's measures, in order; written out at the end of the run when T3_PARITY_REPORT names a file
+
+
+def record(what, r: dict) -> None:
+    ACHIEVED.append({"what": repr(what), **{k: float(v) for k, v in r.items()}})
+
+
 def check(got: np.ndarray, ref: np.ndarray, dt: str, what=None) -> dict:
     r = report(got, ref, dt)
+    record(what, r)
     assert np.all(np.isfinite(got)), what
     assert r["compare"] <= COMPARE_BAR[dt], (what, r)
     assert r["rounded"] <= ROUNDED_BAR, (what, r)

@@ -123,7 +123,7 @@ def test_trellis_admitted():  # src/core/spec.zig:80-88
 
 def test_configure_validates():  # src/core/config.zig:139
     with pytest.raises(t3.Exl3Error) as e:
-        t3.configure(dense_split=3)
+        t3.configure(dense_split=17)
     assert e.value.name == "InvalidTurboexl3Config"
     with pytest.raises(t3.Exl3Error):
         t3.configure(ring_bytes=100)

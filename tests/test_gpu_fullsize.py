@@ -1,0 +1,129 @@
+"""The large configurations at their stated sizes, checked on sampled rows.
+
+* config 4: hidden 2048, 512 routed experts of width 512, top-10 (softmax, renormalised), a rate drawn per expert from
+  {2, 3, 4} bits, 4096 tokens, plus the shared expert with its sigmoid gate;
+* config 5: hidden 7168, 256 routed experts of width 2048, top-8 (sigmoid, renormalised), one shared expert, at K = 2 and
+  K = 4, one token in full and 8192 tokens sampled;
+* config 2's two wide shapes at 4096 rows.
+
+The banks are too large to draw on the host in reasonable time (config 5 at K = 4 is 5.6 GB of codes), so the code words are
+drawn on the device from a seeded generator and only the experts a sampled row touches are copied back for the oracle,
+which then decodes exactly those (the reference's own large tests sample rows the same way, src/hip_tests.zig:745-752,
+src/models/glm53f_test.zig:16-17). Bars: gpu_util / test_gpu_moe, no allowance for size."""
+import numpy as np
+import pytest
+import torch
+
+import turboexl3_b200 as t3
+from oracle import binding as ob
+from turboexl3_b200 import mixed, synth
+
+from gpu_util import check, dev, host_f32
+from test_gpu_moe import check_moe
+
+pytestmark = pytest.mark.gpu
+
+PROJ = (("gate", "hidden", "inter"), ("up", "hidden", "inter"), ("down", "inter", "hidden"))
+
+
+def device_bank(seed: int, experts: int, hidden: int, inter: int, n: int):
+    """A routed bank whose code words are drawn on the device (uniform halfwords) and whose scale vectors are synth.bank's
+    kind: random signs, svh scaled by a power of two near 1/sqrt(in). Returns (t3.Bank, dict of the device tensors)."""
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    rng = np.random.default_rng(seed)
+    dims = {"hidden": hidden, "inter": inter}
+    d = {}
+    for name, i, o in PROJ:
+        d[name + "_t"] = torch.randint(-32768, 32768, (experts, dims[i] // 16, dims[o] // 16, n), dtype=torch.int16,
+                                       device="cuda", generator=gen)
+        d[name + "_suh"] = dev(synth.signs(rng, (experts, dims[i])))
+        d[name + "_svh"] = dev(synth.signs(rng, (experts, dims[o]), synth.pow2_inv_sqrt(dims[i])))
+    bank = t3.Bank(*[t3.Proj(d[p + "_t"], d[p + "_suh"], d[p + "_svh"]) for p in ("gate", "up", "down")])
+    return bank, d
+
+
+def oracle_subbank(d: dict, experts, hidden: int, inter: int, n: int):
+    """The oracle's bank holding only `experts` (ascending ids) of the device bank d, and the map id -> local index."""
+    ids = torch.tensor(sorted(int(e) for e in experts), dtype=torch.int64, device="cuda")
+    take = lambda t: t.index_select(0, ids).cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+    arrs = [take(d[p + s]) for p in ("gate", "up", "down") for s in ("_t", "_suh", "_svh")]
+    return ob.Bank(len(ids), hidden, inter, n, *arrs), {int(e): i for i, e in enumerate(ids.tolist())}
+
+
+def oracle_rows(d, hidden, inter, n, x_rows, inds_rows, scores_rows):
+    """ref.moeRow on the given rows, decoding only the experts they touch."""
+    obank, local = oracle_subbank(d, np.unique(inds_rows), hidden, inter, n)
+    remap = np.vectorize(local.__getitem__)(inds_rows).astype(np.int32)
+    return ob.moe_rows(obank, x_rows.astype(np.float32), remap, scores_rows)
+
+
+def half(a):
+    return a.astype(np.float16).astype(np.float32)
+
+
+def sigmoid_gate(seed, rows):
+    return (1.0 / (1.0 + np.exp(-np.random.default_rng(seed).standard_normal((rows, 1))))).astype(np.float32)
+
+
+def test_config4_full_size_rate_per_expert():
+    H, I, E, topk, rows = 2048, 512, 512, 10, 4096
+    rates = [16 * int(k) for k in np.random.default_rng(4).choice([2, 3, 4], E)]
+    buckets = mixed.bucket_by_rate(rates)
+    assert buckets.rates == [32, 48, 64]
+    subs = [device_bank(4000 + b, len(m), H, I, n) for b, (m, n) in enumerate(zip(buckets.members, buckets.rates))]
+    sbank, sd = device_bank(4100, 1, H, I, 48)
+    inds, scores = synth.routing(4200, rows, E, topk)
+    x16 = synth.activations(4201, rows, H)
+    gate = sigmoid_gate(4202, rows)
+    x = dev(x16)
+    zero = torch.zeros((1, rows, 1), dtype=torch.int32, device="cuda")
+    shared = t3.moe(x.view(1, rows, H), sbank, zero, dev(gate).view(1, rows, 1)).view(rows, H)
+    y = mixed.mixed_rate_moe(x, [s[0] for s in subs], buckets, dev(inds), dev(scores), t3.Decode.mul1, shared=shared)
+    sample = [0, 1, 1777, 2048, 4095]
+    # per slot through the sub-bank that holds its expert, then ref.moeRow's sum in slot order (src/core/ref.zig:106)
+    routed = np.zeros((len(sample), H), np.float32)
+    for si, r in enumerate(sample):
+        for k in range(topk):
+            e = int(inds[r, k])
+            b, loc = int(buckets.bank_of[e]), int(buckets.local_of[e])
+            v = oracle_rows(subs[b][1], H, I, buckets.rates[b], x16[r:r + 1], np.array([[loc]], np.int32),
+                            np.ones((1, 1), np.float32))[0]
+            routed[si] = (routed[si] + (scores[r, k] * v).astype(np.float32)).astype(np.float32)
+    sh = oracle_rows(sd, H, I, 48, x16[sample], np.zeros((len(sample), 1), np.int32), gate[sample])
+    ref = half(half(routed) + half(sh))  # one add in the activation dtype (src/root.zig:975-984)
+    check_moe(host_f32(y)[sample], ref, "f16", "config 4 full size, mixed rates, 4096 tokens")
+    assert t3.device_error() == 0
+
+
+@pytest.mark.parametrize("k", [2, 4])
+def test_config5_full_size(k):
+    H, I, E, topk, n = 7168, 2048, 256, 8, 16 * k
+    bank, d = device_bank(5000 + k, E, H, I, n)
+    sbank, sd = device_bank(5100 + k, 1, H, I, n)
+    for rows, sample in ((1, [0]), (8192, [0, 4097, 8191])):
+        inds, scores = synth.routing(5200 + rows, rows, E, topk, kind="sigmoid")
+        x16 = synth.activations(5201 + rows, rows, H)
+        gate = sigmoid_gate(5202 + rows, rows)
+        x = dev(x16).view(1, rows, H)
+        zero = torch.zeros((1, rows, 1), dtype=torch.int32, device="cuda")
+        shared = t3.moe(x, sbank, zero, dev(gate).view(1, rows, 1))
+        y = t3.moe_with_shared(x, bank, dev(inds).view(1, rows, topk), dev(scores).view(1, rows, topk), t3.Decode.mul1, shared)
+        routed = oracle_rows(d, H, I, n, x16[sample], inds[sample], scores[sample])
+        sh = oracle_rows(sd, H, I, n, x16[sample], np.zeros((len(sample), 1), np.int32), gate[sample])
+        ref = half(half(routed) + half(sh))
+        check_moe(host_f32(y).reshape(rows, H)[sample], ref, "f16", ("config 5 full size", k, rows))
+        del shared, y
+    assert t3.device_error() == 0
+
+
+@pytest.mark.parametrize("shape", [(2048, 6144), (6144, 2048)])
+def test_config2_wide_shapes_at_4096_rows(shape):
+    in_dim, out_dim = shape
+    trellis, suh, svh = synth.linear(2400 + in_dim % 97, in_dim, out_dim, 64)
+    x16 = synth.activations(2401, 4096, in_dim)
+    y = t3.linear(dev(x16), dev(trellis), dev(suh), dev(svh))
+    sample = [0, 16, 127, 128, 2047, 2500, 4095]
+    what = ob.reconstruct_inner(trellis, in_dim, out_dim, 64, t3.MUL1, 16)
+    ref = ob.linear_rows_what(x16[sample].astype(np.float32), what, suh, svh, in_dim, out_dim)
+    check(host_f32(y)[sample], ref, "f16", ("config 2 wide shape", shape, 4096))
+    assert t3.device_error() == 0

@@ -139,7 +139,7 @@ def test_split_choices_agree_within_rounding():
     t, a, b = dev(trellis), dev(suh), dev(svh)
     outs = []
     try:
-        for split in (1, 2, 4, 8, 16):
+        for split in (1, 2, 3, 4, 5, 7, 8, 16):
             t3.configure(dense_split=split)
             outs.append(host_f32(t3.linear(x, t, a, b)))
     finally:
@@ -153,8 +153,9 @@ def test_small_ring_recycles_stages():
     trellis, suh, svh = synth.linear(31, 4096, 256, 128, scaled=True)
     x = dev(synth.activations(32, 3, 4096))
     t, a, b = dev(trellis), dev(suh), dev(svh)
-    base = bits16(t3.linear(x, t, a, b))
     try:
+        t3.configure(dense_split=8)
+        base = bits16(t3.linear(x, t, a, b))
         t3.configure(ring_bytes=8192, dense_split=1)
         small = host_f32(t3.linear(x, t, a, b))
         t3.configure(ring_bytes=8192, dense_split=8)

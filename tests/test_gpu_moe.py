@@ -14,7 +14,7 @@ import turboexl3_b200 as t3
 from oracle import binding as ob
 from turboexl3_b200 import synth
 
-from gpu_util import HALF_ULP_BF16, HALF_ULP_F16, TORCH_DT, bits16, dev, host_f32, x_as
+from gpu_util import HALF_ULP_BF16, HALF_ULP_F16, TORCH_DT, bits16, dev, host_f32, record, x_as
 
 pytestmark = pytest.mark.gpu
 
@@ -40,8 +40,10 @@ def check_moe(got, ref, dt, what, terms=1.0):
     assert np.all(np.isfinite(ref)) and np.all(np.isfinite(got)), what
     c = ob.compare(got, ref)["max_ratio"]
     r = ob.compare(got, ref, half)["max_ratio"]
+    record(what, {"compare": c, "rounded": r, "size": got.size})
     assert c <= BAR[dt] * (1.0 if got.size <= 16 * 2560 else 1.5) * terms, (what, c, r)
     assert r <= ROUNDED_BAR * terms, (what, c, r)
+    return {"compare": c, "rounded": r}
 
 
 def run(bank, obank, rows, topk, dt, dec, seed, limit=0, clamp_at=0, x_scale=1.0):

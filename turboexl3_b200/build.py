@@ -27,6 +27,8 @@ UNITS = [
     ("t3_prefill.cu", "t3_prefill", []),
     ("t3_api.cu", "t3_api", []),
     ("t3_dequant.cu", "t3_dequant", []),
+    ("t3_dense_rows.cu", "t3_dense_rows_cb0", ["-DT3_CB=0"]),
+    ("t3_dense_rows.cu", "t3_dense_rows_cb1", ["-DT3_CB=1"]),
     ("t3_decode_rows.cu", "t3_decode_rows_cb0", ["-DT3_CB=0"]),
     ("t3_decode_rows.cu", "t3_decode_rows_cb1", ["-DT3_CB=1"]),
 ]
@@ -45,8 +47,9 @@ def _digest() -> str:
         if name.endswith((".cu", ".cuh", ".h")):
             with open(os.path.join(CSRC, name), "rb") as f:
                 h.update(name.encode() + b"\0" + f.read())
-    with open(os.path.join(os.path.dirname(HERE), "include", "t3.h"), "rb") as f:
-        h.update(f.read())
+    for header in ("t3.h", "t3_table.h"):
+        with open(os.path.join(os.path.dirname(HERE), "include", header), "rb") as f:
+            h.update(f.read())
     h.update(" ".join(NVCC_FLAGS).encode())
     h.update(repr(UNITS).encode())
     return h.hexdigest()

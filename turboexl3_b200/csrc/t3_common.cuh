@@ -240,9 +240,9 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
 }
 
-// Waits for the barrier's phase of the given parity, at most kSpinLimit polls (each poll may itself sleep for a
-// hardware-defined time). Returns false after giving up; the caller records the error and carries on to its exit
-// path, so a lost copy never hangs the device.
+// Waits for the barrier's phase of the given parity: one plain poll, then at most kSleepPolls polls that each sleep in
+// the hardware for up to kSleepHintNs. Returns false after giving up; the caller records the error and carries on to
+// its exit path, so a lost copy never hangs the device. (kSpinLimit bounds the polling loops that do not sleep.)
 constexpr uint32_t kSpinLimit = 1u << 20;
 __device__ __forceinline__ uint32_t mbar_try(uint32_t addr, uint32_t parity) {
     uint32_t done;
@@ -255,15 +255,32 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t addr, uint32_t parity) {
         : "memory");
     return done;
 }
+// The slow path sleeps inside try_wait (the hardware suspends the thread until the phase completes or the hint, in
+// nanoseconds, runs out) instead of spinning: a waiting warp takes no issue slots from the warps that have work.
+constexpr uint32_t kSleepPolls = 1u << 18;
+constexpr uint32_t kSleepHintNs = 4000;
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t addr, uint32_t parity) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i)
-        if (mbar_try(addr, parity)) return true;
+    for (uint32_t i = 0; i < kSleepPolls; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity), "r"(kSleepHintNs)
+            : "memory");
+        if (done) return true;
+    }
     return false;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_addr(bar);
+__device__ __forceinline__ bool mbar_wait_addr(uint32_t addr, uint32_t parity) {
     if (mbar_try(addr, parity)) return true;  // the common case costs one poll and no loop
     return mbar_wait_slow(addr, parity);
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) { return mbar_wait_addr(smem_addr(bar), parity); }
+
+__device__ __forceinline__ void mbar_arrive_addr(uint32_t addr) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(addr) : "memory");
 }
 
 // `bytes` (a multiple of 16) from 16-byte-aligned global memory to 16-byte-aligned shared memory of this CTA; completion

@@ -64,6 +64,27 @@ __host__ __device__ inline GemvSmem gemv_smem(uint32_t rm, uint32_t slice_k, uin
     return s;
 }
 
+// Shared-memory carve-up of a dense decode-row CTA (t3_dense_rows.cu). xp: `xp_bufs` buffers of the prepared rows of
+// `chunk_blocks` 128-input blocks; local: where the two K groups meet; recv: `recv_bufs` buffers of the partial sums the
+// cluster's ranks send for the rows this CTA owns; dq: B fragments decoded ahead of the dependency wait (16 bytes a lane a
+// tile, `dq_stages` ring stages a warp); ring: the code stages.
+struct DenseSmem {
+    uint32_t bars, xp, local, recv, dq, ring, total;
+};
+__host__ __device__ inline DenseSmem dense_smem(uint32_t rm, uint32_t chunk_blocks, uint32_t xp_bufs, uint32_t recv_bufs,
+                                                uint32_t cluster, uint32_t dq_stages, uint32_t stage_bytes, uint32_t stages) {
+    DenseSmem s;
+    auto up = [](uint32_t v) { return (v + 127u) & ~127u; };
+    s.bars = 0;
+    s.xp = up((2u * kMaxStages + 6u) * 8u);
+    s.local = s.xp + up(xp_bufs * rm * (chunk_blocks * 128u + kXpPad) * 2u);
+    s.recv = s.local + up(rm * kPartialStride * 4u);
+    s.dq = s.recv + up(recv_bufs * cluster * rows_owned(rm, cluster) * kPartialStride * 4u);
+    s.ring = s.dq + kConsumerWarps * dq_stages * kBatch * 512u;
+    s.total = s.ring + stage_bytes * stages;
+    return s;
+}
+
 // The CTA's dynamic shared memory rounded up to 128 bytes (launches ask for kSmemSlack bytes more than the carve-up).
 constexpr uint32_t kSmemSlack = 128;
 __device__ __forceinline__ uint8_t* aligned_smem(uint8_t* raw) {
@@ -277,6 +298,55 @@ __device__ __forceinline__ void finish_block(float (&v)[4], const float (&sv)[4]
 __device__ __forceinline__ void load_scales(const __half* blk, uint32_t lane, float (&sv)[4]) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) sv[j] = __half2float(blk[lane + 32u * j]);
+}
+
+// ---- one-sided pushes between the CTAs of a cluster -----------------------------------------------------------------
+
+// the shared::cluster address of `p` (an address in this CTA's shared memory) as CTA `rank` of the cluster sees its own copy
+__device__ __forceinline__ uint32_t peer_addr(const void* p, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr(p)), "r"(rank));
+    return r;
+}
+
+// Two floats into a peer's shared memory; the 8 bytes are counted on the peer's barrier `bar` when they have landed, so
+// the receiver waits on its own barrier and the sender waits for nothing.
+__device__ __forceinline__ void push_f32x2(uint32_t dst, float a, float b, uint32_t bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];" ::"r"(dst), "f"(a),
+                 "f"(b), "r"(bar)
+                 : "memory");
+}
+
+// one arrival on a peer's barrier; this thread's earlier writes are visible to whoever then passes that barrier
+__device__ __forceinline__ void peer_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// waits for a barrier that peers of the cluster arrive on (acquire at cluster scope); bounded like mbar_wait
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_addr(bar);
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+// tk rows (16 inputs each) [t0, t1) of rank r when T rows are cut over s ranks, balanced to a row
+// (T is at most 2^26 / 16 and s at most 16, so the products fit 32 bits)
+__host__ __device__ inline void slice_rows(uint32_t T, uint32_t s, uint32_t r, uint32_t& t0, uint32_t& t1) {
+    t0 = T * r / s;
+    t1 = T * (r + 1u) / s;
 }
 
 // K blocks [b0, b1) of rank r when nb 128-blocks are cut over s ranks
