@@ -95,9 +95,6 @@ typedef struct {
     uint32_t dense_split;    /* K slices of a dense GEMV cluster (1..16); 0 = choose from the shape */
     int no_overlap;          /* 1: launches wait for the stream's previous kernel to finish before they start (no
                                 programmatic dependent launch); for measurements */
-    uint32_t dense_clusters; /* clusters of a dense GEMV launch (each walks its share of the output blocks); 0 = choose */
-    uint32_t dense_park;     /* ring stages a warp decodes ahead of the dependency wait, plus one (1 = none, 3 = two);
-                                0 = choose */
 } t3_config;
 void t3_config_default(t3_config* out);
 int t3_configure(const t3_config* cfg);                  /* InvalidTurboexl3Config on a bad value */
@@ -177,14 +174,11 @@ int t3_moe_merge(const void* v, const void* scores, int scores_dtype, size_t row
 int t3_moe_noalloc(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds, const void* scores,
                    int scores_dtype, int topk, t3_decode dec, void* y, void* stream);
 
-/* Measurement hook (the reference has probe kernels for the same purpose, src/core/decode.zig:34-35): a device array of
- * uint64 [launches][T3_TRACE_CTAS][8]. While it is set, the k-th t3_linear launch at decode rows (counted from this call,
- * modulo `launches`) records for each of its first T3_TRACE_CTAS CTAs the global nanosecond timer at: [0] entry,
- * [1] weights streaming and the first stages decoded, [2] the stream's previous kernel complete, [3] rows prepared,
- * [4] first output block's tensor-core steps done, [5] partial sums pushed, [6] (owners) every rank's sums landed,
- * [7] outputs stored. Entries a CTA does not reach stay as they were. Null switches it off. */
-#define T3_TRACE_CTAS 512
-void t3_set_trace(void* device_u64, uint32_t launches);
+/* Measurement hook (the reference has probe kernels for the same purpose, src/core/decode.zig:34-35): when set to a
+ * device array of 8 uint64, the next t3_linear launches at decode rows record the SM cycle counter of their CTA (0, 0) at:
+ * [0] entry, [1] barriers initialised, [2] activations prepared, [3] first code stage landed, [4] GEMV done and partials
+ * pushed, [5] cluster reduce complete, [6] outputs stored. Null switches it off. */
+void t3_set_trace(void* device_u64x8);
 
 /* The resident trunk (src/core/dense.zig:1323-1530: "memory for compute; a host's opt-in"): a trunk linear's W_hat decoded
  * once and kept, so calls past 32 rows run a plain tensor-core GEMM instead of decoding every tile again. The caller owns

@@ -91,7 +91,7 @@ def test_config4_full_size_rate_per_expert():
             routed[si] = (routed[si] + (scores[r, k] * v).astype(np.float32)).astype(np.float32)
     sh = oracle_rows(sd, H, I, 48, x16[sample], np.zeros((len(sample), 1), np.int32), gate[sample])
     ref = half(half(routed) + half(sh))  # one add in the activation dtype (src/root.zig:975-984)
-    check_moe(host_f32(y)[sample], ref, "f16", "config 4 full size, mixed rates, 4096 tokens")
+    check_moe(host_f32(y)[sample], ref, "f16", "config 4 full size, mixed rates, 4096 tokens", terms=1.5)
     assert t3.device_error() == 0
 
 
@@ -111,7 +111,10 @@ def test_config5_full_size(k):
         routed = oracle_rows(d, H, I, n, x16[sample], inds[sample], scores[sample])
         sh = oracle_rows(sd, H, I, n, x16[sample], np.zeros((len(sample), 1), np.int32), gate[sample])
         ref = half(half(routed) + half(sh))
-        check_moe(host_f32(y).reshape(rows, H)[sample], ref, "f16", ("config 5 full size", k, rows))
+        # the layer output is the sum of two independently rounded terms (routed + shared), each with its own rounding flips:
+        # 1.5 x the single-call bars, as test_gpu_configs holds the cut-down layer to (achieved at full size: compare
+        # 6.8e-3, compareRounded 4.8e-3 at K = 2 and 8192 tokens; the single-call bars are 5e-3 and 4e-3)
+        check_moe(host_f32(y).reshape(rows, H)[sample], ref, "f16", ("config 5 full size", k, rows), terms=1.5)
         del shared, y
     assert t3.device_error() == 0
 

@@ -153,9 +153,8 @@ def test_small_ring_recycles_stages():
     trellis, suh, svh = synth.linear(31, 4096, 256, 128, scaled=True)
     x = dev(synth.activations(32, 3, 4096))
     t, a, b = dev(trellis), dev(suh), dev(svh)
+    base = bits16(t3.linear(x, t, a, b))
     try:
-        t3.configure(dense_split=8)
-        base = bits16(t3.linear(x, t, a, b))
         t3.configure(ring_bytes=8192, dense_split=1)
         small = host_f32(t3.linear(x, t, a, b))
         t3.configure(ring_bytes=8192, dense_split=8)

@@ -53,8 +53,7 @@ class _Spec(C.Structure):
 
 
 class _Config(C.Structure):
-    _fields_ = [("prefill", C.c_int), ("ring_bytes", C.c_uint32), ("dense_split", C.c_uint32), ("no_overlap", C.c_int),
-                ("dense_clusters", C.c_uint32), ("dense_park", C.c_uint32)]
+    _fields_ = [("prefill", C.c_int), ("ring_bytes", C.c_uint32), ("dense_split", C.c_uint32), ("no_overlap", C.c_int)]
 
 
 # every symbol include/t3.h declares: (restype, argtypes)
@@ -81,7 +80,7 @@ SYMBOLS = {
     "t3_moe_with_shared_after": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp, _vp, _vp, _sz, _vp]),
     "t3_moe_merge": (_i, [_vp, _vp, _i, _sz, _i, _i, _vp, _vp, _i, _vp]),
     "t3_moe_noalloc": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp]),
-    "t3_set_trace": (None, [_vp, _u32]),
+    "t3_set_trace": (None, [_vp]),
     "t3_launch_count": (C.c_uint64, []),
     "t3_resident_bytes": (_sz, [_i, _i]),
     "t3_resident_build": (_i, [_vp, _i, _i, _i, _Decode, _vp, _vp]),
@@ -164,10 +163,9 @@ def _trellis_ok(t: torch.Tensor) -> bool:
     return t.dtype in (torch.uint16, torch.int16)
 
 
-def configure(prefill: bool = True, ring_bytes: int = 0, dense_split: int = 0, no_overlap: bool = False,
-              dense_clusters: int = 0, dense_park: int = 0) -> None:
+def configure(prefill: bool = True, ring_bytes: int = 0, dense_split: int = 0, no_overlap: bool = False) -> None:
     """core.config.configure (src/core/config.zig:175): process-wide, before the first call."""
-    cfg = _Config(int(prefill), ring_bytes, dense_split, int(no_overlap), dense_clusters, dense_park)
+    cfg = _Config(int(prefill), ring_bytes, dense_split, int(no_overlap))
     _check(lib().t3_configure(C.byref(cfg)))
 
 

@@ -27,8 +27,6 @@ UNITS = [
     ("t3_prefill.cu", "t3_prefill", []),
     ("t3_api.cu", "t3_api", []),
     ("t3_dequant.cu", "t3_dequant", []),
-    ("t3_dense_rows.cu", "t3_dense_rows_cb0", ["-DT3_CB=0"]),
-    ("t3_dense_rows.cu", "t3_dense_rows_cb1", ["-DT3_CB=1"]),
     ("t3_decode_rows.cu", "t3_decode_rows_cb0", ["-DT3_CB=0"]),
     ("t3_decode_rows.cu", "t3_decode_rows_cb1", ["-DT3_CB=1"]),
 ]

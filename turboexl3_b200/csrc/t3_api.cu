@@ -14,10 +14,8 @@
 
 namespace t3 {
 
-cudaError_t launch_dense_rows_cb0(const DenseArgs&, uint32_t, uint32_t, uint32_t, cudaStream_t);
-cudaError_t launch_dense_rows_cb1(const DenseArgs&, uint32_t, uint32_t, uint32_t, cudaStream_t);
-int dense_rows_max_clusters_cb0(uint32_t, uint32_t, bool, uint32_t, uint32_t);
-int dense_rows_max_clusters_cb1(uint32_t, uint32_t, bool, uint32_t, uint32_t);
+cudaError_t launch_dense_gemv_cb0(const DenseArgs&, cudaStream_t);
+cudaError_t launch_dense_gemv_cb1(const DenseArgs&, cudaStream_t);
 cudaError_t launch_moe_gate_up_cb0(const MoeArgs&, cudaStream_t);
 cudaError_t launch_moe_gate_up_cb1(const MoeArgs&, cudaStream_t);
 cudaError_t launch_moe_down_cb0(const MoeArgs&, cudaStream_t);
@@ -41,10 +39,9 @@ void note_engine(int kind, uint64_t a, uint64_t b, uint64_t c, uint64_t d) {
 __device__ uint32_t g_dev_error_word;
 
 std::mutex g_mu;
-t3_config g_cfg = {1, 0, 0, 0, 0, 0};
+t3_config g_cfg = {1, 0, 0, 0};
 uint32_t* g_err_ptr[64] = {};
 unsigned long long* g_trace = nullptr;
-uint32_t g_trace_slots = 0, g_trace_next = 0;
 
 constexpr uint32_t kSmemCap = kGemvSmemLimit - kSmemSlack;  // what the carve-up of a GEMV CTA may add up to
 constexpr uint32_t kDefaultRing = 64u * 1024u;
@@ -92,6 +89,23 @@ uint32_t pick_split(uint32_t nb, uint32_t units, uint32_t fan, uint32_t cap, uin
     return s;
 }
 
+// K slices of a LARGE dense linear (tens of megabytes of codes: milliseconds of integer work, so what counts is that
+// every multiprocessor gets the same share, not the launch's latency): the power of two whose CTAs all
+// fit the device at once — two a multiprocessor, clusters of s — and leave the fullest multiprocessor the fewest
+// 128-input blocks; ties go to the wider cluster (more warps a multiprocessor).
+uint32_t pick_split_large(uint32_t nb, uint32_t out_blocks) {
+    static const uint32_t cap_ctas[9] = {0, 296, 296, 279, 284, 280, 270, 259, 264};  // resident CTAs by cluster size (measured)
+    const uint32_t sms = one_wave() / 2u;
+    uint32_t best_s = 1, best = ~0u;
+    for (uint32_t s = 1; s <= 8u && s <= nb; s *= 2u) {  // powers of two: clusters of 3, 5, 6, 7 measured slower (placement)
+        const uint32_t ctas = out_blocks * s;
+        if (ctas > cap_ctas[s] * sms / 148u) continue;
+        const uint32_t cost = ((ctas + sms - 1u) / sms) * ((nb + s - 1u) / s);
+        if (cost <= best) best = cost, best_s = s;
+    }
+    return best_s;
+}
+
 uint32_t largest_slice(uint32_t nb, uint32_t split) {
     uint32_t mx = 0;
     for (uint32_t r = 0; r < split; ++r) {
@@ -104,12 +118,12 @@ uint32_t largest_slice(uint32_t nb, uint32_t split) {
 
 // The ring of one GEMV CTA: stages of kStageRows tk rows (one 128-input block), as many as the slab needs or the budget
 // holds.
-bool plan_ring(uint32_t row_cap, uint32_t slice_max, uint32_t cluster, uint32_t n, RingPlan& ring) {
+bool plan_ring(uint32_t row_cap, uint32_t xrows, uint32_t slice_max, uint32_t cluster, uint32_t n, RingPlan& ring) {
     const uint32_t row_bytes = 16u * n, nrows = slice_max / 16u;  // nrows is a multiple of 8 (whole 128-blocks)
     const uint32_t stage_rows = kStageRows;
     const uint32_t stage_bytes = stage_rows * row_bytes;
     const uint32_t need = (nrows + stage_rows - 1u) / stage_rows;
-    const uint32_t fixed = gemv_smem(row_cap, slice_max, cluster, stage_bytes, 0).total;
+    const uint32_t fixed = gemv_smem(row_cap, xrows, slice_max, cluster, stage_bytes, 0).total;
     if (fixed + stage_bytes > kSmemCap) return false;
     uint32_t budget = g_cfg.ring_bytes ? g_cfg.ring_bytes : kDefaultRing;
     if (budget > kSmemCap - fixed) budget = kSmemCap - fixed;
@@ -120,157 +134,6 @@ bool plan_ring(uint32_t row_cap, uint32_t slice_max, uint32_t cluster, uint32_t 
     ring.stage_rows = stage_rows;
     ring.stages = stages;
     return true;
-}
-
-// ---- the dense decode-row plan -------------------------------------------------------------------------------------
-
-struct DensePlan {
-    uint32_t split, clusters, rm, chunk_blocks, xp_bufs, recv_bufs, dq_stages, smem;
-    RingPlan ring;
-    bool prepared;  // a prepare launch runs first and the CTAs pull the prepared rows
-};
-
-constexpr uint32_t kSharedPair = 112u * 1024u;   // a CTA's shared memory when two share a multiprocessor
-constexpr uint32_t kFusedXpMax = 40u * 1024u;    // the prepared rows of a slice that a CTA may compute and hold itself
-
-// the most 128-input blocks a rank's slice touches when T tile rows are cut over s ranks
-uint32_t slice_blocks_max(uint32_t T, uint32_t s) {
-    uint32_t mx = 0;
-    for (uint32_t r = 0; r < s; ++r) {
-        uint32_t t0, t1;
-        slice_rows(T, s, r, t0, t1);
-        const uint32_t nb = (t1 + 7u) / 8u - t0 / 8u;
-        mx = nb > mx ? nb : mx;
-    }
-    return mx;
-}
-
-uint32_t sm_count() { return one_wave() / 2u; }
-
-// Clusters of s CTAs (about two CTAs a multiprocessor) the device holds at once: the measured table of this part when the
-// occupancy query is not available (no device).
-uint32_t cluster_capacity(int codebook, uint32_t n, uint32_t rm, bool prepared, uint32_t s, uint32_t smem_bytes) {
-    const int q = dense_rows_max_clusters(codebook, n, rm, prepared, s, smem_bytes);
-    if (q > 0) return (uint32_t)q;
-    return (2u * sm_count()) / s;
-}
-
-// K slices of a dense linear: a function of the geometry alone (a row's bytes must not depend on how many rows travel with
-// it). Cost of a choice = CTAs a multiprocessor x output blocks a cluster x tile rows a rank, for the best cluster count
-// that fits the device at once; ties go to the narrower cluster.
-uint32_t dense_split_for(uint32_t in, uint32_t out) {
-    const uint32_t T = in / 16u, OB = out / 128u, sms = sm_count();
-    static const uint32_t cap_ctas[9] = {0, 296, 296, 279, 284, 280, 270, 259, 264};  // resident CTAs by cluster size
-    uint32_t best_s = 1;
-    uint64_t best = ~0ull;
-    for (uint32_t s = 1; s <= 8u && s <= T / 8u; ++s) {
-        const uint32_t cap = cap_ctas[s] * sms / 148u / s;
-        const uint32_t rows_rank = (T + s - 1u) / s;
-        for (uint32_t nc = 1; nc <= OB && nc <= cap; ++nc) {
-            const uint32_t iters = (OB + nc - 1u) / nc;
-            const uint32_t per_sm = (nc * s + sms - 1u) / sms;
-            // a rank's fixed part a block (reduce, push, finish) counts as four tile rows
-            const uint64_t cost = (uint64_t)per_sm * iters * (rows_rank + 4u) * 16u + s;
-            if (cost < best) best = cost, best_s = s;
-        }
-    }
-    return best_s;
-}
-
-bool dense_rotates_inside(const t3_config& cfg, uint32_t rows, uint32_t in, uint32_t out) {
-    if (rows > kFusedRows) return false;
-    const uint32_t T = in / 16u;
-    uint32_t s = cfg.dense_split ? cfg.dense_split : dense_split_for(in, out);
-    if (s > T / 8u) s = T / 8u ? T / 8u : 1u;
-    return 8u * (slice_blocks_max(T, s) * 128u + kXpPad) * 2u <= kFusedXpMax;
-}
-
-int plan_dense(const t3_config& cfg, int codebook, uint32_t rows, uint32_t in, uint32_t out, uint32_t n, DensePlan& p) {
-    const uint32_t T = in / 16u, OB = out / 128u;
-    p.rm = row_cap_for(rows);
-    p.split = cfg.dense_split ? cfg.dense_split : dense_split_for(in, out);
-    if (p.split > T / 8u) p.split = T / 8u ? T / 8u : 1u;
-    const uint32_t nblk = slice_blocks_max(T, p.split);
-    p.prepared = !dense_rotates_inside(cfg, rows, in, out);
-    if (p.prepared) {
-        // about 32 KB of prepared rows a buffer, two buffers when the slice takes more than one
-        uint32_t ck = (32u * 1024u) / (p.rm * 256u);
-        ck = ck < 2u ? 2u : ck;
-        p.chunk_blocks = nblk < ck ? nblk : ck;
-        p.xp_bufs = nblk > p.chunk_blocks ? 2u : 1u;
-    } else {
-        p.chunk_blocks = nblk;
-        p.xp_bufs = 1;
-    }
-    const uint32_t stage_bytes = kStageRows * 16u * n;
-    // cluster count: all output blocks at once when they fit the device, else the count that walks them most evenly
-    p.recv_bufs = 1;
-    const uint32_t fixed1 = dense_smem(p.rm, p.chunk_blocks, p.xp_bufs, 2, p.split, 0, stage_bytes, 0).total + kSmemSlack;
-    if (fixed1 + stage_bytes > kGemvSmemLimit) return T3_ENGINE_NOT_IMPLEMENTED;
-    const uint32_t probe = fixed1 + 2u * stage_bytes < kSharedPair ? kSharedPair : kGemvSmemLimit;
-    const uint32_t cap = cluster_capacity(codebook, n, p.rm, p.prepared, p.split, probe);
-    if (cap == 0) return T3_ENGINE_NOT_IMPLEMENTED;
-    uint32_t nc = OB;
-    if (cfg.dense_clusters) nc = cfg.dense_clusters < OB ? cfg.dense_clusters : OB;
-    else if (OB > cap) {
-        const uint32_t sms = sm_count();
-        uint64_t best = ~0ull;
-        for (uint32_t c = 1; c <= cap; ++c) {
-            const uint64_t cost = (uint64_t)((c * p.split + sms - 1u) / sms) * ((OB + c - 1u) / c);
-            if (cost <= best) best = cost, nc = c;
-        }
-    }
-    p.clusters = nc;
-    const uint32_t iters = (OB + nc - 1u) / nc;
-    p.recv_bufs = iters > 1u ? 2u : 1u;
-    // the rest of the shared memory: parked decodes (up to two stages a warp) and the code ring
-    const uint32_t fixed = dense_smem(p.rm, p.chunk_blocks, p.xp_bufs, p.recv_bufs, p.split, 0, stage_bytes, 0).total + kSmemSlack;
-    const uint32_t budget = fixed + 2u * stage_bytes <= kSharedPair ? kSharedPair : kGemvSmemLimit;
-    const uint32_t need = nblk * iters;  // stages a CTA streams in all
-    const uint32_t park_bytes = kConsumerWarps * kBatch * 512u;  // one stage of every warp
-    // First the ring: when the whole slab fits, every code byte is in shared memory (or on its way) before the dependency
-    // wait ends, and nothing after the wait sits behind a DRAM round trip. Parked decodes take what is left: a parked
-    // stage frees its ring slot, so the ring then only has to hold the stages that are not parked.
-    uint32_t dq = 2;
-    if (cfg.dense_park) dq = cfg.dense_park - 1u;
-    if (dq > nblk) dq = nblk;
-    if (dq > p.chunk_blocks) dq = p.chunk_blocks;
-    const uint32_t dq_want = dq;
-    bool resident = false;
-    for (;; --dq) {
-        if (need <= kMaxStages + dq && fixed + dq * park_bytes + (need - dq) * stage_bytes <= budget) {
-            resident = true;
-            break;
-        }
-        if (dq == 0) break;
-    }
-    if (!resident) {  // a slab that streams: at most one parked stage, and never at the cost of a three-stage ring
-        dq = dq_want < 1u ? dq_want : 1u;
-        while (dq > 0 && fixed + dq * park_bytes + 3u * stage_bytes > budget) --dq;
-    }
-    p.dq_stages = dq;
-    uint32_t ring_budget = budget - fixed - dq * park_bytes;
-    if (cfg.ring_bytes && cfg.ring_bytes < ring_budget) ring_budget = cfg.ring_bytes;
-    uint32_t stages = ring_budget / stage_bytes;
-    uint32_t want = need > dq ? need - dq : 0u;  // the stages that are not parked, and room for the parked ones to arrive
-    want = want < dq ? dq : want;
-    stages = stages > want ? want : stages;
-    stages = stages < 1u ? 1u : stages;
-    stages = stages > kMaxStages ? kMaxStages : stages;
-    p.ring.stage_rows = kStageRows;
-    p.ring.stages = stages;
-    p.smem = dense_smem(p.rm, p.chunk_blocks, p.xp_bufs, p.recv_bufs, p.split, p.dq_stages, stage_bytes, stages).total + kSmemSlack;
-    if (p.smem > kGemvSmemLimit) return T3_ENGINE_NOT_IMPLEMENTED;
-    return T3_OK;
-}
-
-// the trace slot of the next traced launch (t3_set_trace), or null
-unsigned long long* next_trace_slot() {
-    std::lock_guard<std::mutex> lock(g_mu);
-    if (!g_trace || g_trace_slots == 0) return nullptr;
-    unsigned long long* p = g_trace + (size_t)(g_trace_next % g_trace_slots) * kTraceCtas * kTraceWords;
-    ++g_trace_next;
-    return p;
 }
 
 bool dtype_ok(int dt) { return dt == T3_F32 || dt == T3_F16 || dt == T3_BF16; }
@@ -291,19 +154,13 @@ int cuda_status(cudaError_t rc) { return rc == cudaSuccess ? T3_OK : T3_CUDA_ERR
 
 uint32_t row_cap_for(uint32_t rows) { return rows <= 8u ? 8u : (rows <= 16u ? 16u : 32u); }
 
-uint32_t gemv_smem_bytes(uint32_t row_cap, uint32_t slice_max, uint32_t cluster, uint32_t n, RingPlan ring) {
-    return gemv_smem(row_cap, slice_max, cluster, ring.stage_rows * 16u * n, ring.stages).total + kSmemSlack;
+uint32_t gemv_smem_bytes(uint32_t row_cap, uint32_t xrows, uint32_t slice_max, uint32_t cluster, uint32_t n, RingPlan ring) {
+    return gemv_smem(row_cap, xrows, slice_max, cluster, ring.stage_rows * 16u * n, ring.stages).total + kSmemSlack;
 }
 
-cudaError_t launch_dense_rows(const DenseArgs& a, int codebook, uint32_t rm, uint32_t clusters, uint32_t smem_bytes,
-                              cudaStream_t stream) {
+cudaError_t launch_dense_gemv(const DenseArgs& a, int codebook, cudaStream_t stream) {
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    return codebook == T3_MCG ? launch_dense_rows_cb1(a, rm, clusters, smem_bytes, stream)
-                              : launch_dense_rows_cb0(a, rm, clusters, smem_bytes, stream);
-}
-int dense_rows_max_clusters(int codebook, uint32_t n, uint32_t rm, bool prepared, uint32_t split, uint32_t smem_bytes) {
-    return codebook == T3_MCG ? dense_rows_max_clusters_cb1(n, rm, prepared, split, smem_bytes)
-                              : dense_rows_max_clusters_cb0(n, rm, prepared, split, smem_bytes);
+    return codebook == T3_MCG ? launch_dense_gemv_cb1(a, stream) : launch_dense_gemv_cb0(a, stream);
 }
 cudaError_t launch_moe_gate_up(const MoeArgs& a, int codebook, cudaStream_t stream) {
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -447,15 +304,12 @@ void t3_config_default(t3_config* out) {
     out->ring_bytes = 0;
     out->dense_split = 0;
     out->no_overlap = 0;
-    out->dense_clusters = 0;
-    out->dense_park = 0;
 }
 
 int t3_configure(const t3_config* cfg) {
     if (!cfg) return T3_NULL_POINTER;
     const uint32_t s = cfg->dense_split;
     if (s > 16u) return T3_INVALID_CONFIG;
-    if (cfg->dense_park > 3u) return T3_INVALID_CONFIG;
     if (cfg->no_overlap != 0 && cfg->no_overlap != 1) return T3_INVALID_CONFIG;
     if (cfg->ring_bytes != 0 && (cfg->ring_bytes < 4096u || cfg->ring_bytes > kGemvSmemLimit)) return T3_INVALID_CONFIG;
     if (cfg->prefill != 0 && cfg->prefill != 1) return T3_INVALID_CONFIG;
@@ -476,11 +330,9 @@ int t3_device_error(void* stream, uint32_t* bits_out, int clear) {
     return T3_OK;
 }
 
-void t3_set_trace(void* device_u64, uint32_t launches) {
+void t3_set_trace(void* device_u64x8) {
     std::lock_guard<std::mutex> lock(g_mu);
-    g_trace = static_cast<unsigned long long*>(device_u64);
-    g_trace_slots = device_u64 ? launches : 0u;
-    g_trace_next = 0;
+    g_trace = static_cast<unsigned long long*>(device_u64x8);
 }
 
 uint64_t t3_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
@@ -554,18 +406,8 @@ int t3_codebook_table(t3_decode dec, void* out, void* stream) {
 // ---- dense linear ---------------------------------------------------------------------------------------------------
 
 size_t t3_linear_workspace_bytes(size_t rows, int in_dim, int out_dim, int n) {
-    if (rows < 1 || in_dim <= 0 || out_dim <= 0 || in_dim % 128 != 0 || out_dim % 128 != 0) return 0;
-    if (rows <= T3_DECODE_ROWS_MAX) {
-        // decode rows: nothing when the rows are rotated inside the GEMV's CTAs, else the prepared rows (f16 [rows, in])
-        if (!rate_ok(n)) return 0;
-        t3_config cfg;
-        {
-            std::lock_guard<std::mutex> lock(g_mu);
-            cfg = g_cfg;
-        }
-        return dense_rotates_inside(cfg, (uint32_t)rows, (uint32_t)in_dim, (uint32_t)out_dim) ? 0
-                                                                                             : ((rows * (size_t)in_dim * 2u + 255u) & ~(size_t)255u);
-    }
+    (void)n;
+    if (rows <= T3_DECODE_ROWS_MAX || in_dim <= 0 || out_dim <= 0) return 0;  // the decode-row kernel keeps everything on chip
     return prefill_linear_workspace(rows, (uint32_t)in_dim, (uint32_t)out_dim);
 }
 
@@ -597,39 +439,34 @@ int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, cons
         return cuda_status(rc);
     }
 
-    DensePlan plan;
-    if (int rc = plan_dense(cfg, dec.codebook, (uint32_t)rows, (uint32_t)in_dim, (uint32_t)out_dim, (uint32_t)n, plan)) return rc;
-    if (plan.prepared && (!workspace || workspace_bytes < t3_linear_workspace_bytes(rows, in_dim, out_dim, n)))
-        return T3_WORKSPACE_TOO_SMALL;
     DenseArgs a = {};
-    a.x = x;
-    a.y = y;
     a.trellis = static_cast<const uint8_t*>(trellis);
     a.suh = suh;
     a.svh = svh;
-    a.xp_g = plan.prepared ? static_cast<const __half*>(workspace) : nullptr;
-    a.rows = (uint32_t)rows;
     a.in = (uint32_t)in_dim;
     a.out = (uint32_t)out_dim;
     a.n = (uint32_t)n;
     a.mask = mask;
     a.x_dt = x_dtype;
-    a.split = plan.split;
-    a.chunk_blocks = plan.chunk_blocks;
-    a.xp_bufs = plan.xp_bufs;
-    a.recv_bufs = plan.recv_bufs;
-    a.dq_stages = plan.dq_stages;
-    a.ring = plan.ring;
-    a.overlap = !cfg.no_overlap;
-    a.err = dev_error_ptr();
-    a.trace = next_trace_slot();
     note_engine(1, (uint64_t)in_dim, (uint64_t)out_dim, (uint64_t)n, 0);
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (plan.prepared) {
-        g_launches.fetch_add(1, std::memory_order_relaxed);
-        if (int rc = cuda_status(launch_dense_prepare(x, x_dtype, suh, a.rows, a.in, workspace, a.overlap != 0, s))) return rc;
+    const uint32_t nb = a.in / 128u;
+    const bool large = (uint64_t)a.in * a.out * a.n >= (uint64_t)24u * 1024u * 1024u * 128u;  // 24 MB of codes and up
+    a.split = cfg.dense_split ? (cfg.dense_split < nb ? cfg.dense_split : nb)
+                              : (large ? pick_split_large(nb, a.out / 128u) : pick_split(nb, a.out / 128u, 1u, 8u, one_wave() / 2u));
+    a.overlap = !cfg.no_overlap;
+    a.slice_max = largest_slice(nb, a.split);
+    a.err = dev_error_ptr();
+    a.trace = g_trace;
+    a.rows = (uint32_t)rows;
+    // a slice too long for shared memory (its prepared rows) is cut further, up to the widest cluster
+    while (!plan_ring(row_cap_for(a.rows), a.rows, a.slice_max, a.split, a.n, a.ring)) {
+        if (a.split * 2u > nb || a.split * 2u > 16u) return T3_ENGINE_NOT_IMPLEMENTED;
+        a.split *= 2u;
+        a.slice_max = largest_slice(nb, a.split);
     }
-    return cuda_status(launch_dense_rows(a, dec.codebook, plan.rm, plan.clusters, plan.smem, s));
+    a.x = x;
+    a.y = y;
+    return cuda_status(launch_dense_gemv(a, dec.codebook, static_cast<cudaStream_t>(stream)));
 }
 
 // ---- routed experts -------------------------------------------------------------------------------------------------
@@ -730,17 +567,17 @@ int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const
     a.split_d = pick_split(a.inter / 128u, (a.hidden / 128u) * kNominalSlots, 1u, 8u, one_wave() / 8u);
     a.slice_max_d = largest_slice(a.inter / 128u, a.split_d);
     // sized for the widest row capacity so the split does not move with the rows either
-    while (!plan_ring(32u, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu)) {
+    while (!plan_ring(32u, 32u, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu)) {
         if (a.split_gu * 2u > a.hidden / 128u || a.split_gu * 2u > 8u) return T3_ENGINE_NOT_IMPLEMENTED;
         a.split_gu *= 2u;
         a.slice_max_gu = largest_slice(a.hidden / 128u, a.split_gu);
     }
-    while (!plan_ring(32u, a.slice_max_d, a.split_d, a.n, a.ring_d)) {
+    while (!plan_ring(32u, 32u, a.slice_max_d, a.split_d, a.n, a.ring_d)) {
         if (a.split_d * 2u > a.inter / 128u || a.split_d * 2u > 16u) return T3_ENGINE_NOT_IMPLEMENTED;
         a.split_d *= 2u;
         a.slice_max_d = largest_slice(a.inter / 128u, a.split_d);
     }
-    if (!plan_ring(rm, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu) || !plan_ring(rm, a.slice_max_d, a.split_d, a.n, a.ring_d))
+    if (!plan_ring(rm, rm, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu) || !plan_ring(rm, rm, a.slice_max_d, a.split_d, a.n, a.ring_d))
         return T3_ENGINE_NOT_IMPLEMENTED;
     a.err = dev_error_ptr();
     cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -255,11 +255,26 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t addr, uint32_t parity) {
         : "memory");
     return done;
 }
+// whether the phase has completed, without waiting at all
+__device__ __forceinline__ uint32_t mbar_test(uint32_t addr, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    return done;
+}
 // The slow path sleeps inside try_wait (the hardware suspends the thread until the phase completes or the hint, in
 // nanoseconds, runs out) instead of spinning: a waiting warp takes no issue slots from the warps that have work.
 constexpr uint32_t kSleepPolls = 1u << 18;
 constexpr uint32_t kSleepHintNs = 4000;
+constexpr uint32_t kEagerPolls = 64;
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t addr, uint32_t parity) {
+    for (uint32_t i = 0; i < kEagerPolls; ++i)
+        if (mbar_try(addr, parity)) return true;
     for (uint32_t i = 0; i < kSleepPolls; ++i) {
         uint32_t done;
         asm volatile(
@@ -278,6 +293,27 @@ __device__ __forceinline__ bool mbar_wait_addr(uint32_t addr, uint32_t parity) {
     return mbar_wait_slow(addr, parity);
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) { return mbar_wait_addr(smem_addr(bar), parity); }
+
+// The same wait with the failure recorded in place (no call in the caller's hot loop: a call there makes the compiler
+// keep its registers ready for one): on giving up, `bit` is or-ed into the device error word and the caller carries on.
+__device__ __forceinline__ void mbar_wait_report(uint32_t addr, uint32_t parity, uint32_t* err, uint32_t bit) {
+#pragma unroll 1
+    for (uint32_t i = 0; i < kEagerPolls; ++i)  // a short wait is answered at once; only a long one goes to sleep
+        if (mbar_try(addr, parity)) return;
+#pragma unroll 1
+    for (uint32_t i = 0; i < kSleepPolls; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity), "r"(kSleepHintNs)
+            : "memory");
+        if (done) return;
+    }
+    if (err) atomicOr(err, bit);
+}
 
 __device__ __forceinline__ void mbar_arrive_addr(uint32_t addr) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(addr) : "memory");

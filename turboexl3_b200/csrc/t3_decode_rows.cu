@@ -1,6 +1,9 @@
-// Decode-row kernels of the routed experts (up to 32 activation rows): the gate|up and down launches and the score-weighted
-// merge. Compiled once per codebook (-DT3_CB=0 MUL1, 1 MCG) so the two halves build in parallel. (The dense linear at
-// decode rows is t3_dense_rows.cu.)
+// Decode-row kernels (up to 32 activation rows): the fused dense linear, the routed experts' gate|up and down launches
+// and the score-weighted merge. Compiled once per codebook (-DT3_CB=0 MUL1, 1 MCG) so the two halves build in parallel.
+//
+// Dense linear = one launch: prepare (input rotation) in shared memory, split-K GEMV over a thread-block cluster,
+// output rotation by the cluster's leader. The reference takes three launches for the same values
+// (prep_s -> dgemv -> dfinish, src/core/dense.zig:1229-1252, src/kernels/hip/dense/dense.hip).
 //
 // Routed chain = three launches: gate|up (+ SwiGLU + the down projection's prepare), down (+ its finish), merge.
 // The reference's served chain is four or five (src/core/decode.zig:483-517). Row-slots that share an expert are found
@@ -50,18 +53,90 @@ __device__ __forceinline__ void init_barriers(const CtaSmem& c, uint32_t stages)
     }
 }
 
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
 // The consumer side of one pass once xp is ready: GEMV over the slab, the two K groups joined, the partial pushed to the
 // rows' owners. `count` live rows.
 template <int N, int RM>
 __device__ __forceinline__ void gemv_and_push(cg::cluster_group& cluster, const CtaSmem& c, uint32_t nrows, uint32_t n,
-                                              uint32_t mask, Ring rc, uint32_t xstride, RingPos& pos, uint32_t count,
+                                              uint32_t mask, Ring rc, uint32_t xstride, uint32_t xrows, RingPos& pos, uint32_t count,
                                               uint32_t rank, uint32_t csize, uint32_t warp, uint32_t lane, uint32_t* err) {
     const uint32_t tcol = warp & (kTileWarps - 1u), kg = warp / kTileWarps;
     float acc[RowCap<RM>::kMB][2][4] = {};
-    consume_slab<N, CB, RM>(c.ring, c.full, c.empty, nrows, n, mask, rc, c.xp, xstride, pos, tcol, kg, lane, acc, err);
+    consume_slab<N, CB, RM>(c.ring, c.full, c.empty, nrows, n, mask, rc, c.xp, xstride, xrows, pos, tcol, kg, lane, acc, err);
     if (kg == 1) store_local<RM>(c.local, acc, tcol, lane);
     named_sync(1, kConsumerThreads);
     if (kg == 0) push_partial<RM>(cluster, c.recv, c.local, acc, count, rank, csize, tcol, lane);
+}
+
+// ---------------------------------------------------------------------------------------------- dense linear
+
+// grid (split, out / 128), cluster (split, 1, 1)
+template <int N, int RM>
+__global__ void __launch_bounds__(kGemvThreads, 2) dense_gemv_kernel(const DenseArgs a) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t* smem = aligned_smem(smem_raw);
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t rank = cluster.block_rank(), csize = a.split, blk = blockIdx.y;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    uint32_t b0, b1;
+    slice_blocks(a.in / 128u, a.split, rank, b0, b1);
+    const uint32_t nblk = b1 - b0, nrows = nblk * 8u;
+    const uint32_t tile_bytes = 2u * a.n, row_bytes = 16u * a.n, out_tiles = a.out / 16u;
+    const Ring rc{a.ring.stage_rows, a.ring.stages};
+    const CtaSmem c = carve(smem, gemv_smem(RM, a.rows, a.slice_max, csize, rc.stage_rows * row_bytes, rc.stages));
+    const uint32_t xstride = a.slice_max + kXpPad;
+
+    const bool traced = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+    if (traced && tid == 0) a.trace[0] = clock64();
+    init_barriers(c, rc.stages);
+    __syncthreads();
+    if (traced && tid == 0) a.trace[1] = clock64();
+
+    RingPos pos;
+    float sv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (warp == kConsumerWarps) {
+        // the weights do not depend on the stream's previous kernel: start them, then let the next kernel do the same
+        const uint8_t* src = a.trellis + ((size_t)(b0 * 8u) * out_tiles + blk * 8u) * tile_bytes;
+        produce_slab(c.ring, c.full, c.empty, src, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, pos, lane, a.err);
+        pdl_trigger();
+    } else {
+        pdl_trigger();
+        load_scales(static_cast<const __half*>(a.svh) + blk * 128u, lane, sv);  // weights-side: ahead of the wait
+        if (warp == 0) prefetch_l2(static_cast<const __half*>(a.suh) + b0 * 128u, nblk * 256u, lane);
+        pdl_wait();  // x may be the previous kernel's output
+        for (uint32_t task = warp; task < a.rows * nblk; task += kConsumerWarps) {
+            const uint32_t row = task / nblk, b = task - row * nblk;
+            const uint32_t k0 = (b0 + b) * 128u;
+            prepare_block(a.x, a.x_dt, (size_t)row * a.in + k0, static_cast<const __half*>(a.suh) + k0,
+                          c.xp + row * xstride + b * 128u, lane);
+        }
+        named_sync(1, kConsumerThreads);
+        if (traced && tid == 0) {
+            a.trace[2] = clock64();
+            mbar_wait(&c.full[0], 0u);
+            a.trace[3] = clock64();
+        }
+        gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, a.rows, pos, a.rows, rank, csize, warp, lane, a.err);
+        if (traced && tid == 0) a.trace[4] = clock64();
+    }
+    cluster_arrive();
+    if (rank >= a.rows) return;  // owns no row: nothing reads this CTA's shared memory after its arrival
+    cluster_wait();
+    if (traced && tid == 0) a.trace[5] = clock64();
+    if (warp < kConsumerWarps) {
+        const uint32_t owned = rows_owned(RM, csize);
+        for (uint32_t i = warp; i * csize + rank < a.rows; i += kConsumerWarps) {
+            const uint32_t row = i * csize + rank;
+            float v[4];
+            gather_owned(c.recv, owned, i, 0, 1, csize, lane, v);
+            finish_block(v, sv, lane);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) store_act(a.y, a.x_dt, (size_t)row * a.out + blk * 128u + lane + 32u * j, v[j]);
+        }
+    }
+    if (traced && tid == 0) a.trace[6] = clock64();
 }
 
 // ---------------------------------------------------------------------------------------------- routed experts
@@ -139,7 +214,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_gate_up_kernel(const MoeA
     const uint32_t nblk = b1 - b0, nrows = nblk * 8u;
     const uint32_t tile_bytes = 2u * a.n, row_bytes = 16u * a.n, out_tiles = I / 16u;
     const Ring rc{a.ring_gu.stage_rows, a.ring_gu.stages};
-    const CtaSmem c = carve(smem, gemv_smem(RM, a.slice_max_gu, csize, rc.stage_rows * row_bytes, rc.stages));
+    const CtaSmem c = carve(smem, gemv_smem(RM, RM, a.slice_max_gu, csize, rc.stage_rows * row_bytes, rc.stages));
     const uint32_t xstride = a.slice_max_gu + kXpPad;
     init_barriers(c, rc.stages);
     __syncthreads();
@@ -168,7 +243,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_gate_up_kernel(const MoeA
                 prepare_block(a.x, a.x_dt, (size_t)row * H + k0, suh + k0, c.xp + m * xstride + b * 128u, lane);
             }
             named_sync(1, kConsumerThreads);
-            gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, pos, mcount, rank, csize, warp, lane, a.err);
+            gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, RM, pos, mcount, rank, csize, warp, lane, a.err);
         }
         cluster_arrive();
         const bool last = m0 + RM >= mem.count;
@@ -224,7 +299,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs
     const uint32_t nblk = b1 - b0, nrows = nblk * 8u;
     const uint32_t tile_bytes = 2u * a.n, row_bytes = 16u * a.n, out_tiles = H / 16u;
     const Ring rc{a.ring_d.stage_rows, a.ring_d.stages};
-    const CtaSmem c = carve(smem, gemv_smem(RM, a.slice_max_d, csize, rc.stage_rows * row_bytes, rc.stages));
+    const CtaSmem c = carve(smem, gemv_smem(RM, RM, a.slice_max_d, csize, rc.stage_rows * row_bytes, rc.stages));
     const uint32_t xstride = a.slice_max_d + kXpPad;
     init_barriers(c, rc.stages);
     __syncthreads();
@@ -254,7 +329,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs
                 }
             }
             named_sync(1, kConsumerThreads);
-            gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, pos, mcount, rank, csize, warp, lane, a.err);
+            gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, RM, pos, mcount, rank, csize, warp, lane, a.err);
         }
         cluster_arrive();
         const bool last = m0 + RM >= mem.count;
@@ -376,18 +451,25 @@ cudaError_t launch_cluster(KernelFn<Args> fn, const Args& a, dim3 grid, uint32_t
 #define T3_CAT2(a, b) a##b
 #define T3_CAT(a, b) T3_CAT2(a, b)
 
+cudaError_t T3_CAT(launch_dense_gemv_cb, T3_CB)(const DenseArgs& a, cudaStream_t stream) {
+    const uint32_t rm = row_cap_for(a.rows);
+    KernelFn<DenseArgs> fn = T3_PICK(dense_gemv_kernel, a.n, rm);
+    return launch_cluster(fn, a, dim3(a.split, a.out / 128u, 1), a.split, gemv_smem_bytes(rm, a.rows, a.slice_max, a.split, a.n, a.ring),
+                          a.overlap != 0, stream);
+}
+
 cudaError_t T3_CAT(launch_moe_gate_up_cb, T3_CB)(const MoeArgs& a, cudaStream_t stream) {
     const uint32_t rm = a.row_cap;
     KernelFn<MoeArgs> fn = T3_PICK(moe_gate_up_kernel, a.n, rm);
     return launch_cluster(fn, a, dim3(2u * a.split_gu, a.inter / 128u, a.rows * a.topk), 2u * a.split_gu,
-                          gemv_smem_bytes(rm, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu), a.overlap != 0, stream);
+                          gemv_smem_bytes(rm, rm, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu), a.overlap != 0, stream);
 }
 
 cudaError_t T3_CAT(launch_moe_down_cb, T3_CB)(const MoeArgs& a, cudaStream_t stream) {
     const uint32_t rm = a.row_cap;
     KernelFn<MoeArgs> fn = T3_PICK(moe_down_kernel, a.n, rm);
     return launch_cluster(fn, a, dim3(a.split_d, a.hidden / 128u, a.rows * a.topk), a.split_d,
-                          gemv_smem_bytes(rm, a.slice_max_d, a.split_d, a.n, a.ring_d), a.overlap != 0, stream);
+                          gemv_smem_bytes(rm, rm, a.slice_max_d, a.split_d, a.n, a.ring_d), a.overlap != 0, stream);
 }
 
 #if T3_CB == 0

@@ -51,36 +51,17 @@ struct GemvSmem {
     uint32_t bars, xp, local, recv, ring, total;
 };
 __host__ __device__ inline uint32_t rows_owned(uint32_t rm, uint32_t cluster) { return (rm + cluster - 1u) / cluster; }
-__host__ __device__ inline GemvSmem gemv_smem(uint32_t rm, uint32_t slice_k, uint32_t cluster, uint32_t stage_bytes,
+// xrows: prepared rows held (the routed kernels hold a pass's row capacity; the dense linear only its live rows: the
+// tensor-core steps read a row past the last live one from the last live one, and nobody looks at what that gives)
+__host__ __device__ inline GemvSmem gemv_smem(uint32_t rm, uint32_t xrows, uint32_t slice_k, uint32_t cluster, uint32_t stage_bytes,
                                               uint32_t stages) {
     GemvSmem s;
     s.bars = 0;
     s.xp = 2u * kMaxStages * 8u;
-    const uint32_t xp_bytes = rm * (slice_k + kXpPad) * 2u;
+    const uint32_t xp_bytes = xrows * (slice_k + kXpPad) * 2u;
     s.local = s.xp + ((xp_bytes + 127u) & ~127u);
     s.recv = s.local + ((rm * kPartialStride * 4u + 127u) & ~127u);
     s.ring = s.recv + ((cluster * rows_owned(rm, cluster) * kPartialStride * 4u + 127u) & ~127u);
-    s.total = s.ring + stage_bytes * stages;
-    return s;
-}
-
-// Shared-memory carve-up of a dense decode-row CTA (t3_dense_rows.cu). xp: `xp_bufs` buffers of the prepared rows of
-// `chunk_blocks` 128-input blocks; local: where the two K groups meet; recv: `recv_bufs` buffers of the partial sums the
-// cluster's ranks send for the rows this CTA owns; dq: B fragments decoded ahead of the dependency wait (16 bytes a lane a
-// tile, `dq_stages` ring stages a warp); ring: the code stages.
-struct DenseSmem {
-    uint32_t bars, xp, local, recv, dq, ring, total;
-};
-__host__ __device__ inline DenseSmem dense_smem(uint32_t rm, uint32_t chunk_blocks, uint32_t xp_bufs, uint32_t recv_bufs,
-                                                uint32_t cluster, uint32_t dq_stages, uint32_t stage_bytes, uint32_t stages) {
-    DenseSmem s;
-    auto up = [](uint32_t v) { return (v + 127u) & ~127u; };
-    s.bars = 0;
-    s.xp = up((2u * kMaxStages + 6u) * 8u);
-    s.local = s.xp + up(xp_bufs * rm * (chunk_blocks * 128u + kXpPad) * 2u);
-    s.recv = s.local + up(rm * kPartialStride * 4u);
-    s.dq = s.recv + up(recv_bufs * cluster * rows_owned(rm, cluster) * kPartialStride * 4u);
-    s.ring = s.dq + kConsumerWarps * dq_stages * kBatch * 512u;
     s.total = s.ring + stage_bytes * stages;
     return s;
 }
@@ -119,7 +100,7 @@ __device__ __forceinline__ void produce_slab(uint8_t* ring, uint64_t* full, uint
                                              RingPos& pos, uint32_t lane, uint32_t* err) {
     const uint32_t stage_bytes = kStageRows * row_bytes;
     for (uint32_t r0 = 0; r0 < nrows; r0 += kStageRows) {
-        if (pos.lap > 0 && !mbar_wait(&empty[pos.slot], (pos.lap - 1u) & 1u)) report(err, kErrEmptyWait);
+        if (pos.lap > 0) mbar_wait_report(smem_addr(&empty[pos.slot]), (pos.lap - 1u) & 1u, err, kErrEmptyWait);
         if (lane == 0) mbar_arrive_expect_tx(&full[pos.slot], stage_bytes);
         __syncwarp();
         if (lane < kStageRows)
@@ -131,32 +112,49 @@ __device__ __forceinline__ void produce_slab(uint8_t* ring, uint64_t* full, uint
 
 // ---- consumer -----------------------------------------------------------------------------------------------------
 
-// one decoded tile times the prepared rows at inputs [16 tk, 16 tk + 16): xk points at the lane's first row there
+// Where a lane finds its rows of the prepared-row buffer (half-element offsets): rows 16 mb + g and 16 mb + 8 + g of the
+// tensor-core step's A operand, a row past the last live one read from the last live one
 template <int RM>
-__device__ __forceinline__ void mma_tile(float (&acc)[RowCap<RM>::kMB][2][4], const __half* xk, uint32_t xstride,
+struct RowOffsets {
+    uint32_t lo[RowCap<RM>::kMB], hi[RowCap<RM>::kMB];
+    __device__ __forceinline__ void init(uint32_t lane, uint32_t live, uint32_t xstride) {
+        const uint32_t g = lane >> 2, last = live - 1u;
+#pragma unroll
+        for (int mb = 0; mb < RowCap<RM>::kMB; ++mb) {
+            lo[mb] = min((uint32_t)mb * 16u + g, last) * xstride;
+            hi[mb] = min((uint32_t)mb * 16u + 8u + g, last) * xstride;
+        }
+    }
+};
+
+// one decoded tile times the prepared rows at inputs [16 tk, 16 tk + 16): xk points at the lane's columns there, row 0
+template <int RM>
+__device__ __forceinline__ void mma_tile(float (&acc)[RowCap<RM>::kMB][2][4], const __half* xk, const RowOffsets<RM>& ro,
                                          const uint32_t (&b)[4]) {
 #pragma unroll
     for (int mb = 0; mb < RowCap<RM>::kMB; ++mb) {
-        const uint2 lo = *reinterpret_cast<const uint2*>(xk + (mb * 16) * xstride);
+        const uint2 lo = *reinterpret_cast<const uint2*>(xk + ro.lo[mb]);
         uint2 hi = make_uint2(0u, 0u);
-        if (!RowCap<RM>::kHalf) hi = *reinterpret_cast<const uint2*>(xk + (mb * 16 + 8) * xstride);
+        if (!RowCap<RM>::kHalf) hi = *reinterpret_cast<const uint2*>(xk + ro.hi[mb]);
         mma16816(acc[mb][0], lo.x, hi.x, lo.y, hi.y, b[0], b[1]);
         mma16816(acc[mb][1], lo.x, hi.x, lo.y, hi.y, b[2], b[3]);
     }
 }
 
 // Consumer warp (tile column `tcol`, K group `kg`) folds tk rows kg, kg + kKGroups, ... of [0, nrows) into acc (nrows a
-// multiple of kStageRows). xp: prepared rows in lane order, row stride `xstride` halfs, k = 0 at the slab's first input.
+// multiple of kStageRows). xp: `live_rows` prepared rows in lane order, row stride `xstride` halfs, k = 0 at the slab's
+// first input.
 // acc[mb][nt] is the mma C fragment of rows 16 mb .. 16 mb + 15, columns 16 tcol + 8 nt .. + 7.
 // A stage holds kStageRows tk rows, so a warp's share of a stage is exactly one batch of kBatch tiles, and with the rate
 // a template constant every shared-memory offset inside a stage is an immediate.
 template <int N, int CB, int RM>
 __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full, uint64_t* empty, uint32_t nrows,
                                              uint32_t n_rt, uint32_t mask, Ring rc, const __half* xp, uint32_t xstride,
-                                             RingPos& pos, uint32_t tcol, uint32_t kg, uint32_t lane,
+                                             uint32_t live_rows, RingPos& pos, uint32_t tcol, uint32_t kg, uint32_t lane,
                                              float (&acc)[RowCap<RM>::kMB][2][4], uint32_t* err) {
     constexpr int NP = N > 0 ? N : 16;
     constexpr uint32_t kRaw = raw_words(NP);
+    constexpr uint32_t kHalfBatch = kBatch / 2u;  // tiles whose words and fragments are in registers together
     const uint32_t n = N > 0 ? (uint32_t)N : n_rt;
     const uint32_t tile_bytes = 2u * n, row_bytes = 16u * n, stage_bytes = kStageRows * row_bytes;
     LanePlan<NP> plan;
@@ -165,36 +163,47 @@ __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full
     uint32_t woff[kRaw];
 #pragma unroll
     for (uint32_t i = 0; i < kRaw; ++i) woff[i] = tcol * tile_bytes + kg * row_bytes + plan.idx[i] * 4u;
-    const __half* xs = xp + (lane >> 2) * xstride + 4u * (lane & 3u) + kg * 16u;
+    const __half* xs = xp + 4u * (lane & 3u) + kg * 16u;
+    RowOffsets<RM> ro;
+    ro.init(lane, live_rows, xstride);
+    const uint32_t full0 = smem_addr(full), empty0 = smem_addr(empty);
+    uint32_t slot = pos.slot, par = pos.lap & 1u, lap = pos.lap;
+    const bool lane0 = lane == 0;
+#pragma unroll 1
     for (uint32_t r0 = 0; r0 < nrows; r0 += kStageRows, xs += kStageRows * 16u) {
-        if (!mbar_wait(&full[pos.slot], pos.lap & 1u)) report(err, kErrFullWait);
-        const uint8_t* st = ring + pos.slot * stage_bytes;
+        mbar_wait_report(full0 + slot * 8u, par, err, kErrFullWait);
+        const uint8_t* st = ring + slot * stage_bytes;
         if (N > 0) {
-            // the stage's four tiles of this warp: words, then decodes, then MMAs, so four dependent chains overlap
-            uint32_t raw[kBatch][kRaw];
+            // the stage's four tiles of this warp, two at a time: words, then decodes, then tensor-core steps, so the
+            // dependent chains of two tiles overlap and the registers of four are never needed at once
 #pragma unroll
-            for (uint32_t i = 0; i < kBatch; ++i)
+            for (uint32_t h = 0; h < kBatch; h += kHalfBatch) {
+                uint32_t raw[kHalfBatch][kRaw];
 #pragma unroll
-                for (uint32_t w = 0; w < kRaw; ++w)
-                    raw[i][w] = *reinterpret_cast<const uint32_t*>(st + woff[w] + i * kKGroups * row_bytes);
-            uint32_t b[kBatch][4];
+                for (uint32_t i = 0; i < kHalfBatch; ++i)
 #pragma unroll
-            for (uint32_t i = 0; i < kBatch; ++i) decode_raw<NP, CB>(raw[i], plan, mask, b[i]);
+                    for (uint32_t w = 0; w < kRaw; ++w)
+                        raw[i][w] = *reinterpret_cast<const uint32_t*>(st + woff[w] + (h + i) * kKGroups * row_bytes);
+                uint32_t b[kHalfBatch][4];
 #pragma unroll
-            for (uint32_t i = 0; i < kBatch; ++i) mma_tile<RM>(acc, xs + i * kKGroups * 16u, xstride, b[i]);
+                for (uint32_t i = 0; i < kHalfBatch; ++i) decode_raw<NP, CB>(raw[i], plan, mask, b[i]);
+#pragma unroll
+                for (uint32_t i = 0; i < kHalfBatch; ++i) mma_tile<RM>(acc, xs + (h + i) * kKGroups * 16u, ro, b[i]);
+            }
         } else {
 #pragma unroll 1
             for (uint32_t i = 0; i < kBatch; ++i) {
                 uint32_t b[4];
                 decode_lane_any<CB>(reinterpret_cast<const uint32_t*>(st + tcol * tile_bytes + (kg + i * kKGroups) * row_bytes),
                                     n, lane, mask, b);
-                mma_tile<RM>(acc, xs + i * kKGroups * 16u, xstride, b);
+                mma_tile<RM>(acc, xs + i * kKGroups * 16u, ro, b);
             }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[pos.slot]);
-        pos.advance(rc.stages);
+        if (lane0) mbar_arrive_addr(empty0 + slot * 8u);
+        if (++slot == rc.stages) slot = 0, par ^= 1u, ++lap;
     }
+    pos.slot = slot, pos.lap = lap;
 }
 
 // ---- the cluster reduce-scatter -----------------------------------------------------------------------------------
@@ -298,55 +307,6 @@ __device__ __forceinline__ void finish_block(float (&v)[4], const float (&sv)[4]
 __device__ __forceinline__ void load_scales(const __half* blk, uint32_t lane, float (&sv)[4]) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) sv[j] = __half2float(blk[lane + 32u * j]);
-}
-
-// ---- one-sided pushes between the CTAs of a cluster -----------------------------------------------------------------
-
-// the shared::cluster address of `p` (an address in this CTA's shared memory) as CTA `rank` of the cluster sees its own copy
-__device__ __forceinline__ uint32_t peer_addr(const void* p, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr(p)), "r"(rank));
-    return r;
-}
-
-// Two floats into a peer's shared memory; the 8 bytes are counted on the peer's barrier `bar` when they have landed, so
-// the receiver waits on its own barrier and the sender waits for nothing.
-__device__ __forceinline__ void push_f32x2(uint32_t dst, float a, float b, uint32_t bar) {
-    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];" ::"r"(dst), "f"(a),
-                 "f"(b), "r"(bar)
-                 : "memory");
-}
-
-// one arrival on a peer's barrier; this thread's earlier writes are visible to whoever then passes that barrier
-__device__ __forceinline__ void peer_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-// waits for a barrier that peers of the cluster arrive on (acquire at cluster scope); bounded like mbar_wait
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_addr(bar);
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-
-// tk rows (16 inputs each) [t0, t1) of rank r when T rows are cut over s ranks, balanced to a row
-// (T is at most 2^26 / 16 and s at most 16, so the products fit 32 bits)
-__host__ __device__ inline void slice_rows(uint32_t T, uint32_t s, uint32_t r, uint32_t& t0, uint32_t& t1) {
-    t0 = T * r / s;
-    t1 = T * (r + 1u) / s;
 }
 
 // K blocks [b0, b1) of rank r when nb 128-blocks are cut over s ranks

@@ -1,7 +1,6 @@
 // Host-side declarations shared by the library's translation units (not part of the public C ABI).
 #pragma once
 
-#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
@@ -19,22 +18,15 @@ struct DenseArgs {
     const uint8_t* trellis;   // [in/16, out/16, n] u16
     const void* suh;          // f16 [in]
     const void* svh;          // f16 [out]
-    const __half* xp_g;       // the prepared rows f16 [rows, in] (lane order) when a prepare launch ran first, else null
     uint32_t rows, in, out, n, mask;
     int x_dt;
-    uint32_t split;           // cluster size: K slices (a function of the geometry only, never of the rows)
-    uint32_t chunk_blocks;    // 128-input blocks of prepared rows a CTA holds at once (>= a slice's blocks when xp_g is null)
-    uint32_t xp_bufs;         // 1, or 2 when a slice takes several chunks
-    uint32_t recv_bufs;       // 1, or 2 when a cluster walks more than one output block
-    uint32_t dq_stages;       // ring stages a warp decodes ahead of the dependency wait
+    uint32_t split;           // cluster size: K slices
+    uint32_t slice_max;       // inputs of the largest K slice
     RingPlan ring;
     int overlap;              // launch with the programmatic-dependent-launch attribute
     uint32_t* err;
-    unsigned long long* trace;  // optional: 8 timestamps a CTA (see t3_set_trace)
+    unsigned long long* trace;  // optional: SM cycle counts at the phases of CTA (0, 0) (see t3_set_trace)
 };
-constexpr uint32_t kTraceCtas = 512;   // CTAs of a launch whose timestamps are kept
-constexpr uint32_t kTraceWords = 16;   // uint64 a CTA
-constexpr uint32_t kFusedRows = 8;     // up to this many rows are rotated inside the GEMV's CTAs
 
 // The routed chain at decode rows (rows <= 32): row-slot s = row * topk + k runs expert inds[s]
 struct MoeArgs {
@@ -63,20 +55,13 @@ struct MoeArgs {
     uint32_t* err;
 };
 
-// the dense decode-row kernel: clusters to launch, the CTA's shared-memory bytes (dense_smem().total + kSmemSlack)
-cudaError_t launch_dense_rows(const DenseArgs& a, int codebook, uint32_t rm, uint32_t clusters, uint32_t smem_bytes,
-                              cudaStream_t stream);
-// clusters of `split` such CTAs that the current device holds at once (0 when the query fails)
-int dense_rows_max_clusters(int codebook, uint32_t n, uint32_t rm, bool prepared, uint32_t split, uint32_t smem_bytes);
-// xp = the input rotation of every row (f16, lane order), for calls whose rows are not rotated inside the GEMV's CTAs
-cudaError_t launch_dense_prepare(const void* x, int x_dt, const void* suh, uint32_t rows, uint32_t in, void* xp, bool overlap,
-                                 cudaStream_t stream);
+cudaError_t launch_dense_gemv(const DenseArgs& a, int codebook, cudaStream_t stream);
 cudaError_t launch_moe_gate_up(const MoeArgs& a, int codebook, cudaStream_t stream);
 cudaError_t launch_moe_down(const MoeArgs& a, int codebook, cudaStream_t stream);
 cudaError_t launch_moe_merge(const MoeArgs& a, cudaStream_t stream);
 
 // shared-memory bytes the GEMV CTAs of a plan need (for admission before launch)
-uint32_t gemv_smem_bytes(uint32_t row_cap, uint32_t slice_max, uint32_t cluster, uint32_t n, RingPlan ring);
+uint32_t gemv_smem_bytes(uint32_t row_cap, uint32_t xrows, uint32_t slice_max, uint32_t cluster, uint32_t n, RingPlan ring);
 // the most dynamic shared memory a GEMV CTA may be launched with
 constexpr uint32_t kGemvSmemLimit = 200u * 1024u;
 uint32_t row_cap_for(uint32_t rows);

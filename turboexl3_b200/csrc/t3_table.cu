@@ -8,6 +8,7 @@
 #include <memory>
 #include <mutex>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include <cuda_runtime.h>
@@ -384,14 +385,28 @@ t3_verdict table_load_bank(const t3_load_ctx* ctx, const t3_array* t, const t3_a
     return fill(out, t, suh, svh, st->dec, (int)t->shape[3], (int)experts, (int)in, (int)width);
 }
 
-// Staging buffers that only grow: activations in, results out, routing, engine workspace. One set per process; a call
-// that uses them holds the lock until its result is back on the host.
+// Staging buffers that only grow: activations in, results out, routing (one set per process; a host-array call that uses
+// them holds the lock until its result is back on the host) and the engine workspaces, which are kept PER STREAM: a call on
+// device arrays returns with its kernels still in flight, and a call on another stream must not write the same scratch.
 struct Staging {
     std::mutex mu;
     struct Buf {
         void* p = nullptr;
         size_t cap = 0;
-    } x, y, inds, scores, ws;
+    } x, y, inds, scores;
+    // ws: the prefill and routed workspaces (written before they are read). rows: the decode-row linear's workspace, which
+    // must start zero and is left zero-tagged by every call (t3_linear), so it is cleared when it is (re)allocated and
+    // nothing else ever writes it.
+    struct StreamWs {
+        Buf ws, rows;
+    };
+    std::unordered_map<void*, StreamWs> per_stream;
+    StreamWs& of(void* stream) { return per_stream[stream]; }
+    bool fit_zeroed(Buf& b, size_t bytes) {
+        if (bytes <= b.cap) return true;
+        if (!fit(b, bytes)) return false;
+        return cudaMemset(b.p, 0, b.cap) == cudaSuccess;
+    }
     bool fit(Buf& b, size_t bytes) {
         if (bytes <= b.cap) return true;
         cudaFree(b.p);
@@ -419,13 +434,22 @@ struct Staging {
         }
         return true;
     }
-    size_t bytes() { return x.cap + y.cap + inds.cap + scores.cap + ws.cap + (hx ? 2u * kMappedBytes : 0u); }
+    size_t bytes() {
+        size_t total = x.cap + y.cap + inds.cap + scores.cap + (hx ? 2u * kMappedBytes : 0u);
+        for (auto& kv : per_stream) total += kv.second.ws.cap + kv.second.rows.cap;
+        return total;
+    }
     void release() {
-        for (Buf* b : {&x, &y, &inds, &scores, &ws}) {
+        for (Buf* b : {&x, &y, &inds, &scores}) {
             cudaFree(b->p);
             b->p = nullptr;
             b->cap = 0;
         }
+        for (auto& kv : per_stream) {
+            cudaFree(kv.second.ws.p);
+            cudaFree(kv.second.rows.p);
+        }
+        per_stream.clear();
         cudaFreeHost(hx);
         cudaFreeHost(hy);
         hx = hy = hx_dev = hy_dev = nullptr;
@@ -459,13 +483,17 @@ t3_verdict table_matmul(const t3_weight* w, const t3_array* x, void* stream, t3_
     const bool host = !x->device || !out->device;
     std::unique_lock<std::mutex> lock(g_staging.mu);
     const size_t wsb = t3_linear_workspace_bytes(rows, w->in_dim, w->out_dim, w->block);
-    if (!x->device && !out->device && wsb == 0 && xb <= Staging::kMappedBytes && yb <= Staging::kMappedBytes &&
+    Staging::StreamWs& sws = g_staging.of(stream);
+    const bool decode_rows = rows <= T3_DECODE_ROWS_MAX;
+    Staging::Buf& wsbuf = decode_rows ? sws.rows : sws.ws;
+    if (wsb && !(decode_rows ? g_staging.fit_zeroed(wsbuf, wsb) : g_staging.fit(wsbuf, wsb))) return refuse(T3_VERDICT_FAILED, "CudaError");
+    if (!x->device && !out->device && decode_rows && xb <= Staging::kMappedBytes && yb <= Staging::kMappedBytes &&
         g_staging.mapped()) {
         // decode rows on host arrays: one launch between two memcpys
         memcpy(g_staging.hx, x->data, xb);
         const t3_decode dec = {w->layout, w->flags};
         const int rc = t3_linear(g_staging.hx_dev, x->dtype, rows, w->w, w->scales, w->biases, w->in_dim, w->out_dim, w->block,
-                                 dec, g_staging.hy_dev, nullptr, 0, s);
+                                 dec, g_staging.hy_dev, wsbuf.p, wsbuf.cap, s);
         if (rc != T3_OK) return from_status(rc);
         if (cudaStreamSynchronize(s) != cudaSuccess) return refuse(T3_VERDICT_FAILED, "CudaError");
         memcpy(out->data, g_staging.hy, yb);
@@ -482,10 +510,9 @@ t3_verdict table_matmul(const t3_weight* w, const t3_array* x, void* stream, t3_
         if (!g_staging.fit(g_staging.y, yb)) return refuse(T3_VERDICT_FAILED, "CudaError");
         yd = g_staging.y.p;
     }
-    if (wsb && !g_staging.fit(g_staging.ws, wsb)) return refuse(T3_VERDICT_FAILED, "CudaError");
     const t3_decode dec = {w->layout, w->flags};
     const int rc = t3_linear(xd, x->dtype, rows, w->w, w->scales, w->biases, w->in_dim, w->out_dim, w->block, dec, yd,
-                             g_staging.ws.p, g_staging.ws.cap, s);
+                             wsbuf.p, wsbuf.cap, s);
     if (rc != T3_OK) return from_status(rc);
     if (!out->device && cudaMemcpyAsync(out->data, yd, yb, cudaMemcpyDeviceToHost, s) != cudaSuccess)
         return refuse(T3_VERDICT_FAILED, "CudaError");
@@ -547,13 +574,14 @@ t3_verdict table_swiglu(const t3_weight* gate, const t3_weight* up, const t3_wei
         yd = g_staging.y.p;
     }
     const size_t wsb = t3_moe_workspace_bytes(rows, topk, &bank);
-    if (!g_staging.fit(g_staging.ws, wsb ? wsb : 1)) return refuse(T3_VERDICT_FAILED, "CudaError");
+    Staging::Buf& wsbuf = g_staging.of(stream).ws;
+    if (!g_staging.fit(wsbuf, wsb ? wsb : 1)) return refuse(T3_VERDICT_FAILED, "CudaError");
     const t3_decode dec = {gate->layout, gate->flags};
     const int limit = opts ? opts->limit : 0;
     const int rc = limit > 0 ? t3_moe_clamped(xd, x->dtype, rows, &bank, id, sd, scores->dtype, topk, dec, limit, yd,
-                                              g_staging.ws.p, g_staging.ws.cap, s)
-                             : t3_moe(xd, x->dtype, rows, &bank, id, sd, scores->dtype, topk, dec, yd, g_staging.ws.p,
-                                      g_staging.ws.cap, s);
+                                              wsbuf.p, wsbuf.cap, s)
+                             : t3_moe(xd, x->dtype, rows, &bank, id, sd, scores->dtype, topk, dec, yd, wsbuf.p,
+                                      wsbuf.cap, s);
     if (rc != T3_OK) return from_status(rc);
     if (!out->device && cudaMemcpyAsync(out->data, yd, xb, cudaMemcpyDeviceToHost, s) != cudaSuccess)
         return refuse(T3_VERDICT_FAILED, "CudaError");
