@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--quick] [--eager] [--dense-split S] [--case NAME --rows R]
 
-Headline workload (BASELINE.json configs[1], decode rows): the dense trunk sweep, shapes 2048x2048, 2048x6144 and
+Headline workload (config 2, decode rows): the dense trunk sweep, shapes 2048x2048, 2048x6144 and
 6144x2048 at K in {1,2,3,4,5,6,8} bits, one f16 activation row each: 21 linears a step, 106.4 MB of trellis code bytes.
 Metric: code-byte GB/s = trellis bytes read per step / step time (the reference's byte convention: code bytes only,
 src/core/gpu_test.zig:136). Weights rotate over three copies (319 MB > L2), so every step streams its codes from HBM.
@@ -13,7 +13,7 @@ its weights while its predecessor finishes, nothing else overlaps).
 
 The JSON line also carries: `e2e` (the same step through the quant-plugin table with HOST arrays: copy in, run, copy
 out, every call), `roofline`, `cpu_baseline` (the oracle's format.project on the host cores, all threads and one), `submetrics`
-(the other two parts of BASELINE's metric: us per MoE layer at decode rows on config 3, prefill TFLOP/s on configs 2 and 4
+(the other two parts of the metric: us per MoE layer at decode rows on config 3, prefill TFLOP/s on configs 2 and 4
 shapes, per-call and on a kept W_hat), `cases` (every linear of the sweep), `rows_2048x6144_K4` (config 2's other row counts)
 and `concurrent` (the 21 independent linears as parallel graph branches: what the device sustains when nothing orders them).
 Optional measurements that fail are reported in place and never void the line.
@@ -120,7 +120,7 @@ class ClockSampler:
 
 
 def host_operands(copy: int):
-    """The sweep's 21 linears for weight copy `copy` as numpy arrays (seeded; BASELINE: seeded uniform codes, +-1 signs)."""
+    """The sweep's 21 linears for weight copy `copy` as numpy arrays (seeded uniform codes, +-1 signs)."""
     from turboexl3_b200 import synth
     ops = []
     for si, (i, o) in enumerate(SHAPES):
@@ -155,6 +155,65 @@ def cpu_single_thread() -> dict:
     dt = time.perf_counter() - t0
     byts = sum(code_bytes(i, o, n // 16) for (i, o, n, _, _, _) in ops)
     return {"value": byts / dt / 1e9, "unit": UNIT, "cores": 1, "sample": "the sweep's three K = 4 linears, one row each"}
+
+
+
+def parity_measures(got: np.ndarray, ref: np.ndarray) -> dict:
+    """ref.compare, ref.compareRounded at half an f16 ulp (src/core/ref.zig:195-218) and the share of outputs whose f16 bits are
+    the oracle's."""
+    from oracle import binding as ob
+    g, r = np.asarray(got, np.float32), np.asarray(ref, np.float32)
+    return {"compare": round(ob.compare(g, r)["max_ratio"], 6), "compareRounded": round(ob.compare(g, r, 2.0 ** -11)["max_ratio"], 6),
+            "bit_equal": round(float(np.mean(g.astype(np.float16) == r.astype(np.float16))), 4), "outputs": int(g.size)}
+
+
+def parity_block(t3, synth, torch, sets, host_sets, x_np, x_dev, full: bool) -> dict:
+    """The GPU results of this run against the CPU oracle, per config (the bars are asserted in tests/; this is the record of
+    how far inside them the timed kernels are). Sampled rows for the large cases, as the reference's own large tests do."""
+    from oracle import binding as ob
+    ob.build()
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    out = {}
+    # config 1: 4096 x 4096, K = 4, seed 0: W_hat bit for bit, and the one-row projection
+    trellis, suh, svh = synth.linear(0, 4096, 4096, 64)
+    what = ob.reconstruct_inner(trellis, 4096, 4096, 64, ob.MUL1)
+    w_gpu = t3.dequantize(dev(trellis)).cpu().view(torch.int16).numpy().view(np.uint16)
+    x1 = synth.activations(1, 1, 4096)
+    y1 = t3.linear(dev(x1), dev(trellis), dev(suh), dev(svh)).float().cpu().numpy()
+    out["config1_4096x4096_K4"] = {"w_hat_equal": int(np.count_nonzero(w_gpu == what)), "w_hat_total": int(what.size),
+                                   **parity_measures(y1, ob.linear_rows_what(x1.astype(np.float32), what, suh, svh, 4096, 4096))}
+    # config 2 at one row: the headline's 21 linears (worst case over them)
+    worst = {"compare": 0.0, "compareRounded": 0.0, "bit_equal": 1.0, "outputs": 0}
+    for (i, o, n, t, a, b), (_, _, _, td, ad, bd) in zip(host_sets[0], sets[0]):
+        y = t3.linear(x_dev[i], td, ad, bd).float().cpu().numpy()
+        m = parity_measures(y, ob.linear_rows(x_np[i].astype(np.float32), t, a, b, i, o, n, ob.MUL1, 16, threads=ob.host_threads()))
+        worst = {"compare": max(worst["compare"], m["compare"]), "compareRounded": max(worst["compareRounded"], m["compareRounded"]),
+                 "bit_equal": min(worst["bit_equal"], m["bit_equal"]), "outputs": worst["outputs"] + m["outputs"]}
+    out["config2_sweep_rows1_worst_of_21"] = worst
+    if not full:
+        return out
+    # config 2 past 32 rows: 2048 x 6144, K = 4, 4096 rows, seven sampled rows
+    i, o = 2048, 6144
+    trellis, suh, svh = synth.linear(5, i, o, 64)
+    x = synth.activations(1, 4096, i)
+    sample = [0, 16, 127, 128, 2047, 2500, 4095]
+    y = t3.linear(dev(x), dev(trellis), dev(suh), dev(svh)).float().cpu().numpy()[sample]
+    what = ob.reconstruct_inner(trellis, i, o, 64, ob.MUL1)
+    out["config2_2048x6144_K4_rows4096_sampled"] = parity_measures(y, ob.linear_rows_what(x[sample].astype(np.float32), what, suh, svh, i, o))
+    # configs 3 and 4: the routed layer (hidden 2048, 512 experts x 512, top-10, K = 3) at 4 rows and at 4096 tokens (sampled)
+    H, I, E, topk, n = 2048, 512, 512, 10, 48
+    arrs = synth.bank(3, E, H, I, n)
+    bank = t3.Bank(t3.Proj(dev(arrs["gate_t"]), dev(arrs["gate_suh"]), dev(arrs["gate_svh"])),
+                   t3.Proj(dev(arrs["up_t"]), dev(arrs["up_suh"]), dev(arrs["up_svh"])),
+                   t3.Proj(dev(arrs["down_t"]), dev(arrs["down_suh"]), dev(arrs["down_svh"])))
+    obank = ob.Bank(E, H, I, n, *[arrs[k] for k in ("gate_t", "gate_suh", "gate_svh", "up_t", "up_suh", "up_svh", "down_t", "down_suh", "down_svh")])
+    for rows, sample, name in ((4, [0, 1, 2, 3], "config3_moe_rows4"), (4096, [0, 1, 2048, 4095], "config4_moe_K3_tokens4096_sampled")):
+        inds, scores = synth.routing(50 + rows, rows, E, topk)
+        xm = synth.activations(5, rows, H)
+        ym = t3.moe(dev(xm).view(1, rows, H), bank, dev(inds).view(1, rows, topk), dev(scores).view(1, rows, topk))
+        ref = ob.moe_rows(obank, xm[sample].astype(np.float32), inds[sample], scores[sample])
+        out[name] = parity_measures(ym.float().cpu().numpy().reshape(rows, H)[sample], ref)
+    return out
 
 
 def run_reference(args) -> None:
@@ -198,19 +257,28 @@ def graph_of(fn):
 
 
 def time_us(run, reps: int) -> float:
+    """Median device time of one run() in microseconds over max(reps, 20) separately timed repetitions (the reference's
+    harness reports min and median over rounds, src/core/bench.zig:1-13; time_stats gives both)."""
+    return time_stats(run, reps)["median"]
+
+
+def time_stats(run, reps: int = 20) -> dict:
     import torch
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(reps, 20)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    run()  # one untimed pass
     torch.cuda.synchronize()
-    e0.record()
-    for _ in range(reps):
+    for e0, e1 in evs:
+        e0.record()
         run()
-    e1.record()
+        e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) * 1e3 / reps
+    us = sorted(e0.elapsed_time(e1) * 1e3 for e0, e1 in evs)
+    return {"median": statistics.median(us), "min": us[0], "reps": reps}
 
 
 def moe_submetric(t3, synth, torch) -> dict:
-    """BASELINE config 3: hidden 2048, 512 experts x width 512, top-10, K = 3, one shared expert; us per MoE layer."""
+    """Config 3: hidden 2048, 512 experts x width 512, top-10, K = 3, one shared expert; us per MoE layer."""
     H, I, E, topk, n = 2048, 512, 512, 10, 48
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
     mk = lambda arrs: t3.Bank(t3.Proj(dev(arrs["gate_t"]), dev(arrs["gate_suh"]), dev(arrs["gate_svh"])),
@@ -244,10 +312,11 @@ def moe_submetric(t3, synth, torch) -> dict:
                 main.wait_stream(side)
 
         g = graph_of(layer_burst)
-        us = time_us(g.replay, 10) / len(calls)
+        st = time_stats(g.replay, 20)
+        us = st["median"] / len(calls)
         byts = (float(np.mean(distinct)) + 1.0) * 3 * H * I * 3 / 8
-        out[f"rows{rows}"] = {"us_per_layer": round(us, 2), "distinct_experts": float(np.mean(distinct)),
-                              "code_GBps": round(byts / us / 1e3, 1)}
+        out[f"rows{rows}"] = {"us_per_layer": round(us, 2), "us_per_layer_min": round(st["min"] / len(calls), 2),
+                              "distinct_experts": float(np.mean(distinct)), "code_GBps": round(byts / us / 1e3, 1), "reps": st["reps"]}
     return out
 
 
@@ -258,13 +327,17 @@ def prefill_submetric(t3, synth, torch) -> dict:
         w = tuple(dev(a) for a in synth.linear(5, i, o, 16 * k))
         x = dev(synth.activations(1, rows, i))
         t3.linear(x, *w)
-        us = time_us(lambda: t3.linear(x, *w), 5)
-        out[f"dense_{i}x{o}_K{k}_rows{rows}"] = {"us": round(us, 1), "TFLOPS": round(2.0 * rows * i * o / us / 1e6, 1)}
+        st = time_stats(lambda: t3.linear(x, *w), 20)
+        us = st["median"]
+        out[f"dense_{i}x{o}_K{k}_rows{rows}"] = {"us": round(us, 1), "us_min": round(st["min"], 1),
+                                                 "TFLOPS": round(2.0 * rows * i * o / us / 1e6, 1), "reps": st["reps"]}
         if rows >= 4096:  # the same call on a kept W_hat (the resident trunk: 2 bytes a weight held, nothing decoded)
             w_t = t3.resident_build(w[0])
             t3.linear_resident(x, w_t, w[1], w[2])
-            us = time_us(lambda: t3.linear_resident(x, w_t, w[1], w[2]), 5)
-            out[f"resident_{i}x{o}_rows{rows}"] = {"us": round(us, 1), "TFLOPS": round(2.0 * rows * i * o / us / 1e6, 1)}
+            st = time_stats(lambda: t3.linear_resident(x, w_t, w[1], w[2]), 20)
+            us = st["median"]
+            out[f"resident_{i}x{o}_rows{rows}"] = {"us": round(us, 1), "us_min": round(st["min"], 1),
+                                                   "TFLOPS": round(2.0 * rows * i * o / us / 1e6, 1), "reps": st["reps"]}
     H, I, E, topk, n = 2048, 512, 512, 10, 48
     arrs = synth.bank(3, E, H, I, n)
     bank = t3.Bank(t3.Proj(dev(arrs["gate_t"]), dev(arrs["gate_suh"]), dev(arrs["gate_svh"])),
@@ -275,9 +348,10 @@ def prefill_submetric(t3, synth, torch) -> dict:
         x = dev(synth.activations(5, rows, H)).view(1, rows, H)
         di, ds = dev(inds).view(1, rows, topk), dev(scores).view(1, rows, topk)
         t3.moe(x, bank, di, ds)
-        us = time_us(lambda: t3.moe(x, bank, di, ds), 3)
-        out[f"moe_config4_K3_tokens{rows}"] = {"us": round(us, 1),
-                                               "TFLOPS": round(2.0 * rows * topk * 3 * H * I / us / 1e6, 1)}
+        st = time_stats(lambda: t3.moe(x, bank, di, ds), 20)
+        us = st["median"]
+        out[f"moe_config4_K3_tokens{rows}"] = {"us": round(us, 1), "us_min": round(st["min"], 1),
+                                               "TFLOPS": round(2.0 * rows * topk * 3 * H * I / us / 1e6, 1), "reps": st["reps"]}
     return out
 
 
@@ -324,7 +398,7 @@ def sharded_submetric(t3, synth, torch, dist, rank: int, world: int) -> dict:
 
 
 def trunk_submetric(t3, synth, torch) -> dict:
-    """BASELINE config 5's MLA trunk projections (K = 4) at one row: larger linears than the sweep's, where bytes start to
+    """Config 5's MLA trunk projections (K = 4) at one row: larger linears than the sweep's, where bytes start to
     matter. Each linear runs over enough distinct weight copies (slices of one 288 MB buffer of random codes) to stream
     from HBM, one graph of launches a shape."""
     n = 64
@@ -343,9 +417,11 @@ def trunk_submetric(t3, synth, torch) -> dict:
             for w in ws:
                 t3.linear(x, w, suh_d, svh_d)
         g = graph_of(burst)
-        us = time_us(g.replay, 5) / copies
+        st = time_stats(g.replay, 20)
+        us = st["median"] / copies
         byts = i * o * n // 128
-        out[f"{name}_{i}x{o}"] = {"us": round(us, 2), "GBps": round(byts / us / 1e3, 1), "MB": round(byts / 1e6, 1)}
+        out[f"{name}_{i}x{o}"] = {"us": round(us, 2), "us_min": round(st["min"] / copies, 2), "GBps": round(byts / us / 1e3, 1),
+                                  "MB": round(byts / 1e6, 1), "reps": st["reps"]}
     return out
 
 
@@ -599,13 +675,21 @@ def run_ours(args) -> None:
             dist.destroy_process_group()
         return
 
+    extra["parity"] = guarded(lambda: parity_block(t3, synth, torch, sets, host_sets, x_np, x_dev, full=not args.quick))
+
     peaks = measured_peaks()
     value = world * STEP_BYTES / (ms_per_step * 1e-3) / 1e9
     achieved = (STEP_BYTES / LINEARS) / (ms_per_step * 1e-3 / LINEARS) / 1e9
-    traffic = None
+    # DRAM bytes a launch of the dominant kernel moves: captured once under ncu (profiles/traffic.json), stamped with the
+    # digest of the kernel sources it was captured on; a capture taken on other sources is reported as stale, not as current
+    traffic, traffic_note = None, "no capture"
     try:
+        from turboexl3_b200 import build as t3_build
         with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
-            traffic = json.load(f).get("dense_gemv_sweep_bytes_per_launch")
+            cap = json.load(f)
+        traffic = cap.get("dense_gemv_sweep_bytes_per_launch")
+        traffic_note = ("captured on these kernel sources" if cap.get("sources_digest") == t3_build.sources_digest()
+                        else "captured on earlier kernel sources")
     except Exception:
         pass
 
@@ -623,7 +707,7 @@ def run_ours(args) -> None:
                    "launch": launch_mode,
                    "multi_gpu": "replicas only: each rank runs the sweep on its own weight copies, no collective"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm"], "traffic": traffic, "peak_kind": peaks["kind"],
+                     "frac": achieved / peaks["hbm"], "traffic": traffic, "traffic_capture": traffic_note, "peak_kind": peaks["kind"],
                      "kernel": "dense_gemv_kernel (21 launches a step; bytes and time are the step's, per launch)"},
         "cpu_baseline": {"value": cpu["value"], "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": "one full pass of the 21-linear sweep, format.project decoding every tile per call",

@@ -102,6 +102,16 @@ def test_expert_quant_json():  # src/core/spec.zig:92-160
             t3.parse_expert_quant(base + bad)
         assert e.value.name == "Exl3WindowUnsupported"
     assert t3.parse_expert_quant('{"a":1,"expert_quant":{"format":"exl3","k":4,"codebook":"mul1"}}')["n"] == 64
+    # the block is a TOP-LEVEL field (src/core/spec.zig:38-40): the same text nested deeper, or inside a string, is not it
+    good = '{"format":"exl3","k":4,"codebook":"mul1"}'
+    for text in ('{"text_config":{"expert_quant":' + good + '}}', '{"note":"\\"expert_quant\\":' + good.replace('"', '\\"') + '"}',
+                 '{"expert_quant":"' + good.replace('"', '\\"') + '"}', '[{"expert_quant":' + good + '}]', '{"expert_quant":' + good):
+        with pytest.raises(t3.Exl3Error) as e:
+            t3.parse_expert_quant(text)
+        assert e.value.name == "ExpertLayoutUnsupported", text
+    # sub-keys come from the block itself, not from an object nested inside it
+    with pytest.raises(t3.Exl3Error):
+        t3.parse_expert_quant('{"expert_quant":{"inner":' + good + '}}')
     for bad in ('{}', '{"expert_quant":{"format":"gptq","k":4,"codebook":"mul1"}}',
                 '{"expert_quant":{"format":"exl3","k":4.03,"codebook":"mul1"}}',
                 '{"expert_quant":{"format":"exl3","k":9,"codebook":"mul1"}}',

@@ -1,4 +1,4 @@
-"""BASELINE configs 4 and 5 against the oracle: the hybrid layer with a rate drawn per expert from {2, 3, 4} bits (one
+"""The benchmark configurations 4 and 5 against the oracle: the hybrid layer with a rate drawn per expert from {2, 3, 4} bits (one
 sub-bank a rate, turboexl3_b200.mixed), the large layer's geometry (hidden 7168, width 2048, top-8, sigmoid scores, one
 shared expert, K = 2 and K = 4) at decode and prefill rows, and the MLA trunk projections at K = 4. Expert counts are cut
 down (the oracle decodes every weight of every expert a row touches on the host); geometry, rates, routing and the kernels'

@@ -1,6 +1,6 @@
 """Bit-exact decode: the device decoders over all 65,536 codewords and the W_hat kernel against the oracle's
 reconstructInner (the reference's own GPU tests of the same: src/hip_tests.zig:24-57, 59-123; W_hat bit-exactness is
-BASELINE's first result requirement)."""
+the first result requirement: the decoded weights are the bits of the reference)."""
 import numpy as np
 import pytest
 import torch
@@ -33,7 +33,7 @@ def test_w_hat_bit_exact_every_rate(n, codebook):
 
 
 def test_w_hat_config1_4096x4096_k4():
-    """BASELINE config 1: in 4096, out 4096, K = 4, codes from seed 0; W_hat must match bit for bit."""
+    """Benchmark config 1: in 4096, out 4096, K = 4, codes from seed 0; W_hat must match bit for bit."""
     trellis, _, _ = synth.linear(0, 4096, 4096, 64)
     got = bits16(t3.dequantize(dev(trellis), t3.Decode.mul1))
     want = ob.reconstruct_inner(trellis, 4096, 4096, 64, ob.MUL1)

@@ -1,5 +1,5 @@
 """The dense EXL3 linear against the oracle's format.project, at the shapes and row counts of the reference's own GPU
-tests (src/hip_tests.zig:294-347, src/core/gpu_test.zig:384-398) and of BASELINE configs 1 and 2.
+tests (src/hip_tests.zig:294-347, src/core/gpu_test.zig:384-398) and of the benchmark configs 1 and 2.
 
 Bars (gpu_util.check): the reference's own `ref.compare` max|err|/rms <= 5e-3 for f32/f16 activations and <= 2.5e-2
 for bf16 (src/core/gpu_test.zig:46,438,446), plus compareRounded(half ulp of the output dtype) <= 3e-3."""
@@ -47,7 +47,7 @@ def test_reference_gemv_cases(case):
 
 
 def test_config1_single_linear():
-    """BASELINE config 1: 4096 x 4096, K = 4, seed 0, +-1 signs, one f16 row."""
+    """Benchmark config 1: 4096 x 4096, K = 4, seed 0, +-1 signs, one f16 row."""
     got, ref, _ = run_case(4096, 4096, 64, t3.MUL1, 16, "f16", 1, seed=0, scaled=False)
     check(got, ref, "f16", "config 1")
 
@@ -55,7 +55,7 @@ def test_config1_single_linear():
 @pytest.mark.parametrize("shape", [(2048, 2048), (2048, 6144), (6144, 2048)])
 @pytest.mark.parametrize("k", [1, 2, 3, 4, 5, 6, 8])
 def test_config2_sweep_decode_rows(shape, k):
-    """BASELINE config 2 at the in-register rows {1, 8, 17, 32}, +-1 signs."""
+    """Benchmark config 2 at the in-register rows {1, 8, 17, 32}, +-1 signs."""
     in_dim, out_dim = shape
     for rows in (1, 8, 17, 32):
         got, ref, _ = run_case(in_dim, out_dim, 16 * k, t3.MUL1, 16, "f16", rows, seed=7 * k + rows, scaled=False)
@@ -81,7 +81,7 @@ def test_reference_gemm_cases(case):
 
 
 def test_config2_sweep_gemm_rows():
-    """BASELINE config 2 at the GEMM rows {33, 512, 4096}: every K at 2048x2048, K = 4 at the two wide shapes; +-1 signs."""
+    """Benchmark config 2 at the GEMM rows {33, 512, 4096}: every K at 2048x2048, K = 4 at the two wide shapes; +-1 signs."""
     cases = [((2048, 2048), k) for k in (1, 2, 3, 4, 5, 6, 8)] + [((2048, 6144), 4), ((6144, 2048), 4)]
     for (in_dim, out_dim), k in cases:
         for rows in (33, 512, 4096):

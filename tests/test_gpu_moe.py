@@ -1,5 +1,5 @@
 """The routed-expert chain at decode rows against the oracle's ref.moeRow, at the geometries of the reference's own GPU
-tests (src/hip_tests.zig:451-502, src/core/gpu_test.zig:33-44, src/core/topk_test.zig:33-45) and BASELINE config 3.
+tests (src/hip_tests.zig:451-502, src/core/gpu_test.zig:33-44, src/core/topk_test.zig:33-45) and Benchmark config 3.
 
 Bars: `ref.compare` max|err|/rms <= 5e-3 for f32/f16 activations, the reference's (src/core/gpu_test.zig:46). For bf16
 the reference's routed bar is 1.5e-2 (src/core/gpu_test.zig:256), but one bf16 rounding flip of the final store on a
@@ -97,7 +97,7 @@ def test_small_topk(topk, experts):  # src/core/topk_test.zig:33-45
 
 
 def test_config3_hybrid_layer_with_shared_expert():
-    """BASELINE config 3: hidden 2048, 512 experts of width 512, top-10, K = 3, softmax routing renormalised, one shared
+    """Benchmark config 3: hidden 2048, 512 experts of width 512, top-10, K = 3, softmax routing renormalised, one shared
     expert (a one-expert bank at top-1 whose score is the sigmoid gate), rows {1, 4, 16, 32}. The shared output is added at
     the routed output's rounding point (root.moeWithShared)."""
     H, I, E, topk, n = 2048, 512, 512, 10, 48

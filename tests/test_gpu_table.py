@@ -80,6 +80,57 @@ def test_swiglu_host_arrays():
     assert t3.device_error() == 0
 
 
+def test_device_array_calls_on_two_streams_do_not_share_scratch():
+    """Calls on device arrays return with their kernels in flight; two such calls on two streams run at once. Each stream has
+    its own workspace in the table, so the results are the serial ones."""
+    H, I, E, topk, n, rows = 512, 256, 8, 4, 48, 64
+    arrs = synth.bank(75, E, H, I, n)
+    blk = tb.Block('{"format":"exl3","k":3,"codebook":"mul1"}')
+    ws = {}
+    for name in ("gate", "up", "down"):
+        v, ws[name] = blk.load_bank(arrs[name + "_t"], arrs[name + "_suh"], arrs[name + "_svh"])
+        assert v.ok, v.why
+    tab = tb.table()
+    calls = []
+    for c in range(2):
+        inds, scores = synth.routing(76 + c, rows, E, topk)
+        x = torch.from_numpy(synth.activations(77 + c, rows, H)).cuda()
+        di, ds = torch.from_numpy(inds).cuda(), torch.from_numpy(scores).cuda()
+        y = torch.zeros((rows, H), dtype=torch.float16, device="cuda")
+        calls.append((x, di, ds, y))
+
+    def run(call, stream):
+        x, di, ds, y = call
+        out = tb.device_array(y.data_ptr(), 1, (1, rows, H))
+        v = tab.swiglu(C.byref(ws["gate"]), C.byref(ws["up"]), C.byref(ws["down"]),
+                       C.byref(tb.device_array(x.data_ptr(), 1, (1, rows, H))),
+                       C.byref(tb.device_array(di.data_ptr(), 5, (1, rows, topk))),
+                       C.byref(tb.device_array(ds.data_ptr(), 0, (1, rows, topk))), C.byref(tb.SwigluOpts(0, 0)),
+                       stream.cuda_stream, C.byref(out))
+        assert v.ok, v.why
+
+    main = torch.cuda.current_stream()
+    serial = []
+    for call in calls:
+        run(call, main)
+        torch.cuda.synchronize()
+        serial.append(call[3].clone())
+        call[3].zero_()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    for s in streams:
+        s.wait_stream(main)
+    for _ in range(4):  # several rounds, both streams busy at once
+        for call, s in zip(calls, streams):
+            run(call, s)
+    torch.cuda.synchronize()
+    for call, want in zip(calls, serial):
+        assert torch.equal(call[3], want)
+    for w in ws.values():
+        tab.release(C.byref(w))
+    blk.close()
+    assert t3.device_error() == 0
+
+
 def test_pack_file_to_table_to_matmul(tmp_path):
     """A trunk linear from a safetensors shard (the reference's affine names, i16 trellis) through the table's loader."""
     from turboexl3_b200 import pack

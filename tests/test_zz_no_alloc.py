@@ -50,6 +50,31 @@ def test_two_calls_in_a_row_match_the_workspace_entry_point():
     assert t3.device_error() == 0
 
 
+def test_a_warm_call_takes_no_device_memory():
+    """The point of the entry: no allocation on the caller's behalf. After a first call (which looks up the scratch array's
+    address once), further calls leave the device's free memory where it was and launch the chain's three kernels."""
+    H, I, E, topk, n, rows = 512, 256, 12, 4, 64, 8
+    bank = _bank(96, E, H, I, n)
+    inds, scores = synth.routing(97, rows, E, topk)
+    x = torch.from_numpy(synth.activations(98, rows, H)).cuda().view(1, rows, H)
+    di = torch.from_numpy(inds).cuda().view(1, rows, topk)
+    ds = torch.from_numpy(scores).cuda().view(1, rows, topk)
+    y = torch.empty_like(x)
+    cb = api._bank_c(bank, H)
+    call = lambda: t3.lib().t3_moe_noalloc(x.data_ptr(), 1, rows, C.byref(cb), di.data_ptr(), ds.data_ptr(), 0, topk,
+                                           t3.Decode.mul1._c(), y.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert call() == 0
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    launches_before = t3.launch_count()
+    for _ in range(3):
+        assert call() == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert t3.launch_count() - launches_before == 3 * 3  # gate|up, down, merge
+
+
 def test_sizes_past_the_built_in_scratch_are_refused():
     H, I, E, topk, n = 2048, 512, 4, 32, 32
     bank = _bank(95, E, H, I, n)

@@ -53,6 +53,16 @@ def _digest() -> str:
     return h.hexdigest()
 
 
+def sources_digest() -> str:
+    """A digest of the kernel sources alone (what a captured profile is a profile of)."""
+    h = hashlib.sha256()
+    for name in sorted(os.listdir(CSRC)):
+        if name.endswith((".cu", ".cuh", ".h")):
+            with open(os.path.join(CSRC, name), "rb") as f:
+                h.update(name.encode() + b"\0" + f.read())
+    return h.hexdigest()[:16]
+
+
 def _compile(unit, verbose: bool) -> str:
     src, stem, extra = unit
     obj = os.path.join(OBJ, stem + ".o")

@@ -11,6 +11,7 @@
 #include "../../include/t3.h"
 #include "t3_gemv.cuh"
 #include "t3_internal.h"
+#include "t3_json.h"
 
 namespace t3 {
 
@@ -66,14 +67,16 @@ uint32_t pow2_at_most(uint32_t v, uint32_t cap) {
 
 // CTAs that fit on the device at once (two GEMV CTAs a multiprocessor)
 uint32_t one_wave() {
-    static uint32_t ctas = [] {
-        int dev = 0, sms = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-            sms <= 0)
-            sms = 148;
-        return 2u * (uint32_t)sms;
-    }();
-    return ctas;
+    static std::atomic<uint32_t> ctas[64];  // per device ordinal; 0 = not asked yet
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 2u * 148u;
+    uint32_t v = ctas[dev].load(std::memory_order_relaxed);
+    if (v == 0) {
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        v = 2u * (uint32_t)sms;
+        ctas[dev].store(v, std::memory_order_relaxed);
+    }
+    return v;
 }
 
 // K slices for `units` independent (output block, job) pairs over nb 128-blocks of K: the smallest power of two, at most
@@ -215,80 +218,33 @@ int t3_trellis_admitted(const int* shape, int ndim, uint32_t experts, uint32_t i
 
 // ---- expert_quant ---------------------------------------------------------------------------------------------------
 
-namespace {
-
-// the value text of `"key":` inside [begin, end): a string's contents, or a bare number / literal
-bool json_value(const char* begin, const char* end, const char* key, std::string& out, bool& is_string) {
-    const std::string pat = std::string("\"") + key + "\"";
-    const char* p = begin;
-    while (p < end) {
-        const char* hit = static_cast<const char*>(memmem(p, (size_t)(end - p), pat.data(), pat.size()));
-        if (!hit) return false;
-        const char* q = hit + pat.size();
-        while (q < end && (*q == ' ' || *q == '\t' || *q == '\n' || *q == '\r')) ++q;
-        if (q < end && *q == ':') {
-            ++q;
-            while (q < end && (*q == ' ' || *q == '\t' || *q == '\n' || *q == '\r')) ++q;
-            if (q >= end) return false;
-            if (*q == '"') {
-                const char* r = ++q;
-                while (r < end && *r != '"') ++r;
-                if (r >= end) return false;
-                out.assign(q, r);
-                is_string = true;
-                return true;
-            }
-            const char* r = q;
-            while (r < end && *r != ',' && *r != '}' && *r != ' ' && *r != '\n' && *r != '\r' && *r != '\t') ++r;
-            out.assign(q, r);
-            is_string = false;
-            return !out.empty();
-        }
-        p = hit + 1;
-    }
-    return false;
-}
-
-}  // namespace
-
 int t3_parse_expert_quant(const char* json, size_t len, t3_spec* out) {
     if (!json || !out) return T3_NULL_POINTER;
-    const char* end = json + len;
-    static const char kKey[] = "\"expert_quant\"";
-    const char* blk = static_cast<const char*>(memmem(json, len, kKey, sizeof kKey - 1));
-    if (!blk) return T3_EXPERT_LAYOUT_UNSUPPORTED;
-    const char* open = blk + sizeof kKey - 1;
-    while (open < end && *open != '{' && (*open == ':' || *open == ' ' || *open == '\n' || *open == '\t' || *open == '\r')) ++open;
-    if (open >= end || *open != '{') return T3_EXPERT_LAYOUT_UNSUPPORTED;
-    const char* close = open;
-    int depth = 0;
-    for (; close < end; ++close) {
-        if (*close == '{') ++depth;
-        if (*close == '}' && --depth == 0) break;
-    }
-    if (close >= end) return T3_EXPERT_LAYOUT_UNSUPPORTED;
-    std::string v;
-    bool is_str = false;
-    if (!json_value(open, close + 1, "format", v, is_str) || !is_str || v != "exl3") return T3_EXPERT_LAYOUT_UNSUPPORTED;
-    if (!json_value(open, close + 1, "k", v, is_str) || is_str) return T3_EXPERT_LAYOUT_UNSUPPORTED;
-    char* tail = nullptr;
-    const double k = strtod(v.c_str(), &tail);
-    if (tail == v.c_str() || *tail != '\0') return T3_EXPERT_LAYOUT_UNSUPPORTED;
-    const double scaled = k * 16.0, rounded = std::round(scaled);
+    // a top-level object field, as the reference reads it (src/core/spec.zig:38-50): a key of that name nested deeper, or
+    // inside a string, is not the block
+    t3json::JsonReader r{json, json + len};
+    const t3json::Json root = r.value();
+    r.skip();
+    if (!r.ok || r.p != r.end || root.kind != t3json::Json::kObject) return T3_EXPERT_LAYOUT_UNSUPPORTED;
+    const t3json::Json* blk = root.get("expert_quant");
+    if (!blk || blk->kind != t3json::Json::kObject) return T3_EXPERT_LAYOUT_UNSUPPORTED;
+    const t3json::Json* format = blk->get("format");
+    if (!format || format->kind != t3json::Json::kString || format->s != "exl3") return T3_EXPERT_LAYOUT_UNSUPPORTED;
+    const t3json::Json* k = blk->get("k");
+    if (!k || (k->kind != t3json::Json::kInt && k->kind != t3json::Json::kFloat)) return T3_EXPERT_LAYOUT_UNSUPPORTED;
+    const double scaled = k->f * 16.0, rounded = std::round(scaled);
     if (std::fabs(scaled - rounded) > 1e-6 || rounded < 0 || rounded > 1024) return T3_EXPERT_LAYOUT_UNSUPPORTED;
     if (!rate_ok((int)rounded)) return T3_EXPERT_LAYOUT_UNSUPPORTED;
-    if (!json_value(open, close + 1, "codebook", v, is_str) || !is_str) return T3_EXPERT_LAYOUT_UNSUPPORTED;
+    const t3json::Json* codebook = blk->get("codebook");
+    if (!codebook || codebook->kind != t3json::Json::kString) return T3_EXPERT_LAYOUT_UNSUPPORTED;
     int cb;
-    if (v == "mul1") cb = T3_MUL1;
-    else if (v == "mcg") cb = T3_MCG;
+    if (codebook->s == "mul1") cb = T3_MUL1;
+    else if (codebook->s == "mcg") cb = T3_MCG;
     else return T3_EXPERT_LAYOUT_UNSUPPORTED;
     int window = 16;
-    if (json_value(open, close + 1, "window", v, is_str)) {
-        if (is_str) return T3_WINDOW_UNSUPPORTED;
-        char* t2 = nullptr;
-        const long w = strtol(v.c_str(), &t2, 10);
-        if (t2 == v.c_str() || *t2 != '\0' || w < 8 || w > 16) return T3_WINDOW_UNSUPPORTED;
-        window = (int)w;
+    if (const t3json::Json* w = blk->get("window")) {
+        if (w->kind != t3json::Json::kInt || w->i < 8 || w->i > 16) return T3_WINDOW_UNSUPPORTED;
+        window = (int)w->i;
     }
     out->n = (uint32_t)rounded;
     out->codebook = cb;
@@ -385,6 +341,7 @@ int t3_linear_resident(const void* x, int x_dtype, size_t rows, const void* w_ha
     if (!dtype_ok(x_dtype)) return T3_BAD_EXL3_DTYPE;
     if (rows <= T3_DECODE_ROWS_MAX) return T3_ENGINE_NOT_IMPLEMENTED;  // decode rows read the codes, never W_hat
     if (rows > 0x7FFFFFFFu / (size_t)(in_dim > out_dim ? in_dim : out_dim)) return T3_BAD_EXL3_SHAPE;
+    if (rows > kPrefillDenseRowsMax) return T3_BAD_EXL3_SHAPE;
     if (!workspace || workspace_bytes < t3_linear_workspace_bytes(rows, in_dim, out_dim, 16)) return T3_WORKSPACE_TOO_SMALL;
     PrefillLinearArgs p = {x, y, nullptr, w_hat_t, suh, svh, (uint32_t)rows, (uint32_t)in_dim, (uint32_t)out_dim, 16u, 0xFFFFu,
                            x_dtype, workspace, dev_error_ptr()};
@@ -429,6 +386,7 @@ int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, cons
     if (rows > T3_DECODE_ROWS_MAX) {
         if (!cfg.prefill) return T3_ENGINE_NOT_IMPLEMENTED;
         if (rows > 0x7FFFFFFFu / (size_t)(in_dim > out_dim ? in_dim : out_dim)) return T3_BAD_EXL3_SHAPE;
+        if (rows > kPrefillDenseRowsMax) return T3_BAD_EXL3_SHAPE;  // the prepare launch's row groups are a grid dimension
         if (!workspace || workspace_bytes < t3_linear_workspace_bytes(rows, in_dim, out_dim, n)) return T3_WORKSPACE_TOO_SMALL;
         PrefillLinearArgs p = {x, y, static_cast<const uint8_t*>(trellis), nullptr, suh, svh, (uint32_t)rows, (uint32_t)in_dim,
                                (uint32_t)out_dim, (uint32_t)n, mask, x_dtype, workspace, dev_error_ptr()};
@@ -505,6 +463,9 @@ int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const
         cfg = g_cfg;
     }
     if (rows > T3_DECODE_ROWS_MAX && !cfg.prefill) return T3_ENGINE_NOT_IMPLEMENTED;  // src/root.zig:850-852
+    // the prefill chain's launches carry row groups in a grid dimension (65535 at most): 8 rows a group in the last launch,
+    // 64 row-slots a group in the prepare and the middle
+    if (rows > T3_DECODE_ROWS_MAX && (rows > kPrefillMoeRowsMax || rows * (size_t)topk > kPrefillSlotsMax)) return T3_BAD_EXL3_SHAPE;
     if (rows * (size_t)topk > 0x7FFFFFFFu / (size_t)(bank->hidden > bank->inter ? bank->hidden : bank->inter)) return T3_BAD_EXL3_SHAPE;
     const size_t need = t3_moe_workspace_bytes(rows, topk, bank);
     if (!workspace || workspace_bytes < need) return T3_WORKSPACE_TOO_SMALL;
@@ -670,6 +631,7 @@ int t3_moe_swiglu_rows(const void* x, int x_dtype, size_t x_rows, const void* ro
         cfg = g_cfg;
     }
     if (!cfg.prefill || slots <= T3_DECODE_ROWS_MAX) return T3_ENGINE_NOT_IMPLEMENTED;  // src/root.zig:1059,1066
+    if (slots > kPrefillMoeRowsMax) return T3_BAD_EXL3_SHAPE;  // row groups of the last launch are a grid dimension
     if (bank->n_gate != bank->n_down) return T3_ENGINE_NOT_IMPLEMENTED;                 // src/root.zig:1074
     if (slots > 0x7FFFFFFFu / (size_t)(bank->hidden > bank->inter ? bank->hidden : bank->inter)) return T3_BAD_EXL3_SHAPE;
     uint32_t mask;

@@ -395,15 +395,20 @@ __global__ void __launch_bounds__(256) moe_merge_kernel(const MoeArgs a) {
 template <typename Args>
 using KernelFn = void (*)(const Args);
 
-// Raises a kernel's dynamic shared-memory limit once per process (the call is not free, the launches are hot).
+// Raises a kernel's dynamic shared-memory limit once per device and kernel (the attribute is per device; the call is not
+// free and the launches are hot).
 cudaError_t allow_big_smem(const void* fn) {
     static std::mutex mu;
-    static std::unordered_set<const void*> done;
+    static std::unordered_set<uint64_t> done;
+    int dev = 0;
+    cudaError_t rc = cudaGetDevice(&dev);
+    if (rc != cudaSuccess) return rc;
+    const uint64_t key = reinterpret_cast<uint64_t>(fn) ^ ((uint64_t)(dev + 1) << 56);
     std::lock_guard<std::mutex> lock(mu);
-    if (done.count(fn)) return cudaSuccess;
-    cudaError_t rc = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemvSmemLimit);
+    if (done.count(key)) return cudaSuccess;
+    rc = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemvSmemLimit);
     if (rc == cudaSuccess) rc = cudaFuncSetAttribute(fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);  // clusters of 16
-    if (rc == cudaSuccess) done.insert(fn);
+    if (rc == cudaSuccess) done.insert(key);
     return rc;
 }
 

@@ -66,6 +66,12 @@ uint32_t gemv_smem_bytes(uint32_t row_cap, uint32_t xrows, uint32_t slice_max, u
 constexpr uint32_t kGemvSmemLimit = 200u * 1024u;
 uint32_t row_cap_for(uint32_t rows);
 
+// Row limits of the prefill launches, whose row groups are a grid dimension (65535 at most): the dense prepare takes 64
+// rows a group; the routed chain's last launch 8 rows a group, its prepare and middle 64 row-slots a group.
+constexpr size_t kPrefillDenseRowsMax = (size_t)65535 * 64;
+constexpr size_t kPrefillMoeRowsMax = (size_t)65535 * 8;
+constexpr size_t kPrefillSlotsMax = (size_t)65535 * 64;
+
 // One dense linear at prefill rows (rows > 32): prepare -> tcgen05 GEMM with the decode in its weight loader -> finish
 struct PrefillLinearArgs {
     const void* x;

@@ -15,137 +15,12 @@
 
 #include "../../include/t3.h"
 #include "../../include/t3_table.h"
+#include "t3_json.h"
 
 namespace {
 
-// ---- a small JSON reader (objects, arrays, strings, numbers, literals) ----------------------------------------------
-
-struct Json {
-    enum Kind { kNull, kBool, kInt, kFloat, kString, kArray, kObject } kind = kNull;
-    bool b = false;
-    long long i = 0;
-    double f = 0;
-    std::string s;
-    std::vector<Json> items;
-    std::map<std::string, Json> fields;
-    const Json* get(const char* key) const {
-        if (kind != kObject) return nullptr;
-        auto it = fields.find(key);
-        return it == fields.end() ? nullptr : &it->second;
-    }
-};
-
-struct JsonReader {
-    const char* p;
-    const char* end;
-    bool ok = true;
-    void skip() {
-        while (p < end && (*p == ' ' || *p == '\t' || *p == '\n' || *p == '\r')) ++p;
-    }
-    bool eat(char c) {
-        skip();
-        if (p < end && *p == c) {
-            ++p;
-            return true;
-        }
-        return false;
-    }
-    std::string str() {
-        std::string out;
-        if (!eat('"')) {
-            ok = false;
-            return out;
-        }
-        while (p < end && *p != '"') {
-            if (*p == '\\' && p + 1 < end) {
-                ++p;
-                switch (*p) {
-                    case 'n': out += '\n'; break;
-                    case 't': out += '\t'; break;
-                    case 'r': out += '\r'; break;
-                    case 'b': out += '\b'; break;
-                    case 'f': out += '\f'; break;
-                    case 'u':
-                        out += '?';
-                        p += (end - p > 4) ? 4 : 0;
-                        break;
-                    default: out += *p;
-                }
-                ++p;
-            } else {
-                out += *p++;
-            }
-        }
-        if (p >= end) ok = false;
-        else ++p;
-        return out;
-    }
-    Json value(int depth = 0) {
-        Json v;
-        skip();
-        if (p >= end || depth > 64) {
-            ok = false;
-            return v;
-        }
-        if (*p == '{') {
-            ++p;
-            v.kind = Json::kObject;
-            if (eat('}')) return v;
-            do {
-                std::string key = str();
-                if (!ok || !eat(':')) {
-                    ok = false;
-                    return v;
-                }
-                v.fields[key] = value(depth + 1);
-                if (!ok) return v;
-            } while (eat(','));
-            if (!eat('}')) ok = false;
-        } else if (*p == '[') {
-            ++p;
-            v.kind = Json::kArray;
-            if (eat(']')) return v;
-            do {
-                v.items.push_back(value(depth + 1));
-                if (!ok) return v;
-            } while (eat(','));
-            if (!eat(']')) ok = false;
-        } else if (*p == '"') {
-            v.kind = Json::kString;
-            v.s = str();
-        } else if (end - p >= 4 && !strncmp(p, "true", 4)) {
-            v.kind = Json::kBool, v.b = true, p += 4;
-        } else if (end - p >= 5 && !strncmp(p, "false", 5)) {
-            v.kind = Json::kBool, p += 5;
-        } else if (end - p >= 4 && !strncmp(p, "null", 4)) {
-            p += 4;
-        } else {
-            const char* q = p;
-            bool is_float = false;
-            while (q < end && (isdigit((unsigned char)*q) || *q == '-' || *q == '+' || *q == '.' || *q == 'e' || *q == 'E')) {
-                if (*q == '.' || *q == 'e' || *q == 'E') is_float = true;
-                ++q;
-            }
-            if (q == p) {
-                ok = false;
-                return v;
-            }
-            const std::string tok(p, q);
-            char* tail = nullptr;
-            if (is_float) {
-                v.kind = Json::kFloat;
-                v.f = strtod(tok.c_str(), &tail);
-            } else {
-                v.kind = Json::kInt;
-                v.i = strtoll(tok.c_str(), &tail, 10);
-                v.f = (double)v.i;
-            }
-            if (!tail || *tail != '\0') ok = false;
-            p = q;
-        }
-        return v;
-    }
-};
+using t3json::Json;
+using t3json::JsonReader;
 
 bool parse_object(const char* text, Json& out) {
     if (!text) return false;
@@ -390,6 +265,13 @@ t3_verdict table_load_bank(const t3_load_ctx* ctx, const t3_array* t, const t3_a
 // device arrays returns with its kernels still in flight, and a call on another stream must not write the same scratch.
 struct Staging {
     std::mutex mu;
+    int device = -1;  // the device whose memory the buffers are: a call with another device current is refused, never run
+    bool owns_current() {
+        int dev = -1;
+        if (cudaGetDevice(&dev) != cudaSuccess) return false;
+        if (device < 0) device = dev;
+        return device == dev;
+    }
     struct Buf {
         void* p = nullptr;
         size_t cap = 0;
@@ -450,6 +332,7 @@ struct Staging {
             cudaFree(kv.second.rows.p);
         }
         per_stream.clear();
+        device = -1;
         cudaFreeHost(hx);
         cudaFreeHost(hy);
         hx = hy = hx_dev = hy_dev = nullptr;
@@ -482,6 +365,7 @@ t3_verdict table_matmul(const t3_weight* w, const t3_array* x, void* stream, t3_
     const size_t es = elem_size(x->dtype), xb = rows * w->in_dim * es, yb = rows * w->out_dim * es;
     const bool host = !x->device || !out->device;
     std::unique_lock<std::mutex> lock(g_staging.mu);
+    if (!g_staging.owns_current()) return refuse(T3_VERDICT_FAILED, "CudaError");  // the staging buffers live on another device
     const size_t wsb = t3_linear_workspace_bytes(rows, w->in_dim, w->out_dim, w->block);
     Staging::StreamWs& sws = g_staging.of(stream);
     const bool decode_rows = rows <= T3_DECODE_ROWS_MAX;
@@ -564,6 +448,7 @@ t3_verdict table_swiglu(const t3_weight* gate, const t3_weight* up, const t3_wei
     const size_t es = elem_size(x->dtype), xb = rows * bank.hidden * es;
     const bool host = !x->device || !out->device || !inds->device || !scores->device;
     std::unique_lock<std::mutex> lock(g_staging.mu);
+    if (!g_staging.owns_current()) return refuse(T3_VERDICT_FAILED, "CudaError");  // the staging buffers live on another device
     const void *xd = nullptr, *id = nullptr, *sd = nullptr;
     if (!stage_in(x, g_staging.x, xb, s, &xd) || !stage_in(inds, g_staging.inds, rows * topk * 4u, s, &id) ||
         !stage_in(scores, g_staging.scores, rows * topk * elem_size(scores->dtype), s, &sd))
