@@ -355,10 +355,25 @@ def prefill_submetric(t3, synth, torch) -> dict:
     return out
 
 
+def device_bank(t3, synth, torch, seed: int, experts: int, hidden: int, inter: int, n: int):
+    """A routed bank whose code words are drawn on the device (uniform halfwords; the host generator would take minutes at
+    config 5's size) with synth.bank's scale vectors."""
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    rng = np.random.default_rng(seed)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    projs = []
+    for i, o in ((hidden, inter), (hidden, inter), (inter, hidden)):
+        projs.append(t3.Proj(torch.randint(-32768, 32768, (experts, i // 16, o // 16, n), dtype=torch.int16, device="cuda", generator=gen),
+                             dev(synth.signs(rng, (experts, i))), dev(synth.signs(rng, (experts, o), synth.pow2_inv_sqrt(i)))))
+    return t3.Bank(*projs)
+
+
 def sharded_submetric(t3, synth, torch, dist, rank: int, world: int) -> dict:
-    """The two sharded paths at N > 1 (every rank calls this): the config 4 routed layer expert-parallel, 4096 tokens a
-    rank (two all-to-alls a layer), and config 5's q_b projection column-sharded (one all-gather). Device time, max over
-    ranks."""
+    """The two sharded paths (every rank calls this; at one GPU the same code runs as a world of one, so the per-N values
+    compare): the routed layer expert-parallel at a fixed number of tokens a rank — config 4's geometry at K = 3 and 4096
+    tokens, config 5's (hidden 7168, 256 experts x 2048, top-8, K = 4) at 8192 tokens — and config 5's q_b projection
+    column-sharded, gathered in full and left sharded. Device time, median of the
+    repetitions, max over ranks."""
     from turboexl3_b200 import parallel as par
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
@@ -366,34 +381,37 @@ def sharded_submetric(t3, synth, torch, dist, rank: int, world: int) -> dict:
         fn()
         torch.cuda.synchronize()
         dist.barrier()
-        t = torch.tensor([time_us(fn, reps)], dtype=torch.float64, device="cuda")
+        t = torch.tensor([time_stats(fn, reps)["median"]], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
     out = {}
-    H, I, E, topk, n, rows = 2048, 512, 512, 10, 48, 4096
-    per = E // world
-    arrs = synth.bank(100 + rank, per, H, I, n)  # this rank's experts only
-    local = t3.Bank(t3.Proj(dev(arrs["gate_t"]), dev(arrs["gate_suh"]), dev(arrs["gate_svh"])),
-                    t3.Proj(dev(arrs["up_t"]), dev(arrs["up_suh"]), dev(arrs["up_svh"])),
-                    t3.Proj(dev(arrs["down_t"]), dev(arrs["down_suh"]), dev(arrs["down_svh"])))
-    inds, scores = synth.routing(200 + rank, rows, E, topk)
-    x, di, ds = dev(synth.activations(300 + rank, rows, H)), dev(inds), dev(scores)
-    us = timed(lambda: par.ep_moe_cuda(x, local, di, ds, E, t3.Decode.mul1), 3)
-    out["ep_moe_config4_K3"] = {"tokens_per_rank": rows, "us_per_layer": round(us, 1),
-                                "tokens_per_s": round(world * rows / us * 1e6),
-                                "TFLOPS": round(world * 2.0 * rows * topk * 3 * H * I / us / 1e6, 1),
-                                "exchange": "all_to_all_single x rows out, v rows back; merge at the home rank"}
+    for (name, H, I, E, topk, n, rows, kind, reps) in (("ep_moe_config4_K3", 2048, 512, 512, 10, 48, 4096, "softmax", 20),
+                                                       ("ep_moe_config5_K4", 7168, 2048, 256, 8, 64, 8192, "sigmoid", 5)):
+        local = device_bank(t3, synth, torch, 100 + rank, E // world, H, I, n)  # this rank's experts only
+        inds, scores = synth.routing(200 + rank, rows, E, topk, kind=kind)
+        x, di, ds = dev(synth.activations(300 + rank, rows, H)), dev(inds), dev(scores)
+        us = timed(lambda: par.ep_moe_cuda(x, local, di, ds, E, t3.Decode.mul1), reps)
+        out[name] = {"tokens_per_rank": rows, "us_per_layer": round(us, 1), "tokens_per_s": round(world * rows / us * 1e6),
+                     "TFLOPS": round(world * 2.0 * rows * topk * 3 * H * I / us / 1e6, 1), "scaling": "weak",
+                     "exchange": "all_to_all_single: each token row once to every rank that owns one of its experts, "
+                                 "per-slot v rows back; merge at the home rank in slot order"}
+        del local, x
+        torch.cuda.empty_cache()
     in_dim, out_dim = 1536, 24576
     trellis, suh, svh = synth.linear(400, in_dim, out_dim, 64)
     t_sh, svh_sh = par.shard_columns(dev(trellis), dev(svh), rank, world)
     suh_d = dev(suh)
     for r in (1, 4096):
         xr = dev(synth.activations(401 + r, r, in_dim))
-        us = timed(lambda: par.column_sharded_linear(xr, t_sh, suh_d, svh_sh, out_dim, t3.Decode.mul1), 5)
+        res = {}
+        for label, kw in (("gathered", {}), ("left_sharded", {"gather": "none"})):
+            res[label + "_us"] = round(timed(lambda: par.column_sharded_linear(xr, t_sh, suh_d, svh_sh, out_dim, t3.Decode.mul1, **kw), 20), 1)
+        best = res["gathered_us"]
         out[f"column_sharded_q_b_1536x24576_K4_rows{r}"] = {
-            "us": round(us, 1), "code_GBps": round(in_dim * out_dim * 0.5 / us / 1e3, 1),
-            "TFLOPS": round(2.0 * r * in_dim * out_dim / us / 1e6, 1), "exchange": "all_gather of y column shards"}
+            **res, "TFLOPS_gathered": round(2.0 * r * in_dim * out_dim / best / 1e6, 1),
+            "TFLOPS_left_sharded": round(2.0 * r * in_dim * out_dim / res["left_sharded_us"] / 1e6, 1), "scaling": "strong",
+            "exchange": "all_gather_into_tensor of y column shards (none when left sharded)"}
     return out
 
 
@@ -617,7 +635,28 @@ def run_ours(args) -> None:
         except Exception as exc:  # noqa: BLE001 - reported in the line
             return {"error": f"{type(exc).__name__}: {str(exc)[:120]}"}
 
+    # the sharded paths first: every rank takes part, and the other ranks must not sit in a collective while rank 0 runs
+    # its single-GPU extras
+    sharded = None
+    if not args.quick:
+        if world == 1 and not dist.is_initialized():  # a world of one, so the sharded paths run the code they run at N > 1
+            import socket
+            with socket.socket() as sk:
+                sk.bind(("127.0.0.1", 0))
+                port = sk.getsockname()[1]
+            keep = os.dup(1)
+            os.dup2(2, 1)
+            try:
+                dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1,
+                                        device_id=torch.device("cuda", local))
+            finally:
+                sys.stdout.flush()
+                os.dup2(keep, 1)
+                os.close(keep)
+        sharded = guarded(lambda: sharded_submetric(t3, synth, torch, dist, rank, world))
     extra = {}
+    if sharded is not None:
+        extra.setdefault("submetrics", {})["sharded"] = sharded
     if rank == 0 and not args.quick:
         # the 21 linears with nothing ordering them
         try:
@@ -664,14 +703,11 @@ def run_ours(args) -> None:
             return out
         extra["rows_2048x6144_K4"] = guarded(per_rows)
         extra["trunk_config5_K4_rows1"] = guarded(lambda: trunk_submetric(t3, synth, torch))
-        extra["submetrics"] = {"moe_layer_decode_rows_config3": guarded(lambda: moe_submetric(t3, synth, torch)),
-                               "prefill": guarded(lambda: prefill_submetric(t3, synth, torch))}
+        extra.setdefault("submetrics", {}).update({"moe_layer_decode_rows_config3": guarded(lambda: moe_submetric(t3, synth, torch)),
+                                                   "prefill": guarded(lambda: prefill_submetric(t3, synth, torch))})
 
-    if world > 1 and not args.quick:
-        extra.setdefault("submetrics", {})["sharded"] = guarded(
-            lambda: sharded_submetric(t3, synth, torch, dist, rank, world))
     if rank != 0:
-        if world > 1:
+        if dist.is_initialized():
             dist.destroy_process_group()
         return
 
@@ -721,7 +757,7 @@ def run_ours(args) -> None:
     }
     line.update(extra)
     print(json.dumps(line))
-    if world > 1:
+    if dist.is_initialized():
         dist.destroy_process_group()
 
 

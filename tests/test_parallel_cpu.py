@@ -20,6 +20,12 @@ def test_plan_dispatch_groups_slots_by_owner_in_slot_order():
     assert plan.order.tolist() == [1, 3, 2, 5, 0, 4]          # dest 0: slots 1,3; dest 1: 2,5; dest 2: 0; dest 3: 4
     assert plan.rows_of_sent.tolist() == [0, 1, 0, 1, 0, 1]
     assert plan.local_expert.tolist() == [0, 1, 1, 0, 1, 1]
+    # a row travels once to each rank that owns any of its experts; each sent slot names its row inside that rank's group
+    assert plan.row_counts == [2, 2, 1, 1] and plan.send_rows.tolist() == [0, 1, 0, 1, 0, 1]
+    assert plan.row_in_group.tolist() == [0, 1, 0, 1, 0, 0]
+    dup = par.plan_dispatch(torch.tensor([[0, 1, 4], [5, 2, 3]], dtype=torch.int32), 8, 2)  # 4 experts a rank
+    assert dup.send_counts == [4, 2] and dup.row_counts == [2, 2]       # row 0 -> rank 0 twice, once to rank 1: sent once each
+    assert dup.send_rows.tolist() == [0, 1, 0, 1] and dup.row_in_group.tolist() == [0, 0, 1, 1, 0, 1]
     with pytest.raises(ValueError):
         par.plan_dispatch(inds, 7, 4)
 
@@ -52,8 +58,8 @@ def _worker(rank: int, world: int, port: int, fail):
             inds[:, :] = inds % per                           # rank 0 sends everything to itself and receives from others
         scores = torch.rand((rows, topk), generator=g)
 
-        def expert_fn(xr, er):                                # stand-in expert: scales by (global expert id + 1)
-            return xr * (er.to(torch.float32) + 1.0 + rank * per).unsqueeze(1)
+        def expert_fn(xr, row_of_slot, er):                   # stand-in expert: scales by (global expert id + 1)
+            return xr[row_of_slot.to(torch.int64)] * (er.to(torch.float32) + 1.0 + rank * per).unsqueeze(1)
 
         def merge_fn(v, sc):
             y = torch.zeros((v.shape[0], v.shape[2]))
@@ -80,6 +86,11 @@ def _worker(rank: int, world: int, port: int, fail):
         t_shard, svh_shard = par.shard_columns(trellis, svh, rank, world)
         y = par.column_sharded_linear(xs, t_shard, suh, svh_shard, out_dim, None, linear_fn=fake_linear)
         assert torch.equal(y, fake_linear(xs, trellis, suh, svh, None)), f"rank {rank}: gathered columns differ"
+        stacked = par.column_sharded_linear(xs, t_shard, suh, svh_shard, out_dim, None, linear_fn=fake_linear, gather="stacked")
+        b0, b1 = par.column_blocks(out_dim, rank, world)
+        assert stacked.shape[0] == world and torch.equal(stacked[rank][:, :128 * (b1 - b0)], y[:, 128 * b0:128 * b1])
+        mine = par.column_sharded_linear(xs, t_shard, suh, svh_shard, out_dim, None, linear_fn=fake_linear, gather="none")
+        assert torch.equal(mine, y[:, 128 * b0:128 * b1])
         dist.barrier()
         dist.destroy_process_group()
     except Exception as exc:  # surface the failure in the parent

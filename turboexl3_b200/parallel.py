@@ -33,23 +33,38 @@ def experts_per_rank(experts: int, world: int) -> int:
 
 @dataclass
 class DispatchPlan:
-    """Where each of this rank's row-slots goes. Slot s = row * topk + k."""
+    """Where each of this rank's row-slots goes. Slot s = row * topk + k. A token row travels ONCE to every rank that owns
+    any of its experts (not once per slot): `send_rows` lists the rows to send grouped by destination, and every sent slot
+    names its row by position inside its destination's group."""
     order: torch.Tensor        # [S] slot ids grouped by destination rank (stable: ascending slot inside a rank)
     send_counts: list          # row-slots to each rank
     rows_of_sent: torch.Tensor  # [S] the row of each sent slot, in send order
     local_expert: torch.Tensor  # [S] the expert's index on its owner, in send order (int32)
+    send_rows: torch.Tensor     # [R] distinct (destination, row) pairs' rows, grouped by destination, rows ascending
+    row_counts: list           # token rows to each rank
+    row_in_group: torch.Tensor  # [S] for each sent slot, the position of its row inside its destination's group (int32)
 
 
 def plan_dispatch(inds: torch.Tensor, experts: int, world: int) -> DispatchPlan:
-    """inds [rows, topk] (any int dtype, any device)."""
+    """inds [rows, topk] (any int dtype, any device). One host read: the per-destination counts."""
     per = experts_per_rank(experts, world)
     flat = inds.reshape(-1).to(torch.int64)
-    topk = inds.shape[-1]
+    rows, topk = inds.shape
     dest = torch.div(flat, per, rounding_mode="floor").clamp_(0, world - 1)
     order = torch.sort(dest, stable=True).indices
-    counts = torch.bincount(dest, minlength=world).tolist()
-    return DispatchPlan(order, counts, torch.div(order, topk, rounding_mode="floor"),
-                        (flat[order] % per).to(torch.int32))
+    rows_of_sent = torch.div(order, topk, rounding_mode="floor")
+    dest_sent = dest[order]
+    # the (destination, row) pairs in send order are already sorted (stable sort, slots of a row are adjacent): distinct
+    # pairs are runs
+    key = dest_sent * max(rows, 1) + rows_of_sent
+    uniq, inverse = torch.unique_consecutive(key, return_inverse=True)
+    row_dest = torch.div(uniq, max(rows, 1), rounding_mode="floor")
+    slot_counts = torch.bincount(dest, minlength=world)
+    row_counts = torch.bincount(row_dest, minlength=world)
+    starts = torch.cumsum(row_counts, 0) - row_counts
+    counts = torch.stack([slot_counts, row_counts]).tolist()  # the plan's one host read
+    return DispatchPlan(order, counts[0], rows_of_sent, (flat[order] % per).to(torch.int32), uniq % max(rows, 1), counts[1],
+                        (inverse - starts[dest_sent]).to(torch.int32))
 
 
 def _all_to_all_rows(send: torch.Tensor, send_counts: list, recv_counts: list, group) -> torch.Tensor:
@@ -59,22 +74,37 @@ def _all_to_all_rows(send: torch.Tensor, send_counts: list, recv_counts: list, g
 
 
 def ep_moe(x: torch.Tensor, inds: torch.Tensor, scores: torch.Tensor, experts: int,
-           expert_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor],
+           expert_fn: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor],
            merge_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor], group=None) -> torch.Tensor:
     """One routed layer, expert-parallel. x [rows, hidden] (this rank's rows), inds/scores [rows, topk] with GLOBAL
-    expert ids. expert_fn(x_recv [R, hidden], local_expert [R] int32) -> v [R, hidden]: each received row through one
-    local expert. merge_fn(v [rows, topk, hidden], scores) -> y [rows, hidden]. Returns y for this rank's rows."""
+    expert ids. expert_fn(x_recv [R, hidden], row_of_slot [S] int32, local_expert [S] int32) -> v [S, hidden]: received
+    slot i runs row x_recv[row_of_slot[i]] through local expert local_expert[i]. merge_fn(v [rows, topk, hidden], scores)
+    -> y [rows, hidden]. Returns y for this rank's rows.
+
+    Exchanges: the counts (one small all-to-all; the plan and the received counts are the two host reads), the distinct token rows, the per-slot (row, expert)
+    pairs, and the finished per-slot outputs back."""
     world = dist.get_world_size(group)
     rows, topk = inds.shape
     plan = plan_dispatch(inds, experts, world)
-    counts_out = torch.tensor(plan.send_counts, dtype=torch.int64, device=x.device)
+    counts_out = torch.tensor([plan.send_counts, plan.row_counts], dtype=torch.int64, device=x.device).t().contiguous()
     counts_in = torch.empty_like(counts_out)
     dist.all_to_all_single(counts_in, counts_out, group=group)
-    recv_counts = counts_in.tolist()
-    x_recv = _all_to_all_rows(x[plan.rows_of_sent], plan.send_counts, recv_counts, group)
-    e_recv = _all_to_all_rows(plan.local_expert.to(x.device), plan.send_counts, recv_counts, group)
-    v_recv = expert_fn(x_recv, e_recv) if x_recv.shape[0] else x_recv.new_empty((0, x.shape[1]))
-    v_back = _all_to_all_rows(v_recv, recv_counts, plan.send_counts, group)
+    recv = counts_in.t().tolist()
+    recv_slots, recv_rows = recv[0], recv[1]
+    x_recv = _all_to_all_rows(x[plan.send_rows], plan.row_counts, recv_rows, group)
+    meta = torch.stack([plan.row_in_group.to(x.device), plan.local_expert.to(x.device)], dim=1)  # [S, 2] int32
+    meta_recv = _all_to_all_rows(meta, plan.send_counts, recv_slots, group)
+    # a received slot names its row inside its SOURCE's group: shift by where that source's rows start here
+    row_starts = torch.tensor(recv_rows, dtype=torch.int64, device=x.device)
+    row_starts = torch.cumsum(row_starts, 0) - row_starts
+    slot_src = torch.repeat_interleave(torch.arange(world, device=x.device), torch.tensor(recv_slots, device=x.device),
+                                       output_size=sum(recv_slots))
+    row_of_slot = (meta_recv[:, 0].to(torch.int64) + row_starts[slot_src]).to(torch.int32)
+    if meta_recv.shape[0]:
+        v_recv = expert_fn(x_recv, row_of_slot, meta_recv[:, 1].contiguous())
+    else:
+        v_recv = x_recv.new_empty((0, x.shape[1]))
+    v_back = _all_to_all_rows(v_recv, recv_slots, plan.send_counts, group)
     v = torch.empty_like(v_back)
     v[plan.order] = v_back  # back to slot order
     return merge_fn(v.view(rows, topk, x.shape[1]), scores)
@@ -95,8 +125,12 @@ def ep_moe_cuda(x: torch.Tensor, bank_local, inds: torch.Tensor, scores: torch.T
     from . import api
     from .mixed import expert_rows
 
-    def expert_fn(xr: torch.Tensor, er: torch.Tensor) -> torch.Tensor:
-        return expert_rows(xr, bank_local, er, dec)
+    def expert_fn(xr: torch.Tensor, row_of_slot: torch.Tensor, er: torch.Tensor) -> torch.Tensor:
+        if er.shape[0] > api.DECODE_ROWS_MAX:
+            # the routed prefill chain over gathered rows (root.moeSwigluRows): a row several slots share is read in place
+            ones = torch.ones(er.shape[0], dtype=torch.float32, device=xr.device)
+            return api.moe_swiglu_rows(xr, row_of_slot, bank_local, er, ones, dec, out_dtype=torch.float16)
+        return expert_rows(xr[row_of_slot.to(torch.int64)], bank_local, er, dec)
 
     def merge_fn(v: torch.Tensor, sc: torch.Tensor) -> torch.Tensor:
         return api.moe_merge(v.contiguous(), sc.contiguous(), x.dtype, shared)
@@ -118,25 +152,36 @@ def shard_columns(trellis: torch.Tensor, svh: torch.Tensor, rank: int, world: in
     return trellis[:, b0 * 8:b1 * 8, :].contiguous(), svh[b0 * 128:b1 * 128].contiguous()
 
 
-def gather_columns(y_local: torch.Tensor, out_dim: int, group=None) -> torch.Tensor:
-    """All ranks' column shards [rows, cols_r] into y [rows, out_dim] (shards may differ by one block)."""
+def gather_columns(y_local: torch.Tensor, out_dim: int, group=None, stacked: bool = False) -> torch.Tensor:
+    """All ranks' column shards [rows, cols_r] in one collective (all_gather_into_tensor). stacked=True returns the
+    buffer as gathered, [world, rows, cols_max] (a head-parallel consumer reads its shard in place; shards narrower than
+    the widest are zero-padded on the right); else y [rows, out_dim] (one more copy: the shards interleaved by row)."""
     world = dist.get_world_size(group)
     rows = y_local.shape[0]
     widths = [128 * (column_blocks(out_dim, r, world)[1] - column_blocks(out_dim, r, world)[0]) for r in range(world)]
     wmax = max(widths)
     padded = y_local if y_local.shape[1] == wmax else torch.nn.functional.pad(y_local, (0, wmax - y_local.shape[1]))
-    parts = [torch.empty((rows, wmax), dtype=y_local.dtype, device=y_local.device) for _ in range(world)]
-    dist.all_gather(parts, padded.contiguous(), group=group)
-    return torch.cat([p[:, :w] for p, w in zip(parts, widths)], dim=1)
+    buf = torch.empty((world, rows, wmax), dtype=y_local.dtype, device=y_local.device)
+    dist.all_gather_into_tensor(buf.view(world * rows, wmax), padded.contiguous(), group=group)  # rank r's rows at [r]
+    if stacked:
+        return buf
+    if all(w == wmax for w in widths):
+        return buf.permute(1, 0, 2).reshape(rows, world * wmax)
+    return torch.cat([buf[r, :, :w] for r, w in enumerate(widths)], dim=1)
 
 
 def column_sharded_linear(x: torch.Tensor, trellis_shard: torch.Tensor, suh: torch.Tensor, svh_shard: torch.Tensor,
-                          out_dim: int, dec, group=None, linear_fn=None) -> torch.Tensor:
-    """y [rows, out_dim] from this rank's column shard; x and suh are replicated."""
+                          out_dim: int, dec, group=None, linear_fn=None, gather: str = "full") -> torch.Tensor:
+    """y from this rank's column shard; x and suh are replicated. gather: "full" -> y [rows, out_dim] on every rank;
+    "stacked" -> [world, rows, cols_max] as gathered; "none" -> this rank's shard [rows, cols_r], no collective (the
+    consumer is sharded the same way). (Gathering in row chunks on a second stream beside the GEMM was measured and
+    dropped: at 4096 rows four chunks took 1876 us against 439 us for one gather after one GEMM.)"""
     if linear_fn is None:
         from .api import linear as linear_fn
     if trellis_shard.shape[1] == 0:
         y_local = x.new_empty((x.shape[0], 0))
     else:
         y_local = linear_fn(x, trellis_shard, suh, svh_shard, dec)
-    return gather_columns(y_local, out_dim, group)
+    if gather == "none":
+        return y_local
+    return gather_columns(y_local, out_dim, group, stacked=gather == "stacked")
