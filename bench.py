@@ -440,6 +440,18 @@ def trunk_submetric(t3, synth, torch) -> dict:
         byts = i * o * n // 128
         out[f"{name}_{i}x{o}"] = {"us": round(us, 2), "us_min": round(st["min"] / copies, 2), "GBps": round(byts / us / 1e3, 1),
                                   "MB": round(byts / 1e6, 1), "reps": st["reps"]}
+        if name in ("q_b", "o"):
+            # what bounds it: the same launches with the codebook hash skipped, the window extraction skipped too, and
+            # nothing but the code stream (the kernel's timing probes; their y is not the linear's)
+            probes = {}
+            try:
+                for label, mode in (("no_hash_us", 1), ("no_funnel_us", 2), ("stream_only_us", 3)):
+                    t3.configure(probe=mode)
+                    gp = graph_of(burst)
+                    probes[label] = round(time_stats(gp.replay, 20)["median"] / copies, 2)
+            finally:
+                t3.configure()
+            out[f"{name}_{i}x{o}"]["probes"] = probes
     return out
 
 

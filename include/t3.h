@@ -95,12 +95,20 @@ typedef struct {
     uint32_t dense_split;    /* K slices of a dense GEMV cluster (1..16); 0 = choose from the shape */
     int no_overlap;          /* 1: launches wait for the stream's previous kernel to finish before they start (no
                                 programmatic dependent launch); for measurements */
+    int probe;               /* timing probes only, never a served kernel (decode.Geometry.probe, src/core/decode.zig:34-35):
+                                t3_linear calls of up to 8 rows launch the dense GEMV with 1 the codebook hash skipped, 2 the
+                                window extraction skipped too, 3 nothing but the code stream (a stage is released as soon
+                                as it has landed); y is then NOT the linear's output. 0 = serve */
 } t3_config;
 void t3_config_default(t3_config* out);
 int t3_configure(const t3_config* cfg);                  /* InvalidTurboexl3Config on a bad value */
 
 /* Bits a kernel sets when one of its bounded waits ran out (the context stays usable). Synchronises `stream`. */
 int t3_device_error(void* stream, uint32_t* bits_out, int clear);
+/* Test hook: launches one warp that waits, with the kernels' own bounded wait, for a barrier phase nothing completes. After
+ * about a second the wait gives up, bit 0 (a copy never landed) is set in the error word and the kernel returns: what a
+ * stalled copy looks like to the host. Nothing faults and the context stays usable. */
+int t3_selftest_wait_runs_out(void* stream);
 
 /* W_hat: the inner f16 weight [in, out] (format.reconstructInner, src/core/format.zig:276-291;
  * Dense.dequantize, src/core/dense.zig:909-922). */
@@ -146,6 +154,19 @@ int t3_moe_swiglu_rows(const void* x, int x_dtype, size_t x_rows, const void* ro
                        const void* inds, const void* scores, int scores_dtype, t3_decode dec, int limit, int clamp_at,
                        void* y, int y_dtype, void* workspace, size_t workspace_bytes, void* stream);
 
+/* deepseek_v41.moeClampedBanked / moeClampedBankedAs (src/models/deepseek_v41/api.zig:173-218): t3_moe_clamped over an expert
+ * streamer's three slot banks at decode rows. Row-slot r is one routed pair: x's row r through the expert at ids[r], packed
+ * (bank << 24 | slot), at weight 1; y [rows, hidden] in y_dtype holds each pair's output (the caller weighs and sums). Each
+ * pair's bytes are t3_moe_clamped's on its bank at top-1 with score 1, rounded once to y_dtype. banks: three t3_bank at one
+ * geometry and rate, each its own slot count (a bank no id names may repeat another's arrays). ids u32 / i32 [rows], rows
+ * 1..T3_BANKED_ROWS_MAX; an id equal to T3_BANKED_SKIP_ID runs no expert and its y row is 0 (banked.skip_id,
+ * src/models/deepseek_v41/banked.zig:87); a bank past 2 or a slot past its bank's count is clamped into range.
+ * limit 1..128, else InvalidExl3Clamp. Workspace: t3_moe_workspace_bytes(min(rows, 32), 1, &banks[0]). */
+#define T3_BANKED_ROWS_MAX 64          /* banked.banked_rows_max, src/models/deepseek_v41/banked.zig:185 */
+#define T3_BANKED_SKIP_ID 0xFFFFFFFFu
+int t3_moe_clamped_banked(const void* x, int x_dtype, size_t rows, const t3_bank* banks, const void* ids, t3_decode dec,
+                          int limit, void* y, int y_dtype, void* workspace, size_t workspace_bytes, void* stream);
+
 /* t3_moe_with_shared for a shared-expert output that another stream is still computing: `shared_ready` is a cudaEvent_t
  * recorded on that stream after `shared` was written. Only the call's last launch (the one that adds `shared`) waits for
  * the event, so the routed experts' launches run beside the shared expert's. The reference's moeWithShared
@@ -190,6 +211,20 @@ size_t t3_resident_bytes(int in_dim, int out_dim);
 int t3_resident_build(const void* trellis, int in_dim, int out_dim, int n, t3_decode dec, void* w_hat_t, void* stream);
 int t3_linear_resident(const void* x, int x_dtype, size_t rows, const void* w_hat_t, const void* suh, const void* svh,
                        int in_dim, int out_dim, void* y, void* workspace, size_t workspace_bytes, void* stream);
+
+/* The un-rotated trunk (root.trunkUnrot, src/root.zig:380-420; dense.unrotCols / unrotRows / residentPlain,
+ * src/core/dense.zig:1587-1690, 1261-1263): the linear taken out of the Hadamard basis once,
+ *   W_std = diag(suh) H W_hat H diag(svh),
+ * so a call past 32 rows is ONE plain tensor-core GEMM y = x W_std in x's dtype: no prepare, no finish. t3_unrot_build
+ * fills w_std_t (t3_resident_bytes bytes) with W_std TRANSPOSED [out, in] in act_dtype (T3_F16 or T3_BF16): the butterflies
+ * run in f32 in the reference kernels' order, times 1/128, suh[i], svh[o], one rounding (the device form of
+ * format.reconstructPublic, src/core/format.zig:295-331, whose f32 sums run in another order). t3_linear_unrot: x
+ * [rows, in] and y [rows, out] in the weight's dtype, f32 accumulation, one rounding of each output — the same linear map
+ * as t3_linear with other roundings (a reordering, as the reference says of it). Up to 32 rows: Exl3EngineNotImplemented
+ * (dense.unrot_min_rows: decode rows keep the trellis paths). x and w_std_t 16-byte aligned. */
+int t3_unrot_build(const void* trellis, const void* suh, const void* svh, int in_dim, int out_dim, int n, t3_decode dec,
+                   int act_dtype, void* w_std_t, void* stream);
+int t3_linear_unrot(const void* x, int x_dtype, size_t rows, const void* w_std_t, int in_dim, int out_dim, void* y, void* stream);
 
 /* root.enginesHeld / root.releaseEngines (src/root.zig:1148-1192). The reference caches a compiled engine per geometry and
  * frees them on request; here kernels are compiled ahead and a plan is recomputed per call, so an "engine" is only the

@@ -239,3 +239,42 @@ def test_scales_that_are_not_signs():
         ref = ob.linear_rows_what(host_f32(x), what, suh, svh, in_dim, out_dim)
         check(host_f32(y), ref, dt, ("general scales", rows, dt))
     assert t3.device_error() == 0
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_context_lives_on():
+    """A copy that never lands must not hang the GPU: the kernels' waits are bounded, the one that gives up sets a bit in
+    the device error word, and the next call runs as usual."""
+    assert t3.device_error() == 0
+    stream = torch.cuda.current_stream().cuda_stream
+    assert t3.lib().t3_selftest_wait_runs_out(stream) == 0
+    bits = t3.device_error()  # synchronises; clears
+    assert bits == 1, bits
+    assert t3.device_error() == 0
+    trellis, suh, svh = synth.linear(3, 256, 256, 32, scaled=True)
+    x = synth.activations(4, 1, 256)
+    y = t3.linear(dev(x), dev(trellis), dev(suh), dev(svh))
+    ref = ob.linear_rows(x.astype(np.float32), trellis, suh, svh, 256, 256, 32, ob.MUL1)
+    assert ob.compare(host_f32(y), ref)["max_ratio"] <= 5e-3
+    assert t3.device_error() == 0
+
+
+def test_timing_probes_run_in_the_served_kernels_place():
+    """The dense GEMV's probes (hash skipped, window extraction skipped, stream only) launch, finish and set no error;
+    their outputs are not the linear's, and serving comes back when the probe is switched off."""
+    trellis, suh, svh = synth.linear(5, 1024, 512, 64, scaled=True)
+    x = dev(synth.activations(6, 3, 1024))
+    args = (x, dev(trellis), dev(suh), dev(svh))
+    served = t3.linear(*args)
+    try:
+        for mode in (1, 2, 3):
+            t3.configure(probe=mode)
+            y = t3.linear(*args)
+            assert y.shape == served.shape
+            assert t3.device_error() == 0
+            with pytest.raises(t3.Exl3Error, match="Exl3EngineNotImplemented"):
+                t3.linear(dev(synth.activations(6, 9, 1024)), *args[1:])
+        with pytest.raises(t3.Exl3Error, match="InvalidTurboexl3Config"):
+            t3.configure(probe=4)
+    finally:
+        t3.configure()
+    assert torch.equal(t3.linear(*args), served)

@@ -53,7 +53,8 @@ class _Spec(C.Structure):
 
 
 class _Config(C.Structure):
-    _fields_ = [("prefill", C.c_int), ("ring_bytes", C.c_uint32), ("dense_split", C.c_uint32), ("no_overlap", C.c_int)]
+    _fields_ = [("prefill", C.c_int), ("ring_bytes", C.c_uint32), ("dense_split", C.c_uint32), ("no_overlap", C.c_int),
+                ("probe", C.c_int)]
 
 
 # every symbol include/t3.h declares: (restype, argtypes)
@@ -67,6 +68,7 @@ SYMBOLS = {
     "t3_config_default": (None, [C.POINTER(_Config)]),
     "t3_configure": (_i, [C.POINTER(_Config)]),
     "t3_device_error": (_i, [_vp, C.POINTER(_u32), _i]),
+    "t3_selftest_wait_runs_out": (_i, [_vp]),
     "t3_dequant": (_i, [_vp, _i, _i, _i, _Decode, _vp, _vp]),
     "t3_codebook_table": (_i, [_Decode, _vp, _vp]),
     "t3_linear_workspace_bytes": (_sz, [_sz, _i, _i, _i]),
@@ -85,6 +87,9 @@ SYMBOLS = {
     "t3_resident_bytes": (_sz, [_i, _i]),
     "t3_resident_build": (_i, [_vp, _i, _i, _i, _Decode, _vp, _vp]),
     "t3_linear_resident": (_i, [_vp, _i, _sz, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp]),
+    "t3_unrot_build": (_i, [_vp, _vp, _vp, _i, _i, _i, _Decode, _i, _vp, _vp]),
+    "t3_linear_unrot": (_i, [_vp, _i, _sz, _vp, _i, _i, _vp, _vp]),
+    "t3_moe_clamped_banked": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _Decode, _i, _vp, _i, _vp, _sz, _vp]),
     "t3_engines_held": (None, [_vp]),
     "t3_release_engines": (None, []),
 }
@@ -163,9 +168,10 @@ def _trellis_ok(t: torch.Tensor) -> bool:
     return t.dtype in (torch.uint16, torch.int16)
 
 
-def configure(prefill: bool = True, ring_bytes: int = 0, dense_split: int = 0, no_overlap: bool = False) -> None:
-    """core.config.configure (src/core/config.zig:175): process-wide, before the first call."""
-    cfg = _Config(int(prefill), ring_bytes, dense_split, int(no_overlap))
+def configure(prefill: bool = True, ring_bytes: int = 0, dense_split: int = 0, no_overlap: bool = False, probe: int = 0) -> None:
+    """core.config.configure (src/core/config.zig:175): process-wide, before the first call. probe 1..3 swaps the dense
+    decode-row kernel for a timing probe (see t3_config in include/t3.h): measurements only."""
+    cfg = _Config(int(prefill), ring_bytes, dense_split, int(no_overlap), int(probe))
     _check(lib().t3_configure(C.byref(cfg)))
 
 
@@ -370,6 +376,64 @@ def moe_swiglu_rows(x: torch.Tensor, rows: torch.Tensor, bank: Bank, inds: torch
     _check(L.t3_moe_swiglu_rows(x.data_ptr(), _DTYPES[x.dtype], x.shape[0], rows.data_ptr(), S, C.byref(cb), inds.data_ptr(),
                                 scores.data_ptr(), _DTYPES[scores.dtype], dec._c(), limit, clamp_at, y.data_ptr(),
                                 _DTYPES[out_dtype], ws.data_ptr(), ws_bytes, _stream_ptr(x)))
+    return y
+
+
+BANKED_ROWS_MAX = 64
+BANKED_SKIP_ID = 0xFFFFFFFF
+
+
+def moe_clamped_banked(x: torch.Tensor, banks, ids: torch.Tensor, dec: Decode = Decode.mul1, limit: int = 7,
+                       out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """deepseek_v41.moeClampedBanked / moeClampedBankedAs (src/models/deepseek_v41/api.zig:173-218): x [rows, hidden], banks
+    three `Bank`s of one geometry, ids u32/i32 [rows] packed (bank << 24 | slot); y [rows, hidden] in out_dtype (f32 as
+    the reference's plain entry), each row its pair's output at weight 1; an id of BANKED_SKIP_ID gives a zero row."""
+    _need_cuda(x, ids)
+    if x.dim() != 2 or ids.dim() != 1 or ids.shape[0] != x.shape[0] or len(banks) != 3 or x.shape[1] % 128:
+        raise Exl3Error(1, "BadExl3Shape")
+    if x.dtype not in _DTYPES or out_dtype not in _DTYPES or ids.dtype not in (torch.int32, torch.uint32):
+        raise Exl3Error(2, "BadExl3Dtype")
+    cbs = (_Bank * 3)(*[_bank_c(b, x.shape[1]) for b in banks])
+    rows = x.shape[0]
+    L = lib()
+    ws_bytes = L.t3_moe_workspace_bytes(min(max(rows, 1), 32), 1, C.byref(cbs[0]))
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x.device)
+    y = torch.empty((rows, x.shape[1]), dtype=out_dtype, device=x.device)
+    _check(L.t3_moe_clamped_banked(x.data_ptr(), _DTYPES[x.dtype], rows, cbs, ids.data_ptr(), dec._c(), limit, y.data_ptr(),
+                                   _DTYPES[out_dtype], ws.data_ptr(), ws_bytes, _stream_ptr(x)))
+    return y
+
+
+def unrot_build(trellis: torch.Tensor, suh: torch.Tensor, svh: torch.Tensor, dec: Decode = Decode.mul1,
+                dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """A trunk linear out of the Hadamard basis (t3_unrot_build; root.trunkUnrot, src/root.zig:392-420): W_std transposed,
+    [out, in] in `dtype` (f16 or bf16), W_std = diag(suh) H W_hat H diag(svh)."""
+    _need_cuda(trellis, suh, svh)
+    if trellis.dim() != 3:
+        raise Exl3Error(1, "BadExl3Shape")
+    in_dim, out_dim, n = trellis.shape[0] * 16, trellis.shape[1] * 16, trellis.shape[2]
+    if suh.numel() != in_dim or svh.numel() != out_dim:
+        raise Exl3Error(1, "BadExl3Shape")
+    if not _trellis_ok(trellis) or suh.dtype != torch.float16 or svh.dtype != torch.float16 or dtype not in (torch.float16, torch.bfloat16):
+        raise Exl3Error(2, "BadExl3Dtype")
+    w = torch.empty((out_dim, in_dim), dtype=dtype, device=trellis.device)
+    _check(lib().t3_unrot_build(trellis.data_ptr(), suh.data_ptr(), svh.data_ptr(), in_dim, out_dim, n, dec._c(), _DTYPES[dtype],
+                                w.data_ptr(), _stream_ptr(trellis)))
+    return w
+
+
+def linear_unrot(x: torch.Tensor, w_std_t: torch.Tensor) -> torch.Tensor:
+    """y = x W_std on an un-rotated weight (t3_linear_unrot; dense.residentPlain, src/core/dense.zig:1261-1263): more than
+    32 rows, x in the weight's dtype, one tensor-core GEMM."""
+    _need_cuda(x, w_std_t)
+    if x.dim() < 1 or w_std_t.dim() != 2 or x.shape[-1] != w_std_t.shape[1] or not w_std_t.is_contiguous() or not x.is_contiguous():
+        raise Exl3Error(1, "BadExl3Shape")
+    if x.dtype != w_std_t.dtype or x.dtype not in (torch.float16, torch.bfloat16):
+        raise Exl3Error(2, "BadExl3Dtype")
+    out_dim, in_dim = w_std_t.shape
+    rows = x.numel() // in_dim
+    y = torch.empty(x.shape[:-1] + (out_dim,), dtype=x.dtype, device=x.device)
+    _check(lib().t3_linear_unrot(x.data_ptr(), _DTYPES[x.dtype], rows, w_std_t.data_ptr(), in_dim, out_dim, y.data_ptr(), _stream_ptr(x)))
     return y
 
 

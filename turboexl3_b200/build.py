@@ -29,6 +29,9 @@ UNITS = [
     ("t3_dequant.cu", "t3_dequant", []),
     ("t3_decode_rows.cu", "t3_decode_rows_cb0", ["-DT3_CB=0"]),
     ("t3_decode_rows.cu", "t3_decode_rows_cb1", ["-DT3_CB=1"]),
+    ("t3_decode_rows.cu", "t3_decode_rows_probe2", ["-DT3_CB=2"]),  # the dense GEMV's timing probes
+    ("t3_decode_rows.cu", "t3_decode_rows_probe3", ["-DT3_CB=3"]),
+    ("t3_decode_rows.cu", "t3_decode_rows_probe4", ["-DT3_CB=4"]),
 ]
 
 

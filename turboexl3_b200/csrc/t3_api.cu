@@ -17,6 +17,9 @@ namespace t3 {
 
 cudaError_t launch_dense_gemv_cb0(const DenseArgs&, cudaStream_t);
 cudaError_t launch_dense_gemv_cb1(const DenseArgs&, cudaStream_t);
+cudaError_t launch_dense_gemv_cb2(const DenseArgs&, cudaStream_t);  // timing probes: no codebook hash,
+cudaError_t launch_dense_gemv_cb3(const DenseArgs&, cudaStream_t);  // no window extraction either,
+cudaError_t launch_dense_gemv_cb4(const DenseArgs&, cudaStream_t);  // the code stream alone
 cudaError_t launch_moe_gate_up_cb0(const MoeArgs&, cudaStream_t);
 cudaError_t launch_moe_gate_up_cb1(const MoeArgs&, cudaStream_t);
 cudaError_t launch_moe_down_cb0(const MoeArgs&, cudaStream_t);
@@ -40,7 +43,7 @@ void note_engine(int kind, uint64_t a, uint64_t b, uint64_t c, uint64_t d) {
 __device__ uint32_t g_dev_error_word;
 
 std::mutex g_mu;
-t3_config g_cfg = {1, 0, 0, 0};
+t3_config g_cfg = {1, 0, 0, 0, 0};
 uint32_t* g_err_ptr[64] = {};
 unsigned long long* g_trace = nullptr;
 
@@ -163,6 +166,9 @@ uint32_t gemv_smem_bytes(uint32_t row_cap, uint32_t xrows, uint32_t slice_max, u
 
 cudaError_t launch_dense_gemv(const DenseArgs& a, int codebook, cudaStream_t stream) {
     g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (codebook == 2) return launch_dense_gemv_cb2(a, stream);
+    if (codebook == 3) return launch_dense_gemv_cb3(a, stream);
+    if (codebook == 4) return launch_dense_gemv_cb4(a, stream);
     return codebook == T3_MCG ? launch_dense_gemv_cb1(a, stream) : launch_dense_gemv_cb0(a, stream);
 }
 cudaError_t launch_moe_gate_up(const MoeArgs& a, int codebook, cudaStream_t stream) {
@@ -260,6 +266,7 @@ void t3_config_default(t3_config* out) {
     out->ring_bytes = 0;
     out->dense_split = 0;
     out->no_overlap = 0;
+    out->probe = 0;
 }
 
 int t3_configure(const t3_config* cfg) {
@@ -269,9 +276,17 @@ int t3_configure(const t3_config* cfg) {
     if (cfg->no_overlap != 0 && cfg->no_overlap != 1) return T3_INVALID_CONFIG;
     if (cfg->ring_bytes != 0 && (cfg->ring_bytes < 4096u || cfg->ring_bytes > kGemvSmemLimit)) return T3_INVALID_CONFIG;
     if (cfg->prefill != 0 && cfg->prefill != 1) return T3_INVALID_CONFIG;
+    if (cfg->probe < 0 || cfg->probe > 3) return T3_INVALID_CONFIG;
     std::lock_guard<std::mutex> lock(g_mu);
     g_cfg = *cfg;
     return T3_OK;
+}
+
+int t3_selftest_wait_runs_out(void* stream) {
+    uint32_t* p = dev_error_ptr();
+    if (!p) return T3_CUDA_ERROR;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cuda_status(launch_wait_runs_out(p, static_cast<cudaStream_t>(stream)));
 }
 
 int t3_device_error(void* stream, uint32_t* bits_out, int clear) {
@@ -352,6 +367,33 @@ int t3_linear_resident(const void* x, int x_dtype, size_t rows, const void* w_ha
     return cuda_status(rc);
 }
 
+int t3_unrot_build(const void* trellis, const void* suh, const void* svh, int in_dim, int out_dim, int n, t3_decode dec,
+                   int act_dtype, void* w_std_t, void* stream) {
+    if (!trellis || !suh || !svh || !w_std_t) return T3_NULL_POINTER;
+    if (in_dim <= 0 || out_dim <= 0 || in_dim % 128 != 0 || out_dim % 128 != 0 || !rate_ok(n)) return T3_BAD_EXL3_SHAPE;
+    if (act_dtype != T3_F16 && act_dtype != T3_BF16) return T3_BAD_EXL3_DTYPE;
+    uint32_t mask;
+    if (int rc = decode_mask(dec, mask)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    g_launches.fetch_add(2, std::memory_order_relaxed);
+    cudaError_t rc = launch_dequant(static_cast<const uint8_t*>(trellis), (uint32_t)in_dim, (uint32_t)out_dim, (uint32_t)n, mask,
+                                    dec.codebook, 1, w_std_t, s);
+    if (rc == cudaSuccess) rc = launch_unrot(w_std_t, suh, svh, (uint32_t)in_dim, (uint32_t)out_dim, act_dtype, s);
+    return cuda_status(rc);
+}
+
+int t3_linear_unrot(const void* x, int x_dtype, size_t rows, const void* w_std_t, int in_dim, int out_dim, void* y, void* stream) {
+    if (!x || !w_std_t || !y) return T3_NULL_POINTER;
+    if (in_dim <= 0 || out_dim <= 0 || in_dim % 128 != 0 || out_dim % 128 != 0 || rows < 1) return T3_BAD_EXL3_SHAPE;
+    if (x_dtype != T3_F16 && x_dtype != T3_BF16) return T3_BAD_EXL3_DTYPE;
+    if (rows <= T3_DECODE_ROWS_MAX) return T3_ENGINE_NOT_IMPLEMENTED;  // dense.unrot_min_rows: those rows keep the trellis paths
+    if (rows > kPrefillDenseRowsMax || rows > 0x7FFFFFFFu / (size_t)(in_dim > out_dim ? in_dim : out_dim)) return T3_BAD_EXL3_SHAPE;
+    note_engine(2, (uint64_t)in_dim, (uint64_t)out_dim, 0, 2);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cuda_status(launch_plain_linear(x, x_dtype, (uint32_t)rows, w_std_t, (uint32_t)in_dim, (uint32_t)out_dim, y,
+                                           dev_error_ptr(), static_cast<cudaStream_t>(stream)));
+}
+
 int t3_codebook_table(t3_decode dec, void* out, void* stream) {
     if (!out) return T3_NULL_POINTER;
     uint32_t mask;
@@ -424,6 +466,10 @@ int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, cons
     }
     a.x = x;
     a.y = y;
+    if (cfg.probe) {  // a timing probe in the served kernel's place: y is not the linear's output
+        if (rows > 8) return T3_ENGINE_NOT_IMPLEMENTED;
+        return cuda_status(launch_dense_gemv(a, 1 + cfg.probe, static_cast<cudaStream_t>(stream)));
+    }
     return cuda_status(launch_dense_gemv(a, dec.codebook, static_cast<cudaStream_t>(stream)));
 }
 
@@ -445,6 +491,58 @@ int validate_bank(const t3_bank* b, int hidden_of_x) {
 }
 
 size_t align256(size_t v) { return (v + 255u) & ~(size_t)255u; }
+
+// The routed chain at decode rows on filled arguments (geometry, rows, top-k, pointers): plans the launches and records
+// them. workspace: t3_moe_workspace_bytes(rows, topk, bank) bytes.
+int decode_chain(MoeArgs a, const t3_config& cfg, int codebook, void* workspace, cudaStream_t s, void* shared_ready) {
+    const size_t slots = (size_t)a.rows * a.topk;
+    a.hd = workspace;
+    a.v = static_cast<uint8_t*>(workspace) + align256(slots * a.inter * 2u);
+    // Rows one pass over an expert's weights serves. Sized from the geometry's expected members an expert (rows * topk /
+    // experts, with headroom), not from the row count: with many experts a 32-row call still has one or two rows an
+    // expert, and a 32-row pass would pay four times the shared memory and twice the tensor-core steps for nothing. An
+    // expert with more members than this takes further passes over its weights. A row's bytes do not depend on it.
+    const uint32_t expect = (uint32_t)((4u * slots + a.experts - 1u) / a.experts) + 4u;
+    const uint32_t rm = row_cap_for(expect < a.rows ? expect : a.rows);
+    a.row_cap = rm;
+    a.overlap = !cfg.no_overlap;
+    // The K splits depend on hidden and inter only (sized as if a row had eight slots), never on the row count, the top-k
+    // or the bank's size: a row-slot's summation order, hence its bytes, is the same alone and in a batch, and the same in
+    // a one-expert bank (a shared expert, an expert-parallel rank's share) as in the whole bank. A shared expert's chain,
+    // run on a second stream beside the routed chain, then launches the same cluster shapes as the routed one (measured:
+    // a 2-CTA-cluster launch beside 4- or 8-CTA-cluster launches costs a 1-row layer 7 us).
+    constexpr uint32_t kNominalSlots = 8;
+    a.split_gu = pick_split(a.hidden / 128u, (a.inter / 128u) * kNominalSlots, 2u, 4u, one_wave() / 8u);
+    a.slice_max_gu = largest_slice(a.hidden / 128u, a.split_gu);
+    a.split_d = pick_split(a.inter / 128u, (a.hidden / 128u) * kNominalSlots, 1u, 8u, one_wave() / 8u);
+    a.slice_max_d = largest_slice(a.inter / 128u, a.split_d);
+    // sized for the widest row capacity so the split does not move with the rows either
+    while (!plan_ring(32u, 32u, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu)) {
+        if (a.split_gu * 2u > a.hidden / 128u || a.split_gu * 2u > 8u) return T3_ENGINE_NOT_IMPLEMENTED;
+        a.split_gu *= 2u;
+        a.slice_max_gu = largest_slice(a.hidden / 128u, a.split_gu);
+    }
+    while (!plan_ring(32u, 32u, a.slice_max_d, a.split_d, a.n, a.ring_d)) {
+        if (a.split_d * 2u > a.inter / 128u || a.split_d * 2u > 16u) return T3_ENGINE_NOT_IMPLEMENTED;
+        a.split_d *= 2u;
+        a.slice_max_d = largest_slice(a.inter / 128u, a.split_d);
+    }
+    if (!plan_ring(rm, rm, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu) || !plan_ring(rm, rm, a.slice_max_d, a.split_d, a.n, a.ring_d))
+        return T3_ENGINE_NOT_IMPLEMENTED;
+    a.err = dev_error_ptr();
+    if (int rc = cuda_status(launch_moe_gate_up(a, codebook, s))) return rc;
+    if (a.topk == 1u) {
+        // one slot a row: the down launch stores y itself (and adds `shared`), there is nothing to merge
+        if (shared_ready)
+            if (int rc = cuda_status(cudaStreamWaitEvent(s, static_cast<cudaEvent_t>(shared_ready), 0))) return rc;
+        return cuda_status(launch_moe_down(a, codebook, s));
+    }
+    if (int rc = cuda_status(launch_moe_down(a, codebook, s))) return rc;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (shared_ready)  // only the merge reads `shared`: the two GEMV launches above do not wait for it
+        if (int rc = cuda_status(cudaStreamWaitEvent(s, static_cast<cudaEvent_t>(shared_ready), 0))) return rc;
+    return cuda_status(launch_moe_merge(a, s));
+}
 
 int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const void* inds, const void* scores,
              int scores_dtype, int topk, t3_decode dec, uint32_t limit, int clamp_at, const void* shared, void* y,
@@ -507,53 +605,7 @@ int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const
         g_launches.fetch_add((uint64_t)launches, std::memory_order_relaxed);
         return cuda_status(rc);
     }
-    a.hd = workspace;
-    a.v = static_cast<uint8_t*>(workspace) + align256(slots * a.inter * 2u);
-    // Rows one pass over an expert's weights serves. Sized from the geometry's expected members an expert (rows * topk /
-    // experts, with headroom), not from the row count: with many experts a 32-row call still has one or two rows an
-    // expert, and a 32-row pass would pay four times the shared memory and twice the tensor-core steps for nothing. An
-    // expert with more members than this takes further passes over its weights. A row's bytes do not depend on it.
-    const uint32_t expect = (uint32_t)((4u * slots + a.experts - 1u) / a.experts) + 4u;
-    const uint32_t rm = row_cap_for(expect < a.rows ? expect : a.rows);
-    a.row_cap = rm;
-    a.overlap = !cfg.no_overlap;
-    // The K splits depend on hidden and inter only (sized as if a row had eight slots), never on the row count, the top-k
-    // or the bank's size: a row-slot's summation order, hence its bytes, is the same alone and in a batch, and the same in
-    // a one-expert bank (a shared expert, an expert-parallel rank's share) as in the whole bank. A shared expert's chain,
-    // run on a second stream beside the routed chain, then launches the same cluster shapes as the routed one (measured:
-    // a 2-CTA-cluster launch beside 4- or 8-CTA-cluster launches costs a 1-row layer 7 us).
-    constexpr uint32_t kNominalSlots = 8;
-    a.split_gu = pick_split(a.hidden / 128u, (a.inter / 128u) * kNominalSlots, 2u, 4u, one_wave() / 8u);
-    a.slice_max_gu = largest_slice(a.hidden / 128u, a.split_gu);
-    a.split_d = pick_split(a.inter / 128u, (a.hidden / 128u) * kNominalSlots, 1u, 8u, one_wave() / 8u);
-    a.slice_max_d = largest_slice(a.inter / 128u, a.split_d);
-    // sized for the widest row capacity so the split does not move with the rows either
-    while (!plan_ring(32u, 32u, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu)) {
-        if (a.split_gu * 2u > a.hidden / 128u || a.split_gu * 2u > 8u) return T3_ENGINE_NOT_IMPLEMENTED;
-        a.split_gu *= 2u;
-        a.slice_max_gu = largest_slice(a.hidden / 128u, a.split_gu);
-    }
-    while (!plan_ring(32u, 32u, a.slice_max_d, a.split_d, a.n, a.ring_d)) {
-        if (a.split_d * 2u > a.inter / 128u || a.split_d * 2u > 16u) return T3_ENGINE_NOT_IMPLEMENTED;
-        a.split_d *= 2u;
-        a.slice_max_d = largest_slice(a.inter / 128u, a.split_d);
-    }
-    if (!plan_ring(rm, rm, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu) || !plan_ring(rm, rm, a.slice_max_d, a.split_d, a.n, a.ring_d))
-        return T3_ENGINE_NOT_IMPLEMENTED;
-    a.err = dev_error_ptr();
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (int rc = cuda_status(launch_moe_gate_up(a, dec.codebook, s))) return rc;
-    if (a.topk == 1u) {
-        // one slot a row: the down launch stores y itself (and adds `shared`), there is nothing to merge
-        if (shared_ready)
-            if (int rc = cuda_status(cudaStreamWaitEvent(s, static_cast<cudaEvent_t>(shared_ready), 0))) return rc;
-        return cuda_status(launch_moe_down(a, dec.codebook, s));
-    }
-    if (int rc = cuda_status(launch_moe_down(a, dec.codebook, s))) return rc;
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    if (shared_ready)  // only the merge reads `shared`: the two GEMV launches above do not wait for it
-        if (int rc = cuda_status(cudaStreamWaitEvent(s, static_cast<cudaEvent_t>(shared_ready), 0))) return rc;
-    return cuda_status(launch_moe_merge(a, s));
+    return decode_chain(a, cfg, dec.codebook, workspace, static_cast<cudaStream_t>(stream), shared_ready);
 }
 
 }  // namespace
@@ -585,6 +637,80 @@ int t3_moe_clamped(const void* x, int x_dtype, size_t rows, const t3_bank* bank,
     if (limit <= 0 || limit > 128) return T3_INVALID_CLAMP;
     return moe_call(x, x_dtype, rows, bank, inds, scores, scores_dtype, topk, dec, (uint32_t)limit, T3_CLAMP_GATE_IN,
                     nullptr, y, workspace, workspace_bytes, stream);
+}
+
+int t3_moe_clamped_banked(const void* x, int x_dtype, size_t rows, const t3_bank* banks, const void* ids, t3_decode dec,
+                          int limit, void* y, int y_dtype, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!x || !banks || !ids || !y) return T3_NULL_POINTER;
+    if (limit <= 0 || limit > 128) return T3_INVALID_CLAMP;               // deepseek_v41/api.zig:249
+    if (rows < 1 || rows > T3_BANKED_ROWS_MAX) return T3_BAD_EXL3_SHAPE;  // api.zig:349
+    if (int rc = validate_bank(&banks[0], banks[0].hidden)) return rc;
+    for (int b = 1; b < 3; ++b) {  // every bank at bank 0's widths and rates, its own slot count (api.zig:375-386)
+        if (int rc = validate_bank(&banks[b], banks[0].hidden)) return rc;
+        if (banks[b].inter != banks[0].inter || banks[b].n_gate != banks[0].n_gate || banks[b].n_down != banks[0].n_down)
+            return T3_BAD_EXL3_SHAPE;
+    }
+    for (int b = 0; b < 3; ++b)
+        if (banks[b].experts > 0x1000000) return T3_BAD_EXL3_SHAPE;  // a slot is 24 bits of the id
+    if (!dtype_ok(x_dtype) || !dtype_ok(y_dtype)) return T3_BAD_EXL3_DTYPE;
+    uint32_t mask;
+    if (int rc = decode_mask(dec, mask)) return rc;
+    if (!workspace || workspace_bytes < t3_moe_workspace_bytes(rows < 32 ? rows : 32, 1, &banks[0])) return T3_WORKSPACE_TOO_SMALL;
+    t3_config cfg;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        cfg = g_cfg;
+    }
+    const t3_bank* bank = &banks[0];
+    MoeArgs a = {};
+    a.x_dt = x_dtype;
+    a.gate_t = static_cast<const uint8_t*>(bank->gate.trellis);
+    a.up_t = static_cast<const uint8_t*>(bank->up.trellis);
+    a.down_t = static_cast<const uint8_t*>(bank->down.trellis);
+    a.gate_suh = bank->gate.suh;
+    a.gate_svh = bank->gate.svh;
+    a.up_suh = bank->up.suh;
+    a.up_svh = bank->up.svh;
+    a.down_suh = bank->down.suh;
+    a.down_svh = bank->down.svh;
+    a.experts = (uint32_t)bank->experts;
+    for (int b = 1; b < 3; ++b) {
+        BankTab& t = a.ext[b - 1];
+        t.gate_t = static_cast<const uint8_t*>(banks[b].gate.trellis);
+        t.up_t = static_cast<const uint8_t*>(banks[b].up.trellis);
+        t.down_t = static_cast<const uint8_t*>(banks[b].down.trellis);
+        t.gate_suh = banks[b].gate.suh;
+        t.gate_svh = banks[b].gate.svh;
+        t.up_suh = banks[b].up.suh;
+        t.up_svh = banks[b].up.svh;
+        t.down_suh = banks[b].down.suh;
+        t.down_svh = banks[b].down.svh;
+        t.experts = (uint32_t)banks[b].experts;
+    }
+    a.banked = 1;
+    a.hidden = (uint32_t)bank->hidden;
+    a.inter = (uint32_t)bank->inter;
+    a.topk = 1;
+    a.n = (uint32_t)bank->n_gate;
+    a.mask = mask;
+    a.limit = (float)limit;
+    a.clamp_at = T3_CLAMP_GATE_IN;
+    a.y_dt = y_dtype;
+    a.err = dev_error_ptr();
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t xs = x_dtype == T3_F32 ? 4u : 2u, ys = y_dtype == T3_F32 ? 4u : 2u;
+    // a skipped row-slot's y row is 0 (banked.skip_id): no CTA writes it
+    if (int rc = cuda_status(cudaMemsetAsync(y, 0, rows * (size_t)a.hidden * ys, s))) return rc;
+    note_engine(0, ((uint64_t)a.hidden << 32) | a.inter, a.experts, a.n, 1u << 8);
+    // an id may name one slot for every row-slot of the call, and a pass over a slot's weights serves 32: two calls past 32
+    for (size_t r0 = 0; r0 < rows; r0 += 32u) {
+        a.rows = (uint32_t)(rows - r0 < 32u ? rows - r0 : 32u);
+        a.x = static_cast<const uint8_t*>(x) + r0 * a.hidden * xs;
+        a.inds = static_cast<const uint32_t*>(ids) + r0;
+        a.y = static_cast<uint8_t*>(y) + r0 * a.hidden * ys;
+        if (int rc = decode_chain(a, cfg, dec.codebook, workspace, s, nullptr)) return rc;
+    }
+    return T3_OK;
 }
 
 int t3_moe_merge(const void* v, const void* scores, int scores_dtype, size_t rows, int topk, int hidden,

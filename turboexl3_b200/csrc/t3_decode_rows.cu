@@ -16,8 +16,9 @@
 #include "t3_internal.h"
 
 #ifndef T3_CB
-#error "compile with -DT3_CB=0 (MUL1) or -DT3_CB=1 (MCG)"
+#error "compile with -DT3_CB=0 (MUL1), 1 (MCG), or 2..4 (the dense linear's timing probes: see t3_lane.cuh)"
 #endif
+#define T3_SERVED (T3_CB < 2)
 
 namespace t3 {
 namespace {
@@ -139,6 +140,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) dense_gemv_kernel(const Dense
     if (traced && tid == 0) a.trace[6] = clock64();
 }
 
+#if T3_SERVED
 // ---------------------------------------------------------------------------------------------- routed experts
 
 struct Members {
@@ -146,16 +148,31 @@ struct Members {
     bool skip;
 };
 
+// A row-slot's id as the kernels use it: an expert of the bank, clamped into it; in a banked call the packed id with its
+// bank clamped to 0..2 and its slot into that bank, or kSkipId as it is.
+__device__ __forceinline__ uint32_t canon_id(const MoeArgs& a, uint32_t id) {
+    if (!a.banked) return min(id, a.experts - 1u);
+    if (id == kSkipId) return id;
+    const uint32_t bk = min(id >> 24, 2u);
+    const uint32_t cap = bk == 0u ? a.experts : (bk == 1u ? a.ext[0].experts : a.ext[1].experts);
+    return (bk << 24) | min(id & 0xFFFFFFu, cap - 1u);
+}
+
+// The arrays of the bank a canonical id names (bank 0: the call's own)
+#define T3_BANK_FIELD(a, id, f) (!(a).banked || ((id) >> 24) == 0u ? (a).f : (((id) >> 24) == 1u ? (a).ext[0].f : (a).ext[1].f))
+
 // Row-slot j's expert and every row-slot of the call on that expert, ascending, into `members`; skip = an earlier
-// row-slot already owns this expert (its CTAs do the work). All threads of the CTA must call this.
-__device__ __forceinline__ Members find_members(const uint32_t* inds, uint32_t slots, uint32_t experts, uint32_t j,
-                                                uint32_t* s_inds, uint16_t* members, uint32_t* s_count) {
-    const uint32_t tid = threadIdx.x;
-    for (uint32_t s = tid; s < slots; s += blockDim.x) s_inds[s] = min(inds[s], experts - 1u);
+// row-slot already owns this expert (its CTAs do the work), or the row-slot runs no expert. All threads of the CTA must
+// call this.
+__device__ __forceinline__ Members find_members(const MoeArgs& a, uint32_t j, uint32_t* s_inds, uint16_t* members,
+                                                uint32_t* s_count) {
+    const uint32_t tid = threadIdx.x, slots = a.rows * a.topk;
+    const uint32_t* inds = static_cast<const uint32_t*>(a.inds);
+    for (uint32_t s = tid; s < slots; s += blockDim.x) s_inds[s] = canon_id(a, inds[s]);
     __syncthreads();
     Members m;
     m.expert = s_inds[j];
-    int earlier = 0;
+    int earlier = a.banked && m.expert == kSkipId;
     for (uint32_t s = tid; s < j; s += blockDim.x) earlier |= (s_inds[s] == m.expert);
     m.skip = __syncthreads_or(earlier) != 0;
     m.count = 0;
@@ -204,10 +221,9 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_gate_up_kernel(const MoeA
     const uint32_t H = a.hidden, I = a.inter;
     pdl_wait();     // the routing (and x) may be the previous kernel's output
     pdl_trigger();  // after the wait: the down launch reads the routing ahead of its own wait
-    const Members mem = find_members(static_cast<const uint32_t*>(a.inds), a.rows * a.topk, a.experts, j, s_inds,
-                                     s_members, &s_count);
+    const Members mem = find_members(a, j, s_inds, s_members, &s_count);
     if (mem.skip) return;
-    const uint32_t e = mem.expert;
+    const uint32_t id = mem.expert, e = a.banked ? id & 0xFFFFFFu : id;
 
     uint32_t b0, b1;
     slice_blocks(H / 128u, a.split_gu, kpart, b0, b1);
@@ -220,14 +236,15 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_gate_up_kernel(const MoeA
     __syncthreads();
 
     const size_t expert_bytes = (size_t)(H / 16u) * out_tiles * tile_bytes;
-    const uint8_t* wsrc = (proj ? a.up_t : a.gate_t) + e * expert_bytes + ((size_t)(b0 * 8u) * out_tiles + ib * 8u) * tile_bytes;
-    const __half* suh = static_cast<const __half*>(proj ? a.up_suh : a.gate_suh) + (size_t)e * H;
+    const uint8_t* wsrc = (proj ? T3_BANK_FIELD(a, id, up_t) : T3_BANK_FIELD(a, id, gate_t)) + e * expert_bytes +
+                          ((size_t)(b0 * 8u) * out_tiles + ib * 8u) * tile_bytes;
+    const __half* suh = static_cast<const __half*>(proj ? T3_BANK_FIELD(a, id, up_suh) : T3_BANK_FIELD(a, id, gate_suh)) + (size_t)e * H;
     if (warp == 0) {  // the expert's scale vectors are first used behind the weight stream and the cluster barrier
         const size_t eo = (size_t)e * I + ib * 128u;
         prefetch_l2(suh + b0 * 128u, nblk * 256u, lane);
-        prefetch_l2(static_cast<const __half*>(a.gate_svh) + eo, 256u, lane);
-        prefetch_l2(static_cast<const __half*>(a.up_svh) + eo, 256u, lane);
-        prefetch_l2(static_cast<const __half*>(a.down_suh) + eo, 256u, lane);
+        prefetch_l2(static_cast<const __half*>(T3_BANK_FIELD(a, id, gate_svh)) + eo, 256u, lane);
+        prefetch_l2(static_cast<const __half*>(T3_BANK_FIELD(a, id, up_svh)) + eo, 256u, lane);
+        prefetch_l2(static_cast<const __half*>(T3_BANK_FIELD(a, id, down_suh)) + eo, 256u, lane);
     }
     const uint32_t owned = rows_owned(RM, csize);
     RingPos pos;
@@ -255,9 +272,9 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_gate_up_kernel(const MoeA
                 const uint32_t m = i * csize + rank;
                 float g[4], u[4];
                 float sg[4], su[4], sd[4];
-                load_scales(static_cast<const __half*>(a.gate_svh) + eo, lane, sg);
-                load_scales(static_cast<const __half*>(a.up_svh) + eo, lane, su);
-                load_scales(static_cast<const __half*>(a.down_suh) + eo, lane, sd);
+                load_scales(static_cast<const __half*>(T3_BANK_FIELD(a, id, gate_svh)) + eo, lane, sg);
+                load_scales(static_cast<const __half*>(T3_BANK_FIELD(a, id, up_svh)) + eo, lane, su);
+                load_scales(static_cast<const __half*>(T3_BANK_FIELD(a, id, down_suh)) + eo, lane, sd);
                 gather_owned(c.recv, owned, i, 0, 2, a.split_gu, lane, g);
                 gather_owned(c.recv, owned, i, 1, 2, a.split_gu, lane, u);
                 finish_block(g, sg, lane);
@@ -289,10 +306,9 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t H = a.hidden, I = a.inter;
     // the routing was complete before the gate|up launch started, so it can be read ahead of pdl_wait
-    const Members mem = find_members(static_cast<const uint32_t*>(a.inds), a.rows * a.topk, a.experts, j, s_inds,
-                                     s_members, &s_count);
+    const Members mem = find_members(a, j, s_inds, s_members, &s_count);
     if (mem.skip) return;
-    const uint32_t e = mem.expert;
+    const uint32_t id = mem.expert, e = a.banked ? id & 0xFFFFFFu : id;
 
     uint32_t b0, b1;
     slice_blocks(I / 128u, a.split_d, rank, b0, b1);
@@ -305,8 +321,8 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs
     __syncthreads();
 
     const size_t expert_bytes = (size_t)(I / 16u) * out_tiles * tile_bytes;
-    const uint8_t* wsrc = a.down_t + e * expert_bytes + ((size_t)(b0 * 8u) * out_tiles + hb * 8u) * tile_bytes;
-    if (warp == 0) prefetch_l2(static_cast<const __half*>(a.down_svh) + (size_t)e * H + hb * 128u, 256u, lane);
+    const uint8_t* wsrc = T3_BANK_FIELD(a, id, down_t) + e * expert_bytes + ((size_t)(b0 * 8u) * out_tiles + hb * 8u) * tile_bytes;
+    if (warp == 0) prefetch_l2(static_cast<const __half*>(T3_BANK_FIELD(a, id, down_svh)) + (size_t)e * H + hb * 128u, 256u, lane);
     const uint32_t owned = rows_owned(RM, csize);
     RingPos pos;
     for (uint32_t m0 = 0; m0 < mem.count; m0 += RM) {
@@ -339,23 +355,23 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs
             for (uint32_t i = warp; i * csize + rank < mcount; i += kConsumerWarps) {
                 const uint32_t m = i * csize + rank;
                 float v[4], sv[4];
-                load_scales(static_cast<const __half*>(a.down_svh) + (size_t)e * H + hb * 128u, lane, sv);
+                load_scales(static_cast<const __half*>(T3_BANK_FIELD(a, id, down_svh)) + (size_t)e * H + hb * 128u, lane, sv);
                 gather_owned(c.recv, owned, i, 0, 1, csize, lane, v);
                 finish_block(v, sv, lane);
                 const uint32_t slot = s_members[m0 + m];
                 if (a.topk == 1u) {
                     // One slot a row: the merge has nothing to gather, so the weighted value (and the shared-expert add)
                     // is stored here and the merge launch is skipped. The arithmetic is moe_merge_kernel's, 0 + w v included.
-                    const float w = load_act(a.scores, a.score_dt, slot);
+                    const float w = a.scores ? load_act(a.scores, a.score_dt, slot) : 1.0f;
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const size_t o = (size_t)slot * H + hb * 128u + lane + 32u * q;
                         float acc = __fadd_rn(0.0f, __fmul_rn(w, v[q]));
                         if (a.shared) {
-                            store_act(a.y, a.x_dt, o, acc);
-                            acc = __fadd_rn(load_act(a.y, a.x_dt, o), load_act(a.shared, a.x_dt, o));
+                            store_act(a.y, a.y_dt, o, acc);
+                            acc = __fadd_rn(load_act(a.y, a.y_dt, o), load_act(a.shared, a.y_dt, o));
                         }
-                        store_act(a.y, a.x_dt, o, acc);
+                        store_act(a.y, a.y_dt, o, acc);
                     }
                     continue;
                 }
@@ -389,6 +405,8 @@ __global__ void __launch_bounds__(256) moe_merge_kernel(const MoeArgs a) {
     }
     store_act(a.y, a.x_dt, o, acc);
 }
+
+#endif  // T3_SERVED
 
 // ---------------------------------------------------------------------------------------------- launch plumbing
 
@@ -437,8 +455,12 @@ cudaError_t launch_cluster(KernelFn<Args> fn, const Args& a, dim3 grid, uint32_t
     return cudaLaunchKernelEx(&cfg, fn, a);
 }
 
+#if T3_SERVED
 #define T3_PICK_RM(KERNEL, NN, rm) \
     ((rm) == 8 ? KERNEL<NN, 8> : ((rm) == 16 ? KERNEL<NN, 16> : KERNEL<NN, 32>))
+#else  // the probes exist at the 8-row capacity only
+#define T3_PICK_RM(KERNEL, NN, rm) KERNEL<NN, 8>
+#endif
 
 #define T3_PICK(KERNEL, n, rm)                                                       \
     ((n) == 16    ? T3_PICK_RM(KERNEL, 16, rm)                                        \
@@ -463,6 +485,7 @@ cudaError_t T3_CAT(launch_dense_gemv_cb, T3_CB)(const DenseArgs& a, cudaStream_t
                           a.overlap != 0, stream);
 }
 
+#if T3_SERVED
 cudaError_t T3_CAT(launch_moe_gate_up_cb, T3_CB)(const MoeArgs& a, cudaStream_t stream) {
     const uint32_t rm = a.row_cap;
     KernelFn<MoeArgs> fn = T3_PICK(moe_gate_up_kernel, a.n, rm);
@@ -477,6 +500,7 @@ cudaError_t T3_CAT(launch_moe_down_cb, T3_CB)(const MoeArgs& a, cudaStream_t str
                           gemv_smem_bytes(rm, rm, a.slice_max_d, a.split_d, a.n, a.ring_d), a.overlap != 0, stream);
 }
 
+#endif  // T3_SERVED
 #if T3_CB == 0
 cudaError_t launch_moe_merge(const MoeArgs& a, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};

@@ -4,6 +4,8 @@
 //
 // grid (out / 128, in / 16), 256 threads: warp w decodes tile (tk, 8 bx + w) from global memory in registers, the CTA
 // transposes the 16 x 128 strip through shared memory and writes whole 256-byte rows.
+#include <atomic>
+
 #include "t3_common.cuh"
 #include "t3_internal.h"
 
@@ -46,6 +48,60 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
     }
 }
 
+
+// The un-rotated weight (the reference's turboexl3_unrot_cols / turboexl3_unrot_rows, src/core/dense.zig:1587-1630 and
+// src/core/kernels/dense/unrot_cols.metal, unrot_rows.metal): W_std = diag(suh) H W_hat H diag(svh), one 128 x 128 tile at a
+// time. wt is W_hat TRANSPOSED [out, in] f16 and is overwritten in place with W_std transposed in `dt` (f16 or bf16): the
+// CTA holds its tile in shared memory as f32, runs the unscaled +-1 butterfly along the output index of every input row,
+// then along the input index of every output column (the reference's order and statement order: lane L holds elements
+// L + 32 j, five exchange stages over the lane bits, then the four-point stage), multiplies by 1/128, suh[i] and svh[o] in
+// that order in f32 and rounds once.
+// grid (in / 128, out / 128), 256 threads, 128 x 129 floats of dynamic shared memory.
+constexpr uint32_t kUnrotStride = 129;
+__global__ void __launch_bounds__(256) unrot_tile_kernel(uint16_t* wt, const __half* __restrict__ suh,
+                                                         const __half* __restrict__ svh, uint32_t in, int dt) {
+    extern __shared__ float tile[];  // tile[o][i]
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t i0 = blockIdx.x * 128u, o0 = blockIdx.y * 128u;
+    for (uint32_t e = tid; e < 128u * 64u; e += 256u) {  // two inputs a load, a row of the tile a pass of 64 threads
+        const uint32_t o = e >> 6, i = (e & 63u) * 2u;
+        const __half2 h = *reinterpret_cast<const __half2*>(reinterpret_cast<const __half*>(wt) + (size_t)(o0 + o) * in + i0 + i);
+        tile[o * kUnrotStride + i] = __low2float(h);
+        tile[o * kUnrotStride + i + 1u] = __high2float(h);
+    }
+    __syncthreads();
+    for (uint32_t i = warp; i < 128u; i += 8u) {  // along the outputs of input row i
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = tile[(lane + 32u * j) * kUnrotStride + i];
+        h128_warp(v, lane);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) tile[(lane + 32u * j) * kUnrotStride + i] = v[j];
+    }
+    __syncthreads();
+    for (uint32_t o = warp; o < 128u; o += 8u) {  // along the inputs of output column o, then scale, round, store
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = tile[o * kUnrotStride + lane + 32u * j];
+        h128_warp(v, lane);
+        const float sv = __half2float(svh[o0 + o]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t i = i0 + lane + 32u * j;
+            const float w = v[j] * 0.0078125f * __half2float(suh[i]) * sv;
+            uint16_t bits;
+            if (dt == (int)kBf16) {
+                const __nv_bfloat16 b = __float2bfloat16_rn(w);
+                bits = *reinterpret_cast<const uint16_t*>(&b);
+            } else {
+                const __half b = __float2half_rn(w);
+                bits = *reinterpret_cast<const uint16_t*>(&b);
+            }
+            wt[(size_t)(o0 + o) * in + i] = bits;
+        }
+    }
+}
+
 template <int CB>
 __global__ void codebook_table_kernel(uint32_t mask, uint16_t* out) {
     const uint32_t cw = 2u * (blockIdx.x * blockDim.x + threadIdx.x);
@@ -53,6 +109,18 @@ __global__ void codebook_table_kernel(uint32_t mask, uint16_t* out) {
     const uint32_t w = decode2<CB>(cw & mask, (cw + 1u) & mask);
     out[cw] = (uint16_t)w;
     out[cw + 1u] = (uint16_t)(w >> 16);
+}
+
+// One warp waits, with the kernels' own bounded wait, for a barrier phase that nothing completes: the wait runs out, the
+// error word gets `bit`, the kernel returns and the context stays usable (what a stalled copy would look like to the host).
+__global__ void wait_runs_out_kernel(uint32_t* err, uint32_t bit) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1u);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_wait_report(smem_addr(&bar), 0u, err, bit);
 }
 
 template <int CB>
@@ -76,6 +144,27 @@ cudaError_t launch_dequant(const uint8_t* trellis, uint32_t in, uint32_t out, ui
                            int transposed, void* what, cudaStream_t stream) {
     return codebook == kMcg ? launch_dequant_cb<kMcg>(trellis, in, out, n, mask, transposed, what, stream)
                             : launch_dequant_cb<kMul1>(trellis, in, out, n, mask, transposed, what, stream);
+}
+
+cudaError_t launch_unrot(void* w_t, const void* suh, const void* svh, uint32_t in, uint32_t out, int dt, cudaStream_t stream) {
+    const int bytes = (int)(128u * kUnrotStride * sizeof(float));
+    static std::atomic<unsigned long long> allowed{0};  // bit d: device d's kernel attribute is set
+    int dev = 0;
+    cudaError_t rc = cudaGetDevice(&dev);
+    if (rc != cudaSuccess) return rc;
+    if (dev >= 64 || !((allowed.load(std::memory_order_acquire) >> dev) & 1ull)) {
+        rc = cudaFuncSetAttribute(reinterpret_cast<const void*>(unrot_tile_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (rc != cudaSuccess) return rc;
+        if (dev < 64) allowed.fetch_or(1ull << dev, std::memory_order_release);
+    }
+    unrot_tile_kernel<<<dim3(in / 128u, out / 128u, 1), 256, bytes, stream>>>(static_cast<uint16_t*>(w_t), static_cast<const __half*>(suh),
+                                                                                static_cast<const __half*>(svh), in, dt);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_wait_runs_out(uint32_t* err, cudaStream_t stream) {
+    wait_runs_out_kernel<<<1, 32, 0, stream>>>(err, kErrFullWait);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_codebook_table(int codebook, uint32_t mask, uint16_t* out, cudaStream_t stream) {

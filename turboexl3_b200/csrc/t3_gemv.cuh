@@ -173,7 +173,9 @@ __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full
     for (uint32_t r0 = 0; r0 < nrows; r0 += kStageRows, xs += kStageRows * 16u) {
         mbar_wait_report(full0 + slot * 8u, par, err, kErrFullWait);
         const uint8_t* st = ring + slot * stage_bytes;
-        if (N > 0) {
+        if (CB == kProbeStream) {
+            // timing probe: the stage has landed, nothing reads it
+        } else if (N > 0) {
             // the stage's four tiles of this warp, two at a time: words, then decodes, then tensor-core steps, so the
             // dependent chains of two tiles overlap and the registers of four are never needed at once
 #pragma unroll

@@ -28,6 +28,14 @@ struct DenseArgs {
     unsigned long long* trace;  // optional: SM cycle counts at the phases of CTA (0, 0) (see t3_set_trace)
 };
 
+// One more bank of a banked call (an expert streamer's slot banks: the same geometry and rate, its own slot count)
+struct BankTab {
+    const uint8_t *gate_t, *up_t, *down_t;
+    const void *gate_suh, *gate_svh, *up_suh, *up_svh, *down_suh, *down_svh;
+    uint32_t experts;
+};
+constexpr uint32_t kSkipId = 0xFFFFFFFFu;  // a banked call's id for a row-slot that runs no expert
+
 // The routed chain at decode rows (rows <= 32): row-slot s = row * topk + k runs expert inds[s]
 struct MoeArgs {
     const void* x;            // [rows, hidden], dtype x_dt
@@ -45,7 +53,9 @@ struct MoeArgs {
     void* y;                  // [rows, hidden], dtype x_dt
     const void* shared;       // optional [rows, hidden] dtype x_dt added at y's rounding point, or null
     const uint32_t* row_map;  // prefill rows only: row-slot p reads x's row row_map[p] (top-1 over gathered rows), or null
-    int y_dt;                 // prefill rows only: y's dtype (the decode-row chain stores y in x_dt)
+    int y_dt;                 // y's dtype: x_dt, except for the gathered-rows and banked entries
+    uint32_t banked;          // decode rows, top-1: inds holds packed ids (bank << 24 | slot); banks 1 and 2 in ext; scores null = 1
+    BankTab ext[2];
     void* shared_ready;       // host side only: an event the last launch (the one that reads `shared`) waits for, or null
     uint32_t row_cap;                  // rows one pass over an expert's weights serves (8, 16 or 32): experts with more members take more passes
     uint32_t split_gu, slice_max_gu;   // K slices of gate|up (cluster = 2 * split_gu), largest slice
@@ -94,6 +104,13 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
 // W_hat f16 from the trellis: [in, out], or transposed [out, in]
 cudaError_t launch_dequant(const uint8_t* trellis, uint32_t in, uint32_t out, uint32_t n, uint32_t mask, int codebook,
                            int transposed, void* what, cudaStream_t stream);
+// W_hat transposed [out, in] f16 -> W_std transposed in dtype dt (f16 / bf16), in place: diag(suh) H W_hat H diag(svh)
+cudaError_t launch_unrot(void* w_t, const void* suh, const void* svh, uint32_t in, uint32_t out, int dt, cudaStream_t stream);
+// y = x W_std (x and the weight in the same 16-bit dtype, f32 accumulation, one rounding): the plain tensor-core GEMM
+cudaError_t launch_plain_linear(const void* x, int dt, uint32_t rows, const void* w_std_t, uint32_t in, uint32_t out, void* y,
+                                uint32_t* err, cudaStream_t stream);
+// test hook: a one-warp kernel whose bounded wait runs out (about a second) and sets the full-wait bit of `err`
+cudaError_t launch_wait_runs_out(uint32_t* err, cudaStream_t stream);
 // all 65,536 codewords through the kernels' decoders: out[cw] = f16 bits (test hook)
 cudaError_t launch_codebook_table(int codebook, uint32_t mask, uint16_t* out, cudaStream_t stream);
 

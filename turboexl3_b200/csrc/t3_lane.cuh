@@ -144,8 +144,14 @@ T3_HD uint32_t decode2_mcg(uint32_t cw0, uint32_t cw1) {
     return hadd2_bits(pack_lo(p0, p1), pack_hi(p0, p1));
 }
 
+// Timing probes (never a served kernel; the reference's Geometry.probe, src/core/decode.zig:34-35): a "codebook" past the
+// two real ones. kProbeNoHash skips the codebook hash (the codewords go to the tensor cores as they are), kProbeNoFunnel
+// skips the window extraction too (the raw words go), kProbeStream leaves the stage as soon as it has landed.
+constexpr int kProbeNoHash = 2, kProbeNoFunnel = 3, kProbeStream = 4;
+
 template <int CB>
 T3_HD uint32_t decode2(uint32_t cw0, uint32_t cw1) {
+    if (CB >= kProbeNoHash) return cw0 | (cw1 << 16);
     if (CB == kMcg) return decode2_mcg(cw0, cw1);
     return decode2_mul1(cw0, cw1);
 }
@@ -215,6 +221,11 @@ T3_HD void load_lane(const uint32_t* tile, const LanePlan<N>& plan, uint32_t (&r
 template <int N, int CB>
 T3_HD void decode_raw(const uint32_t (&raw)[raw_words(N)], const LanePlan<N>& plan, uint32_t mask, uint32_t (&b)[4]) {
     constexpr uint32_t kRaw = raw_words(N);
+    if (CB >= kProbeNoFunnel) {
+#pragma unroll
+        for (uint32_t j = 0; j < 4u; ++j) b[j] = raw[j < kRaw ? j : kRaw - 1u];
+        return;
+    }
     uint32_t cw[8];
     if (uniform_shift(N)) {
         constexpr uint32_t o = (win_end(N, 0) + 16u * N - 16u) & 31u;

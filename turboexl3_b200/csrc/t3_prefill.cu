@@ -85,16 +85,17 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr) {
     return d;
 }
 
-// kind::f16, f16 x f16 -> f32, both operands K-major, M = 128, N = kBN
+// kind::f16, f16 x f16 -> f32, both operands K-major, M = 128, N = kBN; kIdescBf16 switches both operands to bf16
 constexpr uint32_t kIdesc = (1u << 4) | ((kBN >> 3) << 17) | ((128u >> 4) << 24);
+constexpr uint32_t kIdescBf16 = (1u << 7) | (1u << 10);
 
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate, uint32_t idesc) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         :
-        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate)
+        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 
@@ -154,6 +155,7 @@ struct GemmArgs {
     size_t svh_stride;
     void* y;                    // [rows][N], one op
     int y_dt;
+    uint32_t ab_bf16;           // both operands are bf16 (the un-rotated trunk on bf16 activations); else f16
     uint32_t* err;
 };
 
@@ -261,6 +263,7 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
         }
     } else if (warp == 1) {
         if (lane == 0) {
+            const uint32_t idesc = kIdesc | (a.ab_bf16 ? kIdescBf16 : 0u);
             for (uint32_t ks = 0; ks < ksteps; ++ks) {
                 const uint32_t s = ks % kStages, u = ks / kStages;
                 if (!mbar_wait(&full_a[s], u & 1u)) report(a.err, kErrFullWait);
@@ -270,10 +273,10 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
 #pragma unroll
                 for (uint32_t kk = 0; kk < kBK / 16u; ++kk) {
                     const uint64_t bdesc = umma_desc(b_addr + kk * 32u);
-                    umma_f16(tmem, umma_desc(a_addr + kk * 32u), bdesc, (ks | kk) != 0u);
+                    umma_f16(tmem, umma_desc(a_addr + kk * 32u), bdesc, (ks | kk) != 0u, idesc);
 #pragma unroll
                     for (uint32_t h = 1; h < BM / 128u; ++h)
-                        umma_f16(tmem + h * 128u, umma_desc(a_addr + h * 128u * 128u + kk * 32u), bdesc, (ks | kk) != 0u);
+                        umma_f16(tmem + h * 128u, umma_desc(a_addr + h * 128u * 128u + kk * 32u), bdesc, (ks | kk) != 0u, idesc);
                 }
                 umma_commit(&empty[s]);
             }
@@ -388,15 +391,23 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
         for (uint32_t hc = 0; hc < (BM / 128u) * 2u; ++hc) {
             const uint32_t half = hc >> 1, c = (hc & 1u) * 16u;
             const int r = (int)(half * 128u + quarter * 32u + lane);
-            __half* zrow = a.z + op * a.z_op_stride + (size_t)(first + r) * a.N + nt * kBN + col0;
+            // the inner products as they are: to y in its 16-bit dtype when it is given (one rounding: the un-rotated
+            // trunk), else to z as f16
+            __half* zrow = (a.y ? static_cast<__half*>(a.y) : a.z + op * a.z_op_stride) + (size_t)(first + r) * a.N + nt * kBN + col0;
+            const bool to_bf16 = a.y != nullptr && a.y_dt == (int)kBf16;
             uint32_t v[16];
             tmem_ld16(tmem + ((quarter * 32u) << 16) + half * 128u + col0 + c, v);
             if (r < rows) {
                 uint32_t packed[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const __half2 h = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
-                    packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+                    if (to_bf16) {
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                        packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+                    } else {
+                        const __half2 h = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                        packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
                 }
                 uint4* dst = reinterpret_cast<uint4*>(zrow + c);
                 dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -797,6 +808,39 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
     if (rc != cudaSuccess) return rc;
     *launches += 2;  // the output rotation runs in the GEMM's epilogue
     return cudaGetLastError();
+}
+
+// ---- the un-rotated trunk, more than 32 rows ----------------------------------------------------------------------------
+
+// One launch: both operands by TMA as they lie in memory (x [rows, in] and W_std transposed [out, in], the same 16-bit
+// dtype), the epilogue rounds the f32 accumulators once into y (dense.residentPlain, src/core/dense.zig:1261-1263: "one
+// matmul of x against its resident W_std in x's dtype").
+cudaError_t launch_plain_linear(const void* x, int dt, uint32_t rows, const void* w_std_t, uint32_t in, uint32_t out, void* y,
+                                uint32_t* err, cudaStream_t stream) {
+    const uint32_t sms = one_wave_ctas(), ncol = out / kBN;
+    uint32_t bm = 512u, best = ~0u;
+    for (uint32_t cand : {512u, 256u, 128u}) {
+        const uint32_t ctas = ((rows + cand - 1u) / cand) * ncol;
+        const uint32_t cost = cand == 128u ? (ctas <= sms ? 256u : ((ctas + 2u * sms - 1u) / (2u * sms)) * 512u)
+                                           : ((ctas + sms - 1u) / sms) * (cand + 128u);
+        if (cost < best) best = cost, bm = cand;
+    }
+    CUtensorMap map_a, map_b;
+    if (!make_a_map(&map_a, x, rows, in, bm == 128u ? 128u : 256u)) return cudaErrorNotSupported;
+    if (!make_a_map(&map_b, w_std_t, out, in, kBN)) return cudaErrorNotSupported;
+    GemmArgs g = {};
+    g.K = in;
+    g.N = out;
+    g.ops = 1;
+    g.dense_rows = rows;
+    g.y = y;
+    g.y_dt = dt;
+    g.ab_bf16 = dt == (int)kBf16;
+    g.err = err;
+    const uint32_t tiles = (rows + bm - 1u) / bm;
+    return bm == 512u   ? launch_gemm_resident<512>(map_a, map_b, g, tiles, stream)
+           : bm == 256u ? launch_gemm_resident<256>(map_a, map_b, g, tiles, stream)
+                        : launch_gemm_resident<128>(map_a, map_b, g, tiles, stream);
 }
 
 // ---- routed experts, more than 32 rows --------------------------------------------------------------------------------
