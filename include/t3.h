@@ -182,6 +182,24 @@ int t3_moe_with_shared_after(const void* x, int x_dtype, size_t rows, const t3_b
  * (the reference's per-slot outputs that a caller combines: src/kernels/hip/decode/decode.hip:11-13). */
 int t3_moe_merge(const void* v, const void* scores, int scores_dtype, size_t rows, int topk, int hidden,
                  const void* shared, void* y, int y_dtype, void* stream);
+/* t3_moe_merge on v rows that lie in another order: slot s's row is v[where[s]] (where u32 [rows * topk]; an
+ * expert-parallel combine returns the rows grouped by owning rank, and t3_ep_plan's `where` says which is which). The
+ * sum still runs in slot order, so y is t3_moe_merge's bit for bit. */
+int t3_moe_merge_mapped(const void* v, const void* where, const void* scores, int scores_dtype, size_t rows, int topk,
+                        int hidden, const void* shared, void* y, int y_dtype, void* stream);
+
+/* Expert-parallel dispatch plan of one rank's routing, on the device (no counterpart in the reference, which serves one
+ * device; the split is by experts, expert e on rank e / (experts / world)). inds u32 / i32 [rows, topk] holds GLOBAL expert
+ * ids. All outputs are grouped by destination rank in rank order, ascending slot inside a rank (slot = row * topk + k):
+ *   order u32 [S]      the slot sent at position p          where u32 [S]   slot s's position (order's inverse)
+ *   send_rows u32 [S]  the rows to send, each (rank, row) pair ONCE, rows ascending inside a rank (the first
+ *                      counts[1][*] summed entries are used)
+ *   meta i32 [S, 2]    per sent slot: its row as an index into its rank's group of rows, its expert's index on the owner
+ *   counts i32 [2, world]  slots to each rank, rows to each rank — the one array the host has to read
+ * world 1..T3_EP_WORLD_MAX, experts a multiple of world; one launch. */
+#define T3_EP_WORLD_MAX 8
+int t3_ep_plan(const void* inds, size_t rows, int topk, int experts, int world, void* order, void* where, void* send_rows,
+               void* meta, void* counts, void* stream);
 
 /* t3_moe without a workspace argument, for callers that cannot allocate device memory (a host whose memory pool owns the
  * whole GPU, a plugin that is only handed activations and weights). It has no counterpart in the reference, which

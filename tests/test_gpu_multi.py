@@ -58,6 +58,14 @@ def _worker(rank: int, world: int, port: int, fail):
             whole = t3.linear(x, dev(trellis), dev(suh), dev(svh))
             # a rank computes whole output columns with the unsharded K split: the same bytes as the single-GPU call
             assert torch.equal(y.view(torch.int16), whole.view(torch.int16)), f"rank {rank} rows {rows}: column shards differ"
+            # left sharded (no collective) and gathered as stacked shards: the same columns
+            b0, b1 = par.column_blocks(out_dim, rank, world)
+            mine = par.column_sharded_linear(x, t_sh, dev(suh), svh_sh, out_dim, t3.Decode.mul1, gather="none")
+            assert torch.equal(mine, whole[:, b0 * 128:b1 * 128])
+            stacked = par.column_sharded_linear(x, t_sh, dev(suh), svh_sh, out_dim, t3.Decode.mul1, gather="stacked")
+            for r in range(world):
+                c0, c1 = par.column_blocks(out_dim, r, world)
+                assert torch.equal(stacked[r][:, :(c1 - c0) * 128], whole[:, c0 * 128:c1 * 128])
         assert t3.device_error() == 0
         dist.barrier()
         dist.destroy_process_group()

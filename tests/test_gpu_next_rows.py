@@ -141,3 +141,59 @@ def test_banked_refusals():
     other = make_bank(53, 2, H, 256, n)[0]
     with pytest.raises(t3.Exl3Error, match="BadExl3Shape"):
         t3.moe_clamped_banked(x, [banks[0], other, banks[2]], ids)
+
+
+@pytest.mark.parametrize("rows,experts,topk", [(1200, 4, 2), (900, 3, 1), (2000, 16, 4)])
+def test_routed_prefill_tiles_of_every_height(rows, experts, topk):
+    """Experts with more rows than one 128-row tile holds take 256- and 512-row tiles (one decode of the expert's weights
+    a tile): a skewed routing puts 1..1000+ rows on an expert, so every height and every remainder rule is met, and each
+    row's bytes stay those of the oracle's ref.moeRow."""
+    H, I, n = 256, 128, 32
+    bank, obank = make_bank(60 + experts, experts, H, I, n)
+    rng = np.random.default_rng(61 + rows)
+    # skewed: expert 0 takes about half of all slots
+    p = np.array([0.5] + [0.5 / (experts - 1)] * (experts - 1))
+    inds = np.stack([rng.choice(experts, size=topk, replace=False, p=p) for _ in range(rows)]).astype(np.int32)
+    scores = rng.random((rows, topk), dtype=np.float32)
+    scores /= scores.sum(1, keepdims=True)
+    x16 = synth.activations(62, rows, H)
+    y = t3.moe(dev(x16).view(1, rows, H), bank, dev(inds).view(1, rows, topk), dev(scores).view(1, rows, topk))
+    counts = np.bincount(inds.reshape(-1), minlength=experts)
+    assert counts.max() > 384 and counts.min() >= 1, counts
+    ref = ob.moe_rows(obank, x16.astype(np.float32), inds, scores)
+    # a maximum over 10^5..10^6 outputs that sum several f16-rounded terms: 1.5 x the bars, as for the full-size layer
+    # outputs (achieved at 1200 rows, 4 experts, top-2: compare 6.5e-3, rounded 5.0e-3)
+    check_moe(host_f32(y).reshape(rows, H), ref, "f16", f"tile_heights_rows{rows}_e{experts}_k{topk}", terms=1.5)
+    assert t3.device_error() == 0
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("rows,topk,experts", [(777, 6, 64), (5, 3, 16), (4096, 10, 512)])
+def test_device_dispatch_plan_is_the_host_plan(world, rows, topk, experts):
+    """t3_ep_plan (one launch) against parallel.plan_dispatch (torch ops on the host): the same grouping by owning rank,
+    the same order inside a rank, each token row once a rank."""
+    from turboexl3_b200 import parallel as par
+    rng = np.random.default_rng(70 + world + rows)
+    inds = np.stack([rng.choice(experts, size=topk, replace=False) for _ in range(rows)]).astype(np.int32)
+    order, where, send_rows, meta, counts = t3.ep_plan(dev(inds), experts, world)
+    plan = par.plan_dispatch(torch.from_numpy(inds), experts, world)
+    c = counts.cpu().tolist()
+    assert c[0] == plan.send_counts and c[1] == plan.row_counts
+    S = rows * topk
+    assert torch.equal(order.cpu().long(), plan.order)
+    assert torch.equal(where.cpu().long()[plan.order], torch.arange(S))
+    assert torch.equal(send_rows.cpu().long()[:sum(c[1])], plan.send_rows)
+    assert torch.equal(meta.cpu()[:, 0], plan.row_in_group) and torch.equal(meta.cpu()[:, 1], plan.local_expert)
+
+
+def test_mapped_merge_is_the_merge():
+    rows, topk, H = 37, 5, 384
+    rng = np.random.default_rng(80)
+    v = torch.from_numpy(rng.standard_normal((rows * topk, H)).astype(np.float16)).cuda()
+    scores = torch.from_numpy(rng.random((rows, topk), dtype=np.float32)).cuda()
+    perm = torch.from_numpy(rng.permutation(rows * topk).astype(np.int32)).cuda()  # slot s lies at row perm[s]
+    moved = torch.empty_like(v)
+    moved[perm.long()] = v
+    y0 = t3.moe_merge(v.view(rows, topk, H), scores, torch.float16)
+    y1 = t3.moe_merge(moved, scores, torch.float16, where=perm)
+    assert torch.equal(y0, y1)

@@ -81,6 +81,8 @@ SYMBOLS = {
     "t3_moe_swiglu_rows": (_i, [_vp, _i, _sz, _vp, _sz, C.POINTER(_Bank), _vp, _vp, _i, _Decode, _i, _i, _vp, _i, _vp, _sz, _vp]),
     "t3_moe_with_shared_after": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp, _vp, _vp, _sz, _vp]),
     "t3_moe_merge": (_i, [_vp, _vp, _i, _sz, _i, _i, _vp, _vp, _i, _vp]),
+    "t3_moe_merge_mapped": (_i, [_vp, _vp, _vp, _i, _sz, _i, _i, _vp, _vp, _i, _vp]),
+    "t3_ep_plan": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "t3_moe_noalloc": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _vp, _i, _i, _Decode, _vp, _vp]),
     "t3_set_trace": (None, [_vp]),
     "t3_launch_count": (C.c_uint64, []),
@@ -437,17 +439,44 @@ def linear_unrot(x: torch.Tensor, w_std_t: torch.Tensor) -> torch.Tensor:
     return y
 
 
-def moe_merge(v: torch.Tensor, scores: torch.Tensor, out_dtype: torch.dtype, shared=None) -> torch.Tensor:
-    """The routed chain's last step (t3_moe_merge): v f16 [rows, topk, hidden], scores [rows, topk]; y [rows, hidden]."""
+def moe_merge(v: torch.Tensor, scores: torch.Tensor, out_dtype: torch.dtype, shared=None, where=None) -> torch.Tensor:
+    """The routed chain's last step (t3_moe_merge / t3_moe_merge_mapped): v f16 [rows, topk, hidden] (with `where`, u32/i32
+    [rows * topk]: v [rows * topk, hidden] in any order, slot s's row at v[where[s]]), scores [rows, topk]; y [rows, hidden]."""
     _need_cuda(v, scores)
-    if v.dim() != 3 or v.dtype != torch.float16 or tuple(scores.shape) != tuple(v.shape[:2]):
+    rows, topk = scores.shape
+    hidden = v.shape[-1]
+    if v.dtype != torch.float16 or not v.is_contiguous() or v.numel() != rows * topk * hidden:
         raise Exl3Error(1, "BadExl3Shape")
-    rows, topk, hidden = v.shape
+    if where is not None and (where.numel() != rows * topk or where.dtype not in (torch.int32, torch.uint32)):
+        raise Exl3Error(1, "BadExl3Shape")
     y = torch.empty((rows, hidden), dtype=out_dtype, device=v.device)
-    _check(lib().t3_moe_merge(v.data_ptr(), scores.data_ptr(), _DTYPES[scores.dtype], rows, topk, hidden,
-                              shared.data_ptr() if shared is not None else None, y.data_ptr(), _DTYPES[out_dtype],
-                              _stream_ptr(v)))
+    _check(lib().t3_moe_merge_mapped(v.data_ptr(), where.data_ptr() if where is not None else None, scores.data_ptr(),
+                                     _DTYPES[scores.dtype], rows, topk, hidden,
+                                     shared.data_ptr() if shared is not None else None, y.data_ptr(), _DTYPES[out_dtype],
+                                     _stream_ptr(v)))
     return y
+
+
+EP_WORLD_MAX = 8
+
+
+def ep_plan(inds: torch.Tensor, experts: int, world: int):
+    """t3_ep_plan: (order, where, send_rows, meta, counts) for inds [rows, topk] of global expert ids; device tensors, no
+    host read."""
+    _need_cuda(inds)
+    if inds.dim() != 2 or inds.dtype not in (torch.int32, torch.uint32) or not inds.is_contiguous():
+        raise Exl3Error(1, "BadExl3Shape")
+    rows, topk = inds.shape
+    S = rows * topk
+    dev = inds.device
+    order = torch.empty(S, dtype=torch.int32, device=dev)
+    where = torch.empty(S, dtype=torch.int32, device=dev)
+    send_rows = torch.empty(S, dtype=torch.int32, device=dev)
+    meta = torch.empty((S, 2), dtype=torch.int32, device=dev)
+    counts = torch.empty((2, world), dtype=torch.int32, device=dev)
+    _check(lib().t3_ep_plan(inds.data_ptr(), rows, topk, experts, world, order.data_ptr(), where.data_ptr(), send_rows.data_ptr(),
+                            meta.data_ptr(), counts.data_ptr(), _stream_ptr(inds)))
+    return order, where, send_rows, meta, counts
 
 
 def moe_swiglu(x, bank: Bank, inds, scores, dec: Decode, limit: int, clamp_at: int = CLAMP_GATE_IN) -> torch.Tensor:

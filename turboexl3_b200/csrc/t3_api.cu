@@ -713,14 +713,36 @@ int t3_moe_clamped_banked(const void* x, int x_dtype, size_t rows, const t3_bank
     return T3_OK;
 }
 
+int t3_ep_plan(const void* inds, size_t rows, int topk, int experts, int world, void* order, void* where, void* send_rows,
+               void* meta, void* counts, void* stream) {
+    if (!inds || !order || !where || !send_rows || !meta || !counts) return T3_NULL_POINTER;
+    if (rows < 1 || topk <= 0 || topk > T3_REDUCE_MAX_TOPK || rows * (size_t)topk > 0x7FFFFFFFu || experts <= 0 || world < 1 ||
+        world > T3_EP_WORLD_MAX || experts % world != 0)
+        return T3_BAD_EXL3_SHAPE;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cuda_status(launch_ep_plan(static_cast<const uint32_t*>(inds), (uint32_t)rows, (uint32_t)topk, (uint32_t)experts,
+                                      (uint32_t)world, static_cast<uint32_t*>(order), static_cast<uint32_t*>(where),
+                                      static_cast<uint32_t*>(send_rows), meta, static_cast<int*>(counts),
+                                      static_cast<cudaStream_t>(stream)));
+}
+
+int t3_moe_merge_mapped(const void* v, const void* where, const void* scores, int scores_dtype, size_t rows, int topk, int hidden,
+                        const void* shared, void* y, int y_dtype, void* stream);
+
 int t3_moe_merge(const void* v, const void* scores, int scores_dtype, size_t rows, int topk, int hidden,
                  const void* shared, void* y, int y_dtype, void* stream) {
+    return t3_moe_merge_mapped(v, nullptr, scores, scores_dtype, rows, topk, hidden, shared, y, y_dtype, stream);
+}
+
+int t3_moe_merge_mapped(const void* v, const void* where, const void* scores, int scores_dtype, size_t rows, int topk, int hidden,
+                        const void* shared, void* y, int y_dtype, void* stream) {
     if (!v || !scores || !y) return T3_NULL_POINTER;
     if (rows < 1 || rows > 0x7FFFFFFFu / 32u || topk <= 0 || topk > T3_REDUCE_MAX_TOPK || hidden <= 0) return T3_BAD_EXL3_SHAPE;
     if (rows > 65535u) return T3_BAD_EXL3_SHAPE;  // one grid row a row
     if (!dtype_ok(scores_dtype) || !dtype_ok(y_dtype)) return T3_BAD_EXL3_DTYPE;
     MoeArgs a = {};
     a.v = const_cast<void*>(v);
+    a.row_map = static_cast<const uint32_t*>(where);
     a.scores = scores;
     a.score_dt = scores_dtype;
     a.rows = (uint32_t)rows;

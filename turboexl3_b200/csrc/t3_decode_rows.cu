@@ -396,7 +396,8 @@ __global__ void __launch_bounds__(256) moe_merge_kernel(const MoeArgs a) {
     for (uint32_t k = 0; k < a.topk; ++k) {
         const size_t s = (size_t)row * a.topk + k;
         const float w = load_act(a.scores, a.score_dt, s);
-        acc = __fadd_rn(acc, __fmul_rn(w, __half2float(static_cast<const __half*>(a.v)[s * a.hidden + i])));
+        const size_t at = a.row_map ? a.row_map[s] : s;  // where slot s's v row lies (an expert-parallel combine's order)
+        acc = __fadd_rn(acc, __fmul_rn(w, __half2float(static_cast<const __half*>(a.v)[at * a.hidden + i])));
     }
     const size_t o = (size_t)row * a.hidden + i;
     if (a.shared) {

@@ -102,6 +102,107 @@ __global__ void __launch_bounds__(256) unrot_tile_kernel(uint16_t* wt, const __h
     }
 }
 
+
+// ---- expert-parallel dispatch plan ---------------------------------------------------------------------------------
+// One CTA of 1024 threads. Slot s = row * topk + k goes to rank d = expert / per (clamped). Outputs, all grouped by
+// destination rank in rank order, stable (ascending slot inside a rank):
+//   order[p]      the slot sent at position p;          where[s]  the position of slot s (order's inverse)
+//   meta[p]       (the slot's row as an index into its destination's group of rows, the expert's index on its owner)
+//   send_rows[q]  the rows to send: each (destination, row) pair once, rows ascending inside a destination
+//   counts[0][d]  slots to rank d;                       counts[1][d]  rows to rank d
+// Thread t owns a run of consecutive rows; two passes over them with a block-wide exclusive scan of the per-rank counts
+// between (world <= kEpWorldMax so the counters stay in registers).
+constexpr uint32_t kEpWorldMax = 8;
+struct EpPlanArgs {
+    const uint32_t* inds;
+    uint32_t rows, topk, per, world;
+    uint32_t *order, *where, *send_rows;
+    int2* meta;
+    int* counts;  // [2][world]
+};
+__global__ void __launch_bounds__(1024) ep_plan_kernel(const EpPlanArgs a) {
+    __shared__ uint32_t s_warp[2][kEpWorldMax][32];
+    __shared__ uint32_t s_total[2][kEpWorldMax], s_base[2][kEpWorldMax];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t chunk = (a.rows + 1023u) / 1024u;
+    const uint32_t r0 = min(tid * chunk, a.rows), r1 = min(r0 + chunk, a.rows);
+    uint32_t cs[kEpWorldMax], cr[kEpWorldMax];
+#pragma unroll
+    for (uint32_t d = 0; d < kEpWorldMax; ++d) cs[d] = cr[d] = 0u;
+    for (uint32_t r = r0; r < r1; ++r) {
+        uint32_t seen = 0u;
+        for (uint32_t k = 0; k < a.topk; ++k) {
+            const uint32_t d = min(a.inds[(size_t)r * a.topk + k] / a.per, a.world - 1u);
+            seen |= 1u << d;
+#pragma unroll
+            for (uint32_t q = 0; q < kEpWorldMax; ++q) cs[q] += (q == d);
+        }
+#pragma unroll
+        for (uint32_t q = 0; q < kEpWorldMax; ++q) cr[q] += (seen >> q) & 1u;
+    }
+    // exclusive scan over the threads, per rank, of both counters
+    uint32_t bs[kEpWorldMax], br[kEpWorldMax];
+#pragma unroll
+    for (uint32_t d = 0; d < kEpWorldMax; ++d) {
+        uint32_t vs = cs[d], vr = cr[d];
+#pragma unroll
+        for (uint32_t off = 1; off < 32u; off <<= 1) {
+            const uint32_t ps = __shfl_up_sync(0xFFFFFFFFu, vs, off), pr = __shfl_up_sync(0xFFFFFFFFu, vr, off);
+            if (lane >= off) vs += ps, vr += pr;
+        }
+        if (lane == 31u) s_warp[0][d][warp] = vs, s_warp[1][d][warp] = vr;
+        bs[d] = vs - cs[d];
+        br[d] = vr - cr[d];
+    }
+    __syncthreads();
+    if (warp < 2u * kEpWorldMax) {  // warp w scans the 32 warp totals of counter w / 8, rank w % 8
+        const uint32_t which = warp / kEpWorldMax, d = warp % kEpWorldMax;
+        const uint32_t own = s_warp[which][d][lane];
+        uint32_t v = own;
+#pragma unroll
+        for (uint32_t off = 1; off < 32u; off <<= 1) {
+            const uint32_t p = __shfl_up_sync(0xFFFFFFFFu, v, off);
+            if (lane >= off) v += p;
+        }
+        s_warp[which][d][lane] = v - own;
+        if (lane == 31u) s_total[which][d] = v;
+    }
+    __syncthreads();
+    if (tid < 2u) {  // where each rank's group starts
+        uint32_t run = 0;
+        for (uint32_t d = 0; d < kEpWorldMax; ++d) {
+            s_base[tid][d] = run;
+            run += s_total[tid][d];
+        }
+    }
+    if (tid < 2u * a.world) a.counts[tid] = (int)s_total[tid / a.world][tid % a.world];
+    __syncthreads();
+#pragma unroll
+    for (uint32_t d = 0; d < kEpWorldMax; ++d) {
+        bs[d] += s_warp[0][d][warp];  // now: slots of rank d ahead of this thread's
+        br[d] += s_warp[1][d][warp];  // rows of rank d ahead of this thread's
+    }
+    for (uint32_t r = r0; r < r1; ++r) {
+        uint32_t seen = 0u;
+        for (uint32_t k = 0; k < a.topk; ++k) {
+            const uint32_t s = r * a.topk + k, e = a.inds[s];
+            const uint32_t d = min(e / a.per, a.world - 1u);
+            uint32_t at = 0, grp = 0;
+#pragma unroll
+            for (uint32_t q = 0; q < kEpWorldMax; ++q)
+                if (q == d) at = bs[q]++, grp = br[q];
+            const uint32_t p = s_base[0][d] + at;
+            a.order[p] = s;
+            a.where[s] = p;
+            a.meta[p] = make_int2((int)grp, (int)(min(e, a.per * a.world - 1u) - d * a.per));
+            if (!((seen >> d) & 1u)) a.send_rows[s_base[1][d] + grp] = r;
+            seen |= 1u << d;
+        }
+#pragma unroll
+        for (uint32_t q = 0; q < kEpWorldMax; ++q) br[q] += (seen >> q) & 1u;
+    }
+}
+
 template <int CB>
 __global__ void codebook_table_kernel(uint32_t mask, uint16_t* out) {
     const uint32_t cw = 2u * (blockIdx.x * blockDim.x + threadIdx.x);
@@ -159,6 +260,14 @@ cudaError_t launch_unrot(void* w_t, const void* suh, const void* svh, uint32_t i
     }
     unrot_tile_kernel<<<dim3(in / 128u, out / 128u, 1), 256, bytes, stream>>>(static_cast<uint16_t*>(w_t), static_cast<const __half*>(suh),
                                                                                 static_cast<const __half*>(svh), in, dt);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_ep_plan(const uint32_t* inds, uint32_t rows, uint32_t topk, uint32_t experts, uint32_t world, uint32_t* order,
+                           uint32_t* where, uint32_t* send_rows, void* meta, int* counts, cudaStream_t stream) {
+    if (world < 1u || world > kEpWorldMax || experts % world != 0u) return cudaErrorInvalidValue;
+    const EpPlanArgs a = {inds, rows, topk, experts / world, world, order, where, send_rows, static_cast<int2*>(meta), counts};
+    ep_plan_kernel<<<1, 1024, 0, stream>>>(a);
     return cudaGetLastError();
 }
 

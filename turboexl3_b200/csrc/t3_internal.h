@@ -109,6 +109,9 @@ cudaError_t launch_unrot(void* w_t, const void* suh, const void* svh, uint32_t i
 // y = x W_std (x and the weight in the same 16-bit dtype, f32 accumulation, one rounding): the plain tensor-core GEMM
 cudaError_t launch_plain_linear(const void* x, int dt, uint32_t rows, const void* w_std_t, uint32_t in, uint32_t out, void* y,
                                 uint32_t* err, cudaStream_t stream);
+// the expert-parallel dispatch plan of one rank's routing (see ep_plan_kernel); world 1..8, experts a multiple of world
+cudaError_t launch_ep_plan(const uint32_t* inds, uint32_t rows, uint32_t topk, uint32_t experts, uint32_t world, uint32_t* order,
+                           uint32_t* where, uint32_t* send_rows, void* meta, int* counts, cudaStream_t stream);
 // test hook: a one-warp kernel whose bounded wait runs out (about a second) and sets the full-wait bit of `err`
 cudaError_t launch_wait_runs_out(uint32_t* err, cudaStream_t stream);
 // all 65,536 codewords through the kernels' decoders: out[cw] = f16 bits (test hook)

@@ -35,16 +35,20 @@ constexpr uint32_t kMaxCodeStages = 8;  // stages of the code ring that feeds th
 // MMAs outlast its decode and the kernel is bound by the tensor pipe; two operand stages; large dense calls), 256 rows
 // (two accumulators, three stages; smaller dense calls) and 128 rows (half the shared memory and a quarter of tensor
 // memory, so two CTAs fit a multiprocessor: routed experts, whose tiles are mostly part-full and whose cost is the decode).
-template <int BM>
+// PAIR: 256-row tiles of the routed experts, two CTAs a multiprocessor (two operand stages each, half of tensor memory
+// each): a routed tile's cost is its decode, and two CTAs' decode warps keep the multiprocessor's issue slots as busy as two
+// 128-row CTAs would, on half the decodes.
+template <int BM, bool PAIR = false>
 struct Tile {
     static_assert(BM == 128 || BM == 256 || BM == 512, "tile height");
+    static_assert(!PAIR || BM == 256, "only 256-row tiles come in the paired form");
     static constexpr uint32_t kABytes = BM * kBK * 2u;
     static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-    static constexpr uint32_t kStages = BM == 512 ? 2u : 3u;
+    static constexpr uint32_t kStages = (BM == 512 || PAIR) ? 2u : 3u;
     static constexpr uint32_t kBoxRows = BM % 256u == 0u ? 256u : 128u;  // rows of one TMA box of the activation tile
-    static constexpr uint32_t kCodeStages = BM == 256 ? 6u : (BM == 512 ? 4u : 3u);
+    static constexpr uint32_t kCodeStages = PAIR ? 3u : (BM == 256 ? 6u : (BM == 512 ? 4u : 3u));
     static constexpr uint32_t kTmemCols = BM;  // 128 f32 columns an accumulator
-    static constexpr int kMinBlocks = BM == 128 ? 2 : 1;
+    static constexpr int kMinBlocks = (BM == 128 || PAIR) ? 2 : 1;
     // dynamic shared memory: operand stages, the code ring (4 tile rows of 16 n bytes a stage), barriers, alignment slack
     static constexpr uint32_t smem(uint32_t n) { return kStages * kStageBytes + kCodeStages * 64u * n + 1024u + 512u; }
 };
@@ -160,10 +164,10 @@ struct GemmArgs {
 };
 
 // RES: the B operand is a kept W_hat (transposed, [N, K] f16) loaded by TMA like A; nothing is decoded.
-template <int NN, int CB, int BM, bool RES = false>
-__global__ void __launch_bounds__(kGemmThreads, Tile<BM>::kMinBlocks)
+template <int NN, int CB, int BM, bool RES = false, bool PAIR = false>
+__global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
     gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs a) {
-    using T = Tile<BM>;
+    using T = Tile<BM, PAIR>;
     constexpr uint32_t kStages = T::kStages, kStageBytes = T::kStageBytes, kABytes = T::kABytes;
     int e = 0, first = 0, rows = 0;
     if (a.tiles) {
@@ -430,43 +434,92 @@ __global__ void route_count_kernel(const uint32_t* inds, uint32_t slots, uint32_
     if (s < slots) atomicAdd(&counts[min(inds[s], experts - 1u)], 1u);
 }
 
-// one CTA: each expert's first sorted position (exclusive scan of the counts) into `cursor`, and the M-tile table
+// How an expert's c rows are cut into M tiles: 512-row tiles while more than 384 rows are left, then one 256-row tile
+// (and a 128-row one for what is past 256), or one 128-row tile. A tile decodes its expert's weights once whatever its
+// height, and the decode is what a routed GEMM costs, so an expert's rows go into as few tiles as the accumulators hold
+// (the reference sizes its tiles by the expert's row count for the same reason, src/core/kernels/prefill/table_2.metal).
+struct TileCut {
+    uint32_t n512, n256, n128;
+};
+__host__ __device__ inline TileCut cut_rows(uint32_t c, bool uniform) {
+    TileCut t = {0u, 0u, 0u};
+    if (uniform) {  // 128-row tiles only
+        t.n128 = (c + 127u) / 128u;
+        return t;
+    }
+    while (c > 384u) {
+        ++t.n512;
+        c -= c < 512u ? c : 512u;
+    }
+    if (c > 256u) t.n256 = 1u, t.n128 = 1u;
+    else if (c > 128u) t.n256 = 1u;
+    else if (c > 0u) t.n128 = 1u;
+    return t;
+}
+
+// Tile tables by height: (expert, first row, rows, 0) each; a table's unused tail is zero rows
+struct TileTables {
+    int4* t[3];       // 512-, 256-, 128-row tiles
+    uint32_t max[3];
+    uint32_t uniform;  // 1: every tile is a 128-row tile (calls with few rows an expert: one launch a GEMM instead of three)
+};
+
+// one CTA: each expert's first sorted position (exclusive scan of the counts) into `cursor`, and the M-tile tables
 __global__ void __launch_bounds__(1024) route_plan_kernel(const uint32_t* counts, uint32_t experts, uint32_t* cursor,
-                                                          int4* tiles, uint32_t max_tiles, uint32_t bm) {
-    __shared__ uint32_t s_pos[1024], s_tile[1024];
+                                                          const TileTables tt) {
+    __shared__ uint32_t s_scan[4][1024];
+    __shared__ uint32_t base[4];
     const uint32_t tid = threadIdx.x;
-    // experts are walked in chunks of 1024 with running bases
-    __shared__ uint32_t base_pos, base_tile;
-    if (tid == 0) base_pos = base_tile = 0;
+    if (tid < 4u) base[tid] = 0;
     __syncthreads();
+    // experts are walked in chunks of 1024 with running bases
     for (uint32_t e0 = 0; e0 < experts; e0 += 1024u) {
         const uint32_t e = e0 + tid;
         const uint32_t c = e < experts ? counts[e] : 0u;
-        const uint32_t t = (c + bm - 1u) / bm;
-        s_pos[tid] = c;
-        s_tile[tid] = t;
+        const TileCut cut = cut_rows(c, tt.uniform != 0u);
+        const uint32_t mine[4] = {c, cut.n512, cut.n256, cut.n128};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) s_scan[k][tid] = mine[k];
         __syncthreads();
-        for (uint32_t off = 1; off < 1024u; off <<= 1) {  // inclusive Hillis-Steele scan
-            const uint32_t p = tid >= off ? s_pos[tid - off] : 0u, tt = tid >= off ? s_tile[tid - off] : 0u;
+        for (uint32_t off = 1; off < 1024u; off <<= 1) {  // inclusive Hillis-Steele scans
+            uint32_t add[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) add[k] = tid >= off ? s_scan[k][tid - off] : 0u;
             __syncthreads();
-            s_pos[tid] += p;
-            s_tile[tid] += tt;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) s_scan[k][tid] += add[k];
             __syncthreads();
         }
-        const uint32_t pos0 = base_pos + s_pos[tid] - c, tile0 = base_tile + s_tile[tid] - t;
         if (e < experts) {
+            const uint32_t pos0 = base[0] + s_scan[0][tid] - c;
             cursor[e] = pos0;
-            for (uint32_t i = 0; i < t && tile0 + i < max_tiles; ++i)
-                tiles[tile0 + i] = make_int4((int)e, (int)(pos0 + i * bm), (int)min(bm, c - i * bm), 0);
+            uint32_t at[3];
+#pragma unroll
+            for (int k = 0; k < 3; ++k) at[k] = base[k + 1] + s_scan[k + 1][tid] - mine[k + 1];
+            uint32_t first = pos0, left = c;
+            for (uint32_t i = 0; i < cut.n512; ++i) {
+                const uint32_t r = left < 512u ? left : 512u;
+                if (at[0] + i < tt.max[0]) tt.t[0][at[0] + i] = make_int4((int)e, (int)first, (int)r, 0);
+                first += r, left -= r;
+            }
+            if (cut.n256) {
+                const uint32_t r = left < 256u ? left : 256u;
+                if (at[1] < tt.max[1]) tt.t[1][at[1]] = make_int4((int)e, (int)first, (int)r, 0);
+                first += r, left -= r;
+            }
+            for (uint32_t i = 0; i < cut.n128; ++i) {
+                const uint32_t r = left < 128u ? left : 128u;
+                if (at[2] + i < tt.max[2]) tt.t[2][at[2] + i] = make_int4((int)e, (int)first, (int)r, 0);
+                first += r, left -= r;
+            }
         }
         __syncthreads();
-        if (tid == 1023u) {
-            base_pos += s_pos[1023];
-            base_tile += s_tile[1023];
-        }
+        if (tid < 4u) base[tid] += s_scan[tid][1023];
         __syncthreads();
     }
-    for (uint32_t i = base_tile + tid; i < max_tiles; i += 1024u) tiles[i] = make_int4(0, 0, 0, 0);
+#pragma unroll
+    for (int k = 0; k < 3; ++k)
+        for (uint32_t i = base[k + 1] + tid; i < tt.max[k]; i += 1024u) tt.t[k][i] = make_int4(0, 0, 0, 0);
 }
 
 __global__ void route_scatter_kernel(const uint32_t* inds, uint32_t slots, uint32_t experts, uint32_t* cursor,
@@ -701,30 +754,33 @@ cudaError_t launch_gemm_resident(const CUtensorMap& map_a, const CUtensorMap& ma
     return cudaGetLastError();
 }
 
-template <int CB, int BM>
+template <int CB, int BM, bool PAIR = false>
 cudaError_t launch_gemm_cb(const CUtensorMap& map, const GemmArgs& g, uint32_t max_tiles, cudaStream_t stream) {
     void (*fn)(const CUtensorMap, const CUtensorMap, const GemmArgs) = nullptr;
     switch (g.n) {
 #define T3_CASE(NN) \
-    case NN: fn = gemm_decode_kernel<NN, CB, BM>; break;
+    case NN: fn = gemm_decode_kernel<NN, CB, BM, false, PAIR>; break;
         T3_CASE(16) T3_CASE(32) T3_CASE(48) T3_CASE(64) T3_CASE(80) T3_CASE(96) T3_CASE(112) T3_CASE(128)
 #undef T3_CASE
-        default: fn = gemm_decode_kernel<0, CB, BM>; break;
+        default: fn = gemm_decode_kernel<0, CB, BM, false, PAIR>; break;
     }
-    const uint32_t smem_bytes = Tile<BM>::smem(g.n);
+    const uint32_t smem_bytes = Tile<BM, PAIR>::smem(g.n);
     cudaError_t rc = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)Tile<BM>::smem(128u));
+                                          (int)Tile<BM, PAIR>::smem(128u));
     if (rc != cudaSuccess) return rc;
     fn<<<dim3(g.ops * g.N / kBN, max_tiles, 1), kGemmThreads, smem_bytes, stream>>>(map, map, g);
     return cudaGetLastError();
 }
 
-// bm: 256 (dense) or 128 (routed)
+// bm: the tile height (512, 256, 128); pair: 256-row tiles two CTAs a multiprocessor (the routed experts')
 cudaError_t launch_gemm(const CUtensorMap& map, const GemmArgs& g, uint32_t max_tiles, uint32_t bm, int codebook,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, bool pair = false) {
     if (bm == 512u)
         return codebook == kMcg ? launch_gemm_cb<kMcg, 512>(map, g, max_tiles, stream)
                                 : launch_gemm_cb<kMul1, 512>(map, g, max_tiles, stream);
+    if (bm == 256u && pair)
+        return codebook == kMcg ? launch_gemm_cb<kMcg, 256, true>(map, g, max_tiles, stream)
+                                : launch_gemm_cb<kMul1, 256, true>(map, g, max_tiles, stream);
     if (bm == 256u)
         return codebook == kMcg ? launch_gemm_cb<kMcg, 256>(map, g, max_tiles, stream)
                                 : launch_gemm_cb<kMul1, 256>(map, g, max_tiles, stream);
@@ -846,12 +902,10 @@ cudaError_t launch_plain_linear(const void* x, int dt, uint32_t rows, const void
 // ---- routed experts, more than 32 rows --------------------------------------------------------------------------------
 
 namespace {
-constexpr uint32_t kMoeBM = 128;  // routed experts' tile height
 struct MoeWs {
     uint32_t *counts, *cursor, *order, *inv;
-    int4* tiles;
+    TileTables tiles;
     __half *xp, *zgu, *hd, *zd;
-    uint32_t max_tiles;
     size_t total;
 };
 MoeWs carve_moe(uint8_t* base, size_t slots, uint32_t experts, uint32_t hidden, uint32_t inter) {
@@ -862,18 +916,41 @@ MoeWs carve_moe(uint8_t* base, size_t slots, uint32_t experts, uint32_t hidden, 
         off += up256(bytes);
         return p;
     };
-    w.max_tiles = (uint32_t)((slots + kMoeBM - 1u) / kMoeBM) + experts;
+    // the most tiles of each height any routing gives: a 512-row tile holds more than 384 rows, an expert has at most one
+    // 256-row tile (more than 128 rows in it and whatever follows) and one 128-row tile
+    // Calls that average under 96 rows an expert keep to 128-row tiles (most experts fit one, and three launches a GEMM
+    // with two nearly empty cost more than the few second decodes they save): a function of the call's shape only.
+    w.tiles.uniform = slots < (size_t)96u * experts;
+    w.tiles.max[0] = w.tiles.uniform ? 0u : (uint32_t)(slots / 385u) + 1u;
+    w.tiles.max[1] = w.tiles.uniform ? 0u : (uint32_t)(slots / 129u + 1u < experts ? slots / 129u + 1u : experts);
+    w.tiles.max[2] = w.tiles.uniform ? (uint32_t)(slots / 128u) + experts : (uint32_t)(slots < experts ? slots : experts);
     w.counts = reinterpret_cast<uint32_t*>(take((size_t)experts * 4u));
     w.cursor = reinterpret_cast<uint32_t*>(take((size_t)experts * 4u));
     w.order = reinterpret_cast<uint32_t*>(take(slots * 4u));
     w.inv = reinterpret_cast<uint32_t*>(take(slots * 4u));
-    w.tiles = reinterpret_cast<int4*>(take((size_t)w.max_tiles * 16u));
+    for (int k = 0; k < 3; ++k) w.tiles.t[k] = reinterpret_cast<int4*>(take((size_t)w.tiles.max[k] * 16u));
     w.xp = reinterpret_cast<__half*>(take(2u * slots * hidden * 2u));
     w.zgu = reinterpret_cast<__half*>(take(2u * slots * inter * 2u));
     w.hd = reinterpret_cast<__half*>(take(slots * inter * 2u));
     w.zd = reinterpret_cast<__half*>(take(slots * hidden * 2u));
     w.total = off;
     return w;
+}
+
+// one routed GEMM: a launch a tile height, tallest first
+cudaError_t launch_routed_gemm(const void* a_base, uint64_t a_rows, GemmArgs g, const TileTables& tt, int codebook,
+                               cudaStream_t stream) {
+    CUtensorMap map128, map256;
+    if (!make_a_map(&map128, a_base, a_rows, g.K, 128u) || !make_a_map(&map256, a_base, a_rows, g.K, 256u))
+        return cudaErrorNotSupported;
+    static const uint32_t heights[3] = {512u, 256u, 128u};
+    for (int k = 0; k < 3; ++k) {
+        if (tt.max[k] == 0u) continue;
+        g.tiles = tt.t[k];
+        const cudaError_t rc = launch_gemm(k == 2 ? map128 : map256, g, tt.max[k], heights[k], codebook, stream, true);
+        if (rc != cudaSuccess) return rc;
+    }
+    return cudaSuccess;
 }
 }  // namespace
 
@@ -889,7 +966,7 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
     cudaError_t rc = cudaMemsetAsync(w.counts, 0, (size_t)a.experts * 4u, stream);
     if (rc != cudaSuccess) return rc;
     route_count_kernel<<<(S + 255u) / 256u, 256, 0, stream>>>(inds, S, a.experts, w.counts);
-    route_plan_kernel<<<1, 1024, 0, stream>>>(w.counts, a.experts, w.cursor, w.tiles, w.max_tiles, kMoeBM);
+    route_plan_kernel<<<1, 1024, 0, stream>>>(w.counts, a.experts, w.cursor, w.tiles);
     route_scatter_kernel<<<(S + 255u) / 256u, 256, 0, stream>>>(inds, S, a.experts, w.cursor, w.order, w.inv);
 
     PrepArgs pa = {};
@@ -909,9 +986,6 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
     prep_rows_kernel<<<dim3(spread(S, H / 128u), (S + kRowsPerCta - 1u) / kRowsPerCta), 256, 0, stream>>>(pa);
 
     const uint32_t tile_bytes = 2u * a.n;
-    CUtensorMap map_gu, map_d;
-    if (!make_a_map(&map_gu, w.xp, 2u * slots, H, kMoeBM) || !make_a_map(&map_d, w.hd, slots, I, kMoeBM))
-        return cudaErrorNotSupported;
     GemmArgs g = {};
     g.trellis[0] = a.gate_t;
     g.trellis[1] = a.up_t;
@@ -922,14 +996,13 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
     g.mask = a.mask;
     g.ops = 2;
     g.a_op_rows = S;
-    g.tiles = w.tiles;
     g.z = w.zgu;
     g.z_op_stride = slots * I;
     g.svh[0] = static_cast<const __half*>(a.gate_svh);  // the epilogue finishes gate and up with the tile's expert's scales
     g.svh[1] = static_cast<const __half*>(a.up_svh);
     g.svh_stride = I;
     g.err = a.err;
-    rc = launch_gemm(map_gu, g, w.max_tiles, kMoeBM, codebook, stream);
+    rc = launch_routed_gemm(w.xp, 2u * slots, g, w.tiles, codebook, stream);
     if (rc != cudaSuccess) return rc;
 
     MidArgs m = {w.zgu, static_cast<const __half*>(a.down_suh), w.order, inds, S, I, a.experts, a.limit, a.clamp_at, w.hd};
@@ -943,12 +1016,11 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
     d.n = a.n;
     d.mask = a.mask;
     d.ops = 1;
-    d.tiles = w.tiles;
     d.z = w.zd;
     d.svh[0] = d.svh[1] = static_cast<const __half*>(a.down_svh);  // each slot's finished down output, the per-slot v
     d.svh_stride = H;
     d.err = a.err;
-    rc = launch_gemm(map_d, d, w.max_tiles, kMoeBM, codebook, stream);
+    rc = launch_routed_gemm(w.hd, slots, d, w.tiles, codebook, stream);
     if (rc != cudaSuccess) return rc;
 
     FinArgs f = {w.zd, w.inv, a.scores, a.score_dt, a.shared, a.y, a.y_dt, a.rows, H, a.topk};
@@ -958,7 +1030,7 @@ cudaError_t launch_prefill_moe(const MoeArgs& a, void* workspace, int codebook, 
     }
     const uint32_t fin_groups = (a.rows + 7u) / 8u, fin_want = (1184u + fin_groups - 1u) / fin_groups;
     moe_fin_kernel<<<dim3(fin_want < H / 128u ? fin_want : H / 128u, fin_groups), 256, 0, stream>>>(f);
-    *launches += 8;
+    *launches += w.tiles.uniform ? 8 : 12;
     return cudaGetLastError();
 }
 

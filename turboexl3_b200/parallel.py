@@ -43,6 +43,9 @@ class DispatchPlan:
     send_rows: torch.Tensor     # [R] distinct (destination, row) pairs' rows, grouped by destination, rows ascending
     row_counts: list           # token rows to each rank
     row_in_group: torch.Tensor  # [S] for each sent slot, the position of its row inside its destination's group (int32)
+    where: Optional[torch.Tensor] = None   # [S] slot s's position in send order (order's inverse), when the planner gives it
+    meta: Optional[torch.Tensor] = None    # [S, 2] int32 (row_in_group, local_expert) already interleaved
+    counts_dev: Optional[torch.Tensor] = None  # [2, world] int32 on the device: (send_counts, row_counts)
 
 
 def plan_dispatch(inds: torch.Tensor, experts: int, world: int) -> DispatchPlan:
@@ -68,6 +71,8 @@ def plan_dispatch(inds: torch.Tensor, experts: int, world: int) -> DispatchPlan:
 
 
 def _all_to_all_rows(send: torch.Tensor, send_counts: list, recv_counts: list, group) -> torch.Tensor:
+    if dist.get_world_size(group) == 1:
+        return send  # a world of one: what is sent is what is received
     recv = send.new_empty((sum(recv_counts),) + tuple(send.shape[1:]))
     dist.all_to_all_single(recv, send.contiguous(), recv_counts, send_counts, group=group)
     return recv
@@ -75,38 +80,50 @@ def _all_to_all_rows(send: torch.Tensor, send_counts: list, recv_counts: list, g
 
 def ep_moe(x: torch.Tensor, inds: torch.Tensor, scores: torch.Tensor, experts: int,
            expert_fn: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor],
-           merge_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor], group=None) -> torch.Tensor:
+           merge_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor], group=None,
+           plan_fn: Optional[Callable] = None, mapped_merge_fn: Optional[Callable] = None) -> torch.Tensor:
     """One routed layer, expert-parallel. x [rows, hidden] (this rank's rows), inds/scores [rows, topk] with GLOBAL
     expert ids. expert_fn(x_recv [R, hidden], row_of_slot [S] int32, local_expert [S] int32) -> v [S, hidden]: received
     slot i runs row x_recv[row_of_slot[i]] through local expert local_expert[i]. merge_fn(v [rows, topk, hidden], scores)
-    -> y [rows, hidden]. Returns y for this rank's rows.
+    -> y [rows, hidden]; or mapped_merge_fn(v_back [S, hidden] in send order, where [S], scores) when the planner gives
+    `where` (no reordering copy of v). plan_fn(inds, experts, world) -> DispatchPlan (default: `plan_dispatch`, torch ops).
+    Returns y for this rank's rows.
 
-    Exchanges: the counts (one small all-to-all; the plan and the received counts are the two host reads), the distinct token rows, the per-slot (row, expert)
-    pairs, and the finished per-slot outputs back."""
+    Exchanges: the counts (one small all-to-all; the plan's counts and the received counts are the two host reads), the
+    distinct token rows, the per-slot (row, expert) pairs, and the finished per-slot outputs back."""
     world = dist.get_world_size(group)
     rows, topk = inds.shape
-    plan = plan_dispatch(inds, experts, world)
-    counts_out = torch.tensor([plan.send_counts, plan.row_counts], dtype=torch.int64, device=x.device).t().contiguous()
-    counts_in = torch.empty_like(counts_out)
-    dist.all_to_all_single(counts_in, counts_out, group=group)
-    recv = counts_in.t().tolist()
-    recv_slots, recv_rows = recv[0], recv[1]
+    plan = (plan_fn or plan_dispatch)(inds, experts, world)
+    if plan.counts_dev is not None:
+        counts_out = plan.counts_dev.t().contiguous()
+    else:
+        counts_out = torch.tensor([plan.send_counts, plan.row_counts], dtype=torch.int32, device=x.device).t().contiguous()
+    if world == 1:
+        recv_slots, recv_rows = plan.send_counts, plan.row_counts
+    else:
+        counts_in = torch.empty_like(counts_out)
+        dist.all_to_all_single(counts_in, counts_out, group=group)
+        recv = counts_in.t().tolist()
+        recv_slots, recv_rows = recv[0], recv[1]
     x_recv = _all_to_all_rows(x[plan.send_rows], plan.row_counts, recv_rows, group)
-    meta = torch.stack([plan.row_in_group.to(x.device), plan.local_expert.to(x.device)], dim=1)  # [S, 2] int32
-    meta_recv = _all_to_all_rows(meta, plan.send_counts, recv_slots, group)
-    # a received slot names its row inside its SOURCE's group: shift by where that source's rows start here
-    row_starts = torch.tensor(recv_rows, dtype=torch.int64, device=x.device)
-    row_starts = torch.cumsum(row_starts, 0) - row_starts
-    slot_src = torch.repeat_interleave(torch.arange(world, device=x.device), torch.tensor(recv_slots, device=x.device),
-                                       output_size=sum(recv_slots))
-    row_of_slot = (meta_recv[:, 0].to(torch.int64) + row_starts[slot_src]).to(torch.int32)
+    meta = plan.meta if plan.meta is not None else torch.stack([plan.row_in_group.to(x.device), plan.local_expert.to(x.device)], dim=1)
+    meta_recv = _all_to_all_rows(meta, plan.send_counts, recv_slots, group)  # [S, 2] int32
+    row_of_slot = meta_recv[:, 0]
+    if world > 1:
+        # a received slot names its row inside its SOURCE's group: shift by where that source's rows start here
+        starts = [sum(recv_rows[:r]) for r in range(world)]
+        shift = torch.repeat_interleave(torch.tensor(starts, dtype=torch.int32, device=x.device),
+                                        torch.tensor(recv_slots, device=x.device), output_size=sum(recv_slots))
+        row_of_slot = row_of_slot + shift
     if meta_recv.shape[0]:
-        v_recv = expert_fn(x_recv, row_of_slot, meta_recv[:, 1].contiguous())
+        v_recv = expert_fn(x_recv, row_of_slot.contiguous(), meta_recv[:, 1].contiguous())
     else:
         v_recv = x_recv.new_empty((0, x.shape[1]))
     v_back = _all_to_all_rows(v_recv, recv_slots, plan.send_counts, group)
+    if mapped_merge_fn is not None and plan.where is not None:
+        return mapped_merge_fn(v_back, plan.where, scores)
     v = torch.empty_like(v_back)
-    v[plan.order] = v_back  # back to slot order
+    v[plan.order.to(torch.int64)] = v_back  # back to slot order
     return merge_fn(v.view(rows, topk, x.shape[1]), scores)
 
 
@@ -135,7 +152,20 @@ def ep_moe_cuda(x: torch.Tensor, bank_local, inds: torch.Tensor, scores: torch.T
     def merge_fn(v: torch.Tensor, sc: torch.Tensor) -> torch.Tensor:
         return api.moe_merge(v.contiguous(), sc.contiguous(), x.dtype, shared)
 
-    return ep_moe(x, inds, scores, experts, expert_fn, merge_fn, group)
+    def mapped_merge_fn(v_back: torch.Tensor, where: torch.Tensor, sc: torch.Tensor) -> torch.Tensor:
+        return api.moe_merge(v_back.contiguous(), sc.contiguous(), x.dtype, shared, where=where)
+
+    def plan_fn(ids: torch.Tensor, n_experts: int, world: int) -> DispatchPlan:
+        # the plan in one launch on the device (t3_ep_plan); its counts are the one host read
+        order, where, send_rows, meta, counts = api.ep_plan(ids.to(torch.int32).contiguous(), n_experts, world)
+        c = counts.tolist()
+        return DispatchPlan(order, c[0], None, meta[:, 1], send_rows[:sum(c[1])], c[1], meta[:, 0], where=where, meta=meta,
+                            counts_dev=counts)
+
+    world = dist.get_world_size(group)
+    device_plan = world <= api.EP_WORLD_MAX and inds.is_cuda
+    return ep_moe(x, inds, scores, experts, expert_fn, merge_fn, group, plan_fn if device_plan else None,
+                  mapped_merge_fn if device_plan else None)
 
 
 # ---- column-sharded dense linears ----------------------------------------------------------------------------------
