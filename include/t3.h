@@ -244,6 +244,37 @@ int t3_unrot_build(const void* trellis, const void* suh, const void* svh, int in
                    int act_dtype, void* w_std_t, void* stream);
 int t3_linear_unrot(const void* x, int x_dtype, size_t rows, const void* w_std_t, int in_dim, int out_dim, void* y, void* stream);
 
+/* The native kernel seam (src/hip/plan.zig:9-70: "the launches of turboexl3's kernels, from a shape alone: kernel symbol,
+ * grid, block, shared bytes and arguments by role"). The decode-row kernels carry extern "C" names after the reference's
+ * pattern t3_<group>_<kernel>_<profile>...:
+ *   t3_dense_gemv_<mul1|mcg>_n<n>_r<8|16|32>   t3_dec_gate_up_<..>_n<n>_r<..>   t3_dec_down_<..>_n<n>_r<..>   t3_dec_merge
+ * (n = halfwords a tile for the rates with kernels of their own, 0 for the run-time-rate kernels). t3_plan_linear and
+ * t3_plan_moe give, without launching, the launches t3_linear / t3_moe would record for a decode-row call under the
+ * current configuration: each kernel takes ONE argument block (DenseArgs / MoeArgs of csrc/t3_internal.h) whose buffers are
+ * listed by role, numbered as plan.Role is. They return the number of launches written, or minus a t3_status. Prefill
+ * rows (> T3_DECODE_ROWS_MAX): -Exl3EngineNotImplemented. t3_last_kernel_symbol names the kernel the calling thread's last
+ * decode-row launch ran (so a test can hold the plan against the launches). */
+typedef enum {
+    T3_ROLE_X, T3_ROLE_SUH, T3_ROLE_SVH, T3_ROLE_TRELLIS, T3_ROLE_XP, T3_ROLE_XS, T3_ROLE_Z, T3_ROLE_Y,
+    T3_ROLE_SLOTS, T3_ROLE_SCORES, T3_ROLE_GATE_T, T3_ROLE_UP_T, T3_ROLE_DOWN_T, T3_ROLE_GATE_SUH, T3_ROLE_UP_SUH,
+    T3_ROLE_GATE_SVH, T3_ROLE_UP_SVH, T3_ROLE_DOWN_SUH, T3_ROLE_DOWN_SVH,
+    T3_ROLE_XG, T3_ROLE_XU, T3_ROLE_SG, T3_ROLE_SU, T3_ROLE_ZG, T3_ROLE_ZU, T3_ROLE_HD, T3_ROLE_HS, T3_ROLE_ZD,
+    T3_ROLE_ORDER, T3_ROLE_INV, T3_ROLE_ITEMS, T3_ROLE_COUNTS
+} t3_role;
+typedef struct t3_launch {
+    char symbol[64];    /* the kernel's name in the library's device code */
+    char group[16];     /* "dense" | "decode" (plan.Launch.group) */
+    uint32_t grid[3];
+    uint32_t block;
+    uint32_t shared;    /* dynamic shared-memory bytes */
+    uint32_t cluster;   /* CTAs of a thread-block cluster along grid x; 1 = none */
+    int nroles;
+    int roles[24];      /* t3_role of every buffer the launch reads or writes */
+} t3_launch;
+int t3_plan_linear(size_t rows, int in_dim, int out_dim, int n, t3_decode dec, t3_launch* out, int max_launches);
+int t3_plan_moe(size_t rows, int topk, const t3_bank* bank, t3_decode dec, t3_launch* out, int max_launches);
+const char* t3_last_kernel_symbol(void);
+
 /* root.enginesHeld / root.releaseEngines (src/root.zig:1148-1192). The reference caches a compiled engine per geometry and
  * frees them on request; here kernels are compiled ahead and a plan is recomputed per call, so an "engine" is only the
  * record that a geometry was served on a path. The counts are distinct geometries since the last release. */

@@ -144,3 +144,22 @@ def test_release_engines_is_a_no_op_on_empty_caches():
     """src/root.zig:1194-1199: releaseEngines empties every cache; on empty ones it does nothing."""
     api.release_engines()
     assert api.engines_held() == {"decode": 0, "dense": 0, "prefill": 0}
+
+
+def test_launch_plans_name_kernels_and_shapes():
+    """The native kernel seam (src/hip/plan.zig): from a shape alone, the kernel symbols after the reference's naming
+    pattern, the grid, block, shared bytes and the buffers by role. No GPU is touched."""
+    (l,) = t3.plan_linear(1, 2048, 6144, 64)
+    assert l["symbol"] == "t3_dense_gemv_mul1_n64_r8" and l["group"] == "dense"
+    assert l["grid"][1] == 6144 // 128 and l["grid"][0] == l["cluster"] and l["block"] == 544
+    assert 0 < l["shared"] <= 200 * 1024 and l["roles"][:3] == [0, 7, 3]  # x, y, trellis
+    assert t3.plan_linear(17, 2048, 2048, 36, t3.Decode(t3.MCG))[0]["symbol"] == "t3_dense_gemv_mcg_n0_r32"
+    with pytest.raises(t3.Exl3Error, match="Exl3EngineNotImplemented"):
+        t3.plan_linear(33, 2048, 2048, 64)
+    with pytest.raises(t3.Exl3Error, match="BadExl3Shape"):
+        t3.plan_linear(1, 2000, 2048, 64)
+    chain = t3.plan_moe(4, 10, 512, 2048, 512, 48)
+    assert [c["symbol"] for c in chain] == ["t3_dec_gate_up_mul1_n48_r8", "t3_dec_down_mul1_n48_r8", "t3_dec_merge"]
+    assert chain[0]["grid"][1:] == (512 // 128, 40) and chain[1]["grid"][1:] == (2048 // 128, 40)
+    assert chain[0]["cluster"] == chain[0]["grid"][0] and chain[2]["cluster"] == 1
+    assert len(t3.plan_moe(2, 1, 1, 2048, 512, 48)) == 2  # one slot a row: the down launch stores y, no merge

@@ -197,3 +197,21 @@ def test_mapped_merge_is_the_merge():
     y0 = t3.moe_merge(v.view(rows, topk, H), scores, torch.float16)
     y1 = t3.moe_merge(moved, scores, torch.float16, where=perm)
     assert torch.equal(y0, y1)
+
+
+def test_the_launch_plan_names_the_kernels_that_run():
+    """t3_plan_linear / t3_plan_moe against the launches themselves: the planned symbol is the kernel the call launched."""
+    for rows, n, cb in ((1, 64, t3.MUL1), (12, 48, t3.MCG), (30, 36, t3.MUL1)):
+        trellis, suh, svh = synth.linear(90, 512, 384, n, scaled=True)
+        t3.linear(dev(synth.activations(91, rows, 512)), dev(trellis), dev(suh), dev(svh), t3.Decode(cb))
+        (plan,) = t3.plan_linear(rows, 512, 384, n, t3.Decode(cb))
+        assert t3.last_kernel_symbol() == plan["symbol"], (rows, n, plan)
+    H, I, E, n = 256, 128, 8, 32
+    bank, _ = make_bank(92, E, H, I, n)
+    for rows, topk in ((3, 2), (5, 1)):
+        inds, scores = synth.routing(93, rows, E, topk)
+        x = dev(synth.activations(94, rows, H)).view(1, rows, H)
+        t3.moe(x, bank, dev(inds).view(1, rows, topk), dev(scores).view(1, rows, topk))
+        plan = t3.plan_moe(rows, topk, E, H, I, n)
+        assert t3.last_kernel_symbol() == plan[-1]["symbol"], plan
+    assert t3.device_error() == 0

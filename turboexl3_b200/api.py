@@ -52,6 +52,12 @@ class _Spec(C.Structure):
     _fields_ = [("n", C.c_uint32), ("codebook", C.c_int), ("window_bits", C.c_int)]
 
 
+class Launch(C.Structure):
+    """t3_launch: one kernel launch of a plan (symbol, group, grid, block, shared bytes, cluster size, buffer roles)."""
+    _fields_ = [("symbol", C.c_char * 64), ("group", C.c_char * 16), ("grid", C.c_uint32 * 3), ("block", C.c_uint32),
+                ("shared", C.c_uint32), ("cluster", C.c_uint32), ("nroles", C.c_int), ("roles", C.c_int * 24)]
+
+
 class _Config(C.Structure):
     _fields_ = [("prefill", C.c_int), ("ring_bytes", C.c_uint32), ("dense_split", C.c_uint32), ("no_overlap", C.c_int),
                 ("probe", C.c_int)]
@@ -92,6 +98,9 @@ SYMBOLS = {
     "t3_unrot_build": (_i, [_vp, _vp, _vp, _i, _i, _i, _Decode, _i, _vp, _vp]),
     "t3_linear_unrot": (_i, [_vp, _i, _sz, _vp, _i, _i, _vp, _vp]),
     "t3_moe_clamped_banked": (_i, [_vp, _i, _sz, C.POINTER(_Bank), _vp, _Decode, _i, _vp, _i, _vp, _sz, _vp]),
+    "t3_plan_linear": (_i, [_sz, _i, _i, _i, _Decode, C.POINTER(Launch), _i]),
+    "t3_plan_moe": (_i, [_sz, _i, C.POINTER(_Bank), _Decode, C.POINTER(Launch), _i]),
+    "t3_last_kernel_symbol": (C.c_char_p, []),
     "t3_engines_held": (None, [_vp]),
     "t3_release_engines": (None, []),
 }
@@ -182,6 +191,34 @@ def device_error(clear: bool = True) -> int:
     bits = C.c_uint32(0)
     _check(lib().t3_device_error(torch.cuda.current_stream().cuda_stream, C.byref(bits), int(clear)))
     return bits.value
+
+
+def plan_linear(rows: int, in_dim: int, out_dim: int, n: int, dec: "Decode" = None) -> list:
+    """t3_plan_linear: the launches a decode-row `linear` records, as dicts (symbol, group, grid, block, shared, cluster, roles)."""
+    out = (Launch * 4)()
+    k = lib().t3_plan_linear(rows, in_dim, out_dim, n, (dec or Decode.mul1)._c(), out, 4)
+    if k < 0:
+        _check(-k)
+    return [_launch_dict(out[i]) for i in range(k)]
+
+
+def plan_moe(rows: int, topk: int, experts: int, hidden: int, inter: int, n: int, dec: "Decode" = None) -> list:
+    """t3_plan_moe for a bank geometry (no device memory needed)."""
+    bank = _Bank(_Proj(), _Proj(), _Proj(), experts, hidden, inter, n, n, n)
+    out = (Launch * 4)()
+    k = lib().t3_plan_moe(rows, topk, C.byref(bank), (dec or Decode.mul1)._c(), out, 4)
+    if k < 0:
+        _check(-k)
+    return [_launch_dict(out[i]) for i in range(k)]
+
+
+def _launch_dict(l: Launch) -> dict:
+    return {"symbol": l.symbol.decode(), "group": l.group.decode(), "grid": tuple(l.grid), "block": l.block, "shared": l.shared,
+            "cluster": l.cluster, "roles": [l.roles[i] for i in range(l.nroles)]}
+
+
+def last_kernel_symbol() -> str:
+    return lib().t3_last_kernel_symbol().decode()
 
 
 def launch_count() -> int:

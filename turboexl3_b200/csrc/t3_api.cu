@@ -3,7 +3,9 @@
 #include <atomic>
 #include <cmath>
 #include <cstdlib>
+#include <cstdio>
 #include <cstring>
+#include <initializer_list>
 #include <mutex>
 #include <unordered_set>
 #include <string>
@@ -163,6 +165,9 @@ uint32_t row_cap_for(uint32_t rows) { return rows <= 8u ? 8u : (rows <= 16u ? 16
 uint32_t gemv_smem_bytes(uint32_t row_cap, uint32_t xrows, uint32_t slice_max, uint32_t cluster, uint32_t n, RingPlan ring) {
     return gemv_smem(row_cap, xrows, slice_max, cluster, ring.stage_rows * 16u * n, ring.stages).total + kSmemSlack;
 }
+
+thread_local const void* g_last_kernel = nullptr;
+void note_symbol(const void* kernel) { g_last_kernel = kernel; }
 
 cudaError_t launch_dense_gemv(const DenseArgs& a, int codebook, cudaStream_t stream) {
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -404,6 +409,43 @@ int t3_codebook_table(t3_decode dec, void* out, void* stream) {
 
 // ---- dense linear ---------------------------------------------------------------------------------------------------
 
+namespace {
+// The launch shape of a dense linear at decode rows: the K split (cluster size) and the code ring. a.rows, in, out, n set.
+int plan_dense(DenseArgs& a, const t3_config& cfg) {
+    const uint32_t nb = a.in / 128u;
+    const bool large = (uint64_t)a.in * a.out * a.n >= (uint64_t)24u * 1024u * 1024u * 128u;  // 24 MB of codes and up
+    a.split = cfg.dense_split ? (cfg.dense_split < nb ? cfg.dense_split : nb)
+                              : (large ? pick_split_large(nb, a.out / 128u) : pick_split(nb, a.out / 128u, 1u, 8u, one_wave() / 2u));
+    a.overlap = !cfg.no_overlap;
+    a.slice_max = largest_slice(nb, a.split);
+    // a slice too long for shared memory (its prepared rows) is cut further, up to the widest cluster
+    while (!plan_ring(row_cap_for(a.rows), a.rows, a.slice_max, a.split, a.n, a.ring)) {
+        if (a.split * 2u > nb || a.split * 2u > 16u) return T3_ENGINE_NOT_IMPLEMENTED;
+        a.split *= 2u;
+        a.slice_max = largest_slice(nb, a.split);
+    }
+    return T3_OK;
+}
+
+// the rate as the kernels' names carry it: the integer rates have their own kernels, any other even rate runs the n0 ones
+uint32_t named_rate(uint32_t n) { return (n % 16u == 0u && n >= 16u && n <= 128u) ? n : 0u; }
+
+void fill_launch(t3_launch* l, const char* symbol, const char* group, dim3 grid, uint32_t block, uint32_t shared, uint32_t cluster,
+                 std::initializer_list<int> roles) {
+    std::memset(l, 0, sizeof *l);
+    std::snprintf(l->symbol, sizeof l->symbol, "%s", symbol);
+    std::snprintf(l->group, sizeof l->group, "%s", group);
+    l->grid[0] = grid.x, l->grid[1] = grid.y, l->grid[2] = grid.z;
+    l->block = block;
+    l->shared = shared;
+    l->cluster = cluster;
+    for (int r : roles)
+        if (l->nroles < (int)(sizeof l->roles / sizeof l->roles[0])) l->roles[l->nroles++] = r;
+}
+
+}  // namespace
+
+
 size_t t3_linear_workspace_bytes(size_t rows, int in_dim, int out_dim, int n) {
     (void)n;
     if (rows <= T3_DECODE_ROWS_MAX || in_dim <= 0 || out_dim <= 0) return 0;  // the decode-row kernel keeps everything on chip
@@ -449,21 +491,10 @@ int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, cons
     a.mask = mask;
     a.x_dt = x_dtype;
     note_engine(1, (uint64_t)in_dim, (uint64_t)out_dim, (uint64_t)n, 0);
-    const uint32_t nb = a.in / 128u;
-    const bool large = (uint64_t)a.in * a.out * a.n >= (uint64_t)24u * 1024u * 1024u * 128u;  // 24 MB of codes and up
-    a.split = cfg.dense_split ? (cfg.dense_split < nb ? cfg.dense_split : nb)
-                              : (large ? pick_split_large(nb, a.out / 128u) : pick_split(nb, a.out / 128u, 1u, 8u, one_wave() / 2u));
-    a.overlap = !cfg.no_overlap;
-    a.slice_max = largest_slice(nb, a.split);
+    a.rows = (uint32_t)rows;
+    if (int rc = plan_dense(a, cfg)) return rc;
     a.err = dev_error_ptr();
     a.trace = g_trace;
-    a.rows = (uint32_t)rows;
-    // a slice too long for shared memory (its prepared rows) is cut further, up to the widest cluster
-    while (!plan_ring(row_cap_for(a.rows), a.rows, a.slice_max, a.split, a.n, a.ring)) {
-        if (a.split * 2u > nb || a.split * 2u > 16u) return T3_ENGINE_NOT_IMPLEMENTED;
-        a.split *= 2u;
-        a.slice_max = largest_slice(nb, a.split);
-    }
     a.x = x;
     a.y = y;
     if (cfg.probe) {  // a timing probe in the served kernel's place: y is not the linear's output
@@ -471,6 +502,36 @@ int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, cons
         return cuda_status(launch_dense_gemv(a, 1 + cfg.probe, static_cast<cudaStream_t>(stream)));
     }
     return cuda_status(launch_dense_gemv(a, dec.codebook, static_cast<cudaStream_t>(stream)));
+}
+
+const char* t3_last_kernel_symbol(void) {
+    const char* name = nullptr;
+    if (!g_last_kernel || cudaFuncGetName(&name, g_last_kernel) != cudaSuccess) return "";
+    return name ? name : "";
+}
+
+int t3_plan_linear(size_t rows, int in_dim, int out_dim, int n, t3_decode dec, t3_launch* out, int max_launches) {
+    if (!out) return -T3_NULL_POINTER;
+    if (in_dim <= 0 || out_dim <= 0 || in_dim % 128 != 0 || out_dim % 128 != 0 || !rate_ok(n) || rows < 1) return -T3_BAD_EXL3_SHAPE;
+    uint32_t mask;
+    if (int rc = decode_mask(dec, mask)) return -rc;
+    if (rows > T3_DECODE_ROWS_MAX) return -T3_ENGINE_NOT_IMPLEMENTED;  // the plan covers the decode-row kernels
+    if (max_launches < 1) return -T3_BAD_EXL3_SHAPE;
+    t3_config cfg;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        cfg = g_cfg;
+    }
+    DenseArgs a = {};
+    a.in = (uint32_t)in_dim, a.out = (uint32_t)out_dim, a.n = (uint32_t)n, a.rows = (uint32_t)rows;
+    if (int rc = plan_dense(a, cfg)) return -rc;
+    const uint32_t rm = row_cap_for(a.rows);
+    char symbol[64];
+    std::snprintf(symbol, sizeof symbol, "t3_dense_gemv_%s_n%u_r%u", dec.codebook == T3_MCG ? "mcg" : "mul1", named_rate(a.n), rm);
+    fill_launch(&out[0], symbol, "dense", dim3(a.split, a.out / 128u, 1), 32u * 17u,
+                gemv_smem_bytes(rm, a.rows, a.slice_max, a.split, a.n, a.ring), a.split,
+                {T3_ROLE_X, T3_ROLE_Y, T3_ROLE_TRELLIS, T3_ROLE_SUH, T3_ROLE_SVH});
+    return 1;
 }
 
 // ---- routed experts -------------------------------------------------------------------------------------------------
@@ -494,10 +555,10 @@ size_t align256(size_t v) { return (v + 255u) & ~(size_t)255u; }
 
 // The routed chain at decode rows on filled arguments (geometry, rows, top-k, pointers): plans the launches and records
 // them. workspace: t3_moe_workspace_bytes(rows, topk, bank) bytes.
-int decode_chain(MoeArgs a, const t3_config& cfg, int codebook, void* workspace, cudaStream_t s, void* shared_ready) {
+// The launch shapes of the routed chain at decode rows: row capacity of a pass, K splits, code rings. Geometry, rows and
+// top-k set.
+int plan_moe_decode(MoeArgs& a, const t3_config& cfg) {
     const size_t slots = (size_t)a.rows * a.topk;
-    a.hd = workspace;
-    a.v = static_cast<uint8_t*>(workspace) + align256(slots * a.inter * 2u);
     // Rows one pass over an expert's weights serves. Sized from the geometry's expected members an expert (rows * topk /
     // experts, with headroom), not from the row count: with many experts a 32-row call still has one or two rows an
     // expert, and a 32-row pass would pay four times the shared memory and twice the tensor-core steps for nothing. An
@@ -529,6 +590,14 @@ int decode_chain(MoeArgs a, const t3_config& cfg, int codebook, void* workspace,
     }
     if (!plan_ring(rm, rm, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu) || !plan_ring(rm, rm, a.slice_max_d, a.split_d, a.n, a.ring_d))
         return T3_ENGINE_NOT_IMPLEMENTED;
+    return T3_OK;
+}
+
+int decode_chain(MoeArgs a, const t3_config& cfg, int codebook, void* workspace, cudaStream_t s, void* shared_ready) {
+    const size_t slots = (size_t)a.rows * a.topk;
+    a.hd = workspace;
+    a.v = static_cast<uint8_t*>(workspace) + align256(slots * a.inter * 2u);
+    if (int rc = plan_moe_decode(a, cfg)) return rc;
     a.err = dev_error_ptr();
     if (int rc = cuda_status(launch_moe_gate_up(a, codebook, s))) return rc;
     if (a.topk == 1u) {
@@ -609,6 +678,51 @@ int moe_call(const void* x, int x_dtype, size_t rows, const t3_bank* bank, const
 }
 
 }  // namespace
+
+int t3_plan_moe(size_t rows, int topk, const t3_bank* bank, t3_decode dec, t3_launch* out, int max_launches) {
+    if (!out || !bank) return -T3_NULL_POINTER;
+    if (rows < 1 || topk <= 0 || topk > T3_REDUCE_MAX_TOPK) return -T3_BAD_EXL3_SHAPE;
+    if (bank->experts <= 0 || bank->hidden <= 0 || bank->inter <= 0 || bank->hidden % 128 != 0 || bank->inter % 128 != 0 ||
+        !rate_ok(bank->n_gate) || !rate_ok(bank->n_up) || !rate_ok(bank->n_down))
+        return -T3_BAD_EXL3_SHAPE;
+    if (bank->n_gate != bank->n_up) return -T3_GATE_UP_RATE_MISMATCH;
+    if (bank->n_gate != bank->n_down) return -T3_ENGINE_NOT_IMPLEMENTED;
+    uint32_t mask;
+    if (int rc = decode_mask(dec, mask)) return -rc;
+    if (rows > T3_DECODE_ROWS_MAX) return -T3_ENGINE_NOT_IMPLEMENTED;  // the plan covers the decode-row kernels
+    const int count = topk == 1 ? 2 : 3;
+    if (max_launches < count) return -T3_BAD_EXL3_SHAPE;
+    t3_config cfg;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        cfg = g_cfg;
+    }
+    MoeArgs a = {};
+    a.experts = (uint32_t)bank->experts, a.hidden = (uint32_t)bank->hidden, a.inter = (uint32_t)bank->inter;
+    a.topk = (uint32_t)topk, a.rows = (uint32_t)rows, a.n = (uint32_t)bank->n_gate;
+    if (int rc = plan_moe_decode(a, cfg)) return -rc;
+    const char* cb = dec.codebook == T3_MCG ? "mcg" : "mul1";
+    const uint32_t rm = a.row_cap, slots = a.rows * a.topk;
+    char symbol[64];
+    std::snprintf(symbol, sizeof symbol, "t3_dec_gate_up_%s_n%u_r%u", cb, named_rate(a.n), rm);
+    fill_launch(&out[0], symbol, "decode", dim3(2u * a.split_gu, a.inter / 128u, slots), 32u * 17u,
+                gemv_smem_bytes(rm, rm, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu), 2u * a.split_gu,
+                {T3_ROLE_X, T3_ROLE_SLOTS, T3_ROLE_GATE_T, T3_ROLE_UP_T, T3_ROLE_GATE_SUH, T3_ROLE_UP_SUH, T3_ROLE_GATE_SVH,
+                 T3_ROLE_UP_SVH, T3_ROLE_DOWN_SUH, T3_ROLE_HD});
+    std::snprintf(symbol, sizeof symbol, "t3_dec_down_%s_n%u_r%u", cb, named_rate(a.n), rm);
+    if (topk == 1) {
+        fill_launch(&out[1], symbol, "decode", dim3(a.split_d, a.hidden / 128u, slots), 32u * 17u,
+                    gemv_smem_bytes(rm, rm, a.slice_max_d, a.split_d, a.n, a.ring_d), a.split_d,
+                    {T3_ROLE_HD, T3_ROLE_SLOTS, T3_ROLE_DOWN_T, T3_ROLE_DOWN_SVH, T3_ROLE_SCORES, T3_ROLE_Y});
+        return 2;
+    }
+    fill_launch(&out[1], symbol, "decode", dim3(a.split_d, a.hidden / 128u, slots), 32u * 17u,
+                gemv_smem_bytes(rm, rm, a.slice_max_d, a.split_d, a.n, a.ring_d), a.split_d,
+                {T3_ROLE_HD, T3_ROLE_SLOTS, T3_ROLE_DOWN_T, T3_ROLE_DOWN_SVH, T3_ROLE_ZD});
+    fill_launch(&out[2], "t3_dec_merge", "decode", dim3((a.hidden + 255u) / 256u, a.rows, 1), 256u, 0u, 1u,
+                {T3_ROLE_ZD, T3_ROLE_SCORES, T3_ROLE_Y});
+    return 3;
+}
 
 size_t t3_moe_workspace_bytes(size_t rows, int topk, const t3_bank* bank) {
     if (!bank || topk <= 0 || bank->inter <= 0 || bank->hidden <= 0 || bank->experts <= 0) return 0;

@@ -75,7 +75,7 @@ __device__ __forceinline__ void gemv_and_push(cg::cluster_group& cluster, const 
 
 // grid (split, out / 128), cluster (split, 1, 1)
 template <int N, int RM>
-__global__ void __launch_bounds__(kGemvThreads, 2) dense_gemv_kernel(const DenseArgs a) {
+__device__ __forceinline__ void dense_gemv_body(const DenseArgs& a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* smem = aligned_smem(smem_raw);
     cg::cluster_group cluster = cg::this_cluster();
@@ -208,7 +208,7 @@ __device__ __forceinline__ float swiglu(float g, float u, float limit, int clamp
 // slice r >> 1. A row's owner finishes both projections, applies SwiGLU and prepares the 128 values as inputs of the
 // down projection (ref.moeRow's middle, ref.zig:98-105; the reference kernels' "mid": src/kernels/hip/routed.hpp:64-112).
 template <int N, int RM>
-__global__ void __launch_bounds__(kGemvThreads, 2) moe_gate_up_kernel(const MoeArgs a) {
+__device__ __forceinline__ void moe_gate_up_body(const MoeArgs& a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* smem = aligned_smem(smem_raw);
     __shared__ uint32_t s_inds[kMaxSlots];
@@ -295,7 +295,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_gate_up_kernel(const MoeA
 // grid (SD, hidden/128, row-slots), cluster (SD, 1, 1): the down projection of every member of the slot's expert from the
 // prepared rows hd, finished per row-slot into v (f16): the value the merge weights by the slot's score.
 template <int N, int RM>
-__global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs a) {
+__device__ __forceinline__ void moe_down_body(const MoeArgs& a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* smem = aligned_smem(smem_raw);
     __shared__ uint32_t s_inds[kMaxSlots];
@@ -361,7 +361,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs
                 const uint32_t slot = s_members[m0 + m];
                 if (a.topk == 1u) {
                     // One slot a row: the merge has nothing to gather, so the weighted value (and the shared-expert add)
-                    // is stored here and the merge launch is skipped. The arithmetic is moe_merge_kernel's, 0 + w v included.
+                    // is stored here and the merge launch is skipped. The arithmetic is the merge kernel's, 0 + w v included.
                     const float w = a.scores ? load_act(a.scores, a.score_dt, slot) : 1.0f;
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
@@ -387,7 +387,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) moe_down_kernel(const MoeArgs
 // grid (ceil(hidden / 256), rows): y[row] = sum over the row's slots, in slot order, of score * v in f32 (a multiply and an
 // add, as ref.moeRow has it, ref.zig:106), stored in x's dtype; then the optional shared-expert add in that dtype
 // (root.moeWithShared, src/root.zig:976-984).
-__global__ void __launch_bounds__(256) moe_merge_kernel(const MoeArgs a) {
+__device__ __forceinline__ void moe_merge_body(const MoeArgs& a) {
     const uint32_t i = blockIdx.x * 256u + threadIdx.x, row = blockIdx.y;
     pdl_trigger();
     pdl_wait();  // v is the down launch's output
@@ -453,35 +453,78 @@ cudaError_t launch_cluster(KernelFn<Args> fn, const Args& a, dim3 grid, uint32_t
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = overlap ? 2 : 1;
+    note_symbol(reinterpret_cast<const void*>(fn));
     return cudaLaunchKernelEx(&cfg, fn, a);
 }
 
+}  // namespace
+
+// ---- entry points ---------------------------------------------------------------------------------------------------
+// extern "C" names, as the reference's native kernels have them (t3_<group>_<kernel>_<profile>..., src/kernels/hip/decode/
+// decode.hip:355-460), so that a host which binds kernels by name finds them and a launch plan can name them:
+//   t3_dense_gemv_<codebook>_n<n>_r<rows>      t3_dec_gate_up_<codebook>_n<n>_r<rows>      t3_dec_down_<codebook>_n<n>_r<rows>
+//   t3_dec_merge
+// <codebook> mul1 | mcg (probe2..probe4: the dense kernel's timing probes); <n> the rate's halfwords a tile, 0 = any even
+// rate at run time; <rows> the row capacity of a pass, 8 | 16 | 32.
+#if T3_CB == 0
+#define T3_CBNAME mul1
+#elif T3_CB == 1
+#define T3_CBNAME mcg
+#elif T3_CB == 2
+#define T3_CBNAME probe2
+#elif T3_CB == 3
+#define T3_CBNAME probe3
+#else
+#define T3_CBNAME probe4
+#endif
+#define T3_NAME2(stem, cb, nn, rm) stem##_##cb##_n##nn##_r##rm
+#define T3_NAME(stem, cb, nn, rm) T3_NAME2(stem, cb, nn, rm)
+#define T3_ENTRY(STEM, BODY, ARGS, NN, RM)                                                                      \
+    extern "C" __global__ void __launch_bounds__(kGemvThreads, 2) T3_NAME(STEM, T3_CBNAME, NN, RM)(const ARGS a) { \
+        BODY<NN, RM>(a);                                                                                        \
+    }
 #if T3_SERVED
-#define T3_PICK_RM(KERNEL, NN, rm) \
-    ((rm) == 8 ? KERNEL<NN, 8> : ((rm) == 16 ? KERNEL<NN, 16> : KERNEL<NN, 32>))
+#define T3_ENTRIES(STEM, BODY, ARGS, NN) T3_ENTRY(STEM, BODY, ARGS, NN, 8) T3_ENTRY(STEM, BODY, ARGS, NN, 16) T3_ENTRY(STEM, BODY, ARGS, NN, 32)
 #else  // the probes exist at the 8-row capacity only
-#define T3_PICK_RM(KERNEL, NN, rm) KERNEL<NN, 8>
+#define T3_ENTRIES(STEM, BODY, ARGS, NN) T3_ENTRY(STEM, BODY, ARGS, NN, 8)
+#endif
+#define T3_ALL_RATES(STEM, BODY, ARGS)                                                                          \
+    T3_ENTRIES(STEM, BODY, ARGS, 0) T3_ENTRIES(STEM, BODY, ARGS, 16) T3_ENTRIES(STEM, BODY, ARGS, 32)           \
+    T3_ENTRIES(STEM, BODY, ARGS, 48) T3_ENTRIES(STEM, BODY, ARGS, 64) T3_ENTRIES(STEM, BODY, ARGS, 80)          \
+    T3_ENTRIES(STEM, BODY, ARGS, 96) T3_ENTRIES(STEM, BODY, ARGS, 112) T3_ENTRIES(STEM, BODY, ARGS, 128)
+T3_ALL_RATES(t3_dense_gemv, dense_gemv_body, DenseArgs)
+#if T3_SERVED
+T3_ALL_RATES(t3_dec_gate_up, moe_gate_up_body, MoeArgs)
+T3_ALL_RATES(t3_dec_down, moe_down_body, MoeArgs)
+#endif
+#if T3_CB == 0
+extern "C" __global__ void __launch_bounds__(256) t3_dec_merge(const MoeArgs a) { moe_merge_body(a); }
 #endif
 
-#define T3_PICK(KERNEL, n, rm)                                                       \
-    ((n) == 16    ? T3_PICK_RM(KERNEL, 16, rm)                                        \
-     : (n) == 32  ? T3_PICK_RM(KERNEL, 32, rm)                                        \
-     : (n) == 48  ? T3_PICK_RM(KERNEL, 48, rm)                                        \
-     : (n) == 64  ? T3_PICK_RM(KERNEL, 64, rm)                                        \
-     : (n) == 80  ? T3_PICK_RM(KERNEL, 80, rm)                                        \
-     : (n) == 96  ? T3_PICK_RM(KERNEL, 96, rm)                                        \
-     : (n) == 112 ? T3_PICK_RM(KERNEL, 112, rm)                                       \
-     : (n) == 128 ? T3_PICK_RM(KERNEL, 128, rm)                                       \
-                  : T3_PICK_RM(KERNEL, 0, rm))
+#if T3_SERVED
+#define T3_PICK_RM(STEM, NN, rm) \
+    ((rm) == 8 ? T3_NAME(STEM, T3_CBNAME, NN, 8) : ((rm) == 16 ? T3_NAME(STEM, T3_CBNAME, NN, 16) : T3_NAME(STEM, T3_CBNAME, NN, 32)))
+#else
+#define T3_PICK_RM(STEM, NN, rm) T3_NAME(STEM, T3_CBNAME, NN, 8)
+#endif
 
-}  // namespace
+#define T3_PICK(STEM, n, rm)                                                       \
+    ((n) == 16    ? T3_PICK_RM(STEM, 16, rm)                                        \
+     : (n) == 32  ? T3_PICK_RM(STEM, 32, rm)                                        \
+     : (n) == 48  ? T3_PICK_RM(STEM, 48, rm)                                        \
+     : (n) == 64  ? T3_PICK_RM(STEM, 64, rm)                                        \
+     : (n) == 80  ? T3_PICK_RM(STEM, 80, rm)                                        \
+     : (n) == 96  ? T3_PICK_RM(STEM, 96, rm)                                        \
+     : (n) == 112 ? T3_PICK_RM(STEM, 112, rm)                                       \
+     : (n) == 128 ? T3_PICK_RM(STEM, 128, rm)                                       \
+                  : T3_PICK_RM(STEM, 0, rm))
 
 #define T3_CAT2(a, b) a##b
 #define T3_CAT(a, b) T3_CAT2(a, b)
 
 cudaError_t T3_CAT(launch_dense_gemv_cb, T3_CB)(const DenseArgs& a, cudaStream_t stream) {
     const uint32_t rm = row_cap_for(a.rows);
-    KernelFn<DenseArgs> fn = T3_PICK(dense_gemv_kernel, a.n, rm);
+    KernelFn<DenseArgs> fn = T3_PICK(t3_dense_gemv, a.n, rm);
     return launch_cluster(fn, a, dim3(a.split, a.out / 128u, 1), a.split, gemv_smem_bytes(rm, a.rows, a.slice_max, a.split, a.n, a.ring),
                           a.overlap != 0, stream);
 }
@@ -489,14 +532,14 @@ cudaError_t T3_CAT(launch_dense_gemv_cb, T3_CB)(const DenseArgs& a, cudaStream_t
 #if T3_SERVED
 cudaError_t T3_CAT(launch_moe_gate_up_cb, T3_CB)(const MoeArgs& a, cudaStream_t stream) {
     const uint32_t rm = a.row_cap;
-    KernelFn<MoeArgs> fn = T3_PICK(moe_gate_up_kernel, a.n, rm);
+    KernelFn<MoeArgs> fn = T3_PICK(t3_dec_gate_up, a.n, rm);
     return launch_cluster(fn, a, dim3(2u * a.split_gu, a.inter / 128u, a.rows * a.topk), 2u * a.split_gu,
                           gemv_smem_bytes(rm, rm, a.slice_max_gu, 2u * a.split_gu, a.n, a.ring_gu), a.overlap != 0, stream);
 }
 
 cudaError_t T3_CAT(launch_moe_down_cb, T3_CB)(const MoeArgs& a, cudaStream_t stream) {
     const uint32_t rm = a.row_cap;
-    KernelFn<MoeArgs> fn = T3_PICK(moe_down_kernel, a.n, rm);
+    KernelFn<MoeArgs> fn = T3_PICK(t3_dec_down, a.n, rm);
     return launch_cluster(fn, a, dim3(a.split_d, a.hidden / 128u, a.rows * a.topk), a.split_d,
                           gemv_smem_bytes(rm, rm, a.slice_max_d, a.split_d, a.n, a.ring_d), a.overlap != 0, stream);
 }
@@ -513,7 +556,8 @@ cudaError_t launch_moe_merge(const MoeArgs& a, cudaStream_t stream) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = a.overlap ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, moe_merge_kernel, a);
+    note_symbol(reinterpret_cast<const void*>(t3_dec_merge));
+    return cudaLaunchKernelEx(&cfg, t3_dec_merge, a);
 }
 #endif
 

@@ -65,6 +65,9 @@ struct MoeArgs {
     uint32_t* err;
 };
 
+// remembers, per host thread, the kernel a decode-row launch is about to run (t3_last_kernel_symbol names it)
+void note_symbol(const void* kernel);
+
 cudaError_t launch_dense_gemv(const DenseArgs& a, int codebook, cudaStream_t stream);
 cudaError_t launch_moe_gate_up(const MoeArgs& a, int codebook, cudaStream_t stream);
 cudaError_t launch_moe_down(const MoeArgs& a, int codebook, cudaStream_t stream);
