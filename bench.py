@@ -478,6 +478,18 @@ def run_case(args) -> None:
                           dev(scores).view(1, rows, topk)))
         run = lambda: [t3.moe(x, bank, i_, s_) for (x, i_, s_) in calls]
         per = len(calls)
+    elif args.case == "dense_decode":
+        # one linear at decode rows over enough weight copies (random codes) to stream from HBM: --shape INxOUTxK
+        i, o, k = (int(v) for v in args.shape.lower().split("x"))
+        halfs = (i // 16) * (o // 16) * 16 * k
+        copies = max(2, min(8, int(400e6 // (2 * halfs))))
+        pool = torch.randint(0, 2 ** 31 - 1, (copies * halfs // 2,), dtype=torch.int32, device="cuda").view(torch.int16)
+        ws = [pool[c * halfs:(c + 1) * halfs].view(i // 16, o // 16, 16 * k) for c in range(copies)]
+        _, suh, svh = synth.linear(7, i, o, 16)
+        suh_d, svh_d = dev(suh), dev(svh)
+        x = dev(synth.activations(9, min(max(args.rows, 1), 32), i))
+        run = lambda: [t3.linear(x, w, suh_d, svh_d) for w in ws]
+        per = copies
     else:
         w = tuple(dev(a) for a in synth.linear(5, 2048, 6144, 64))
         x = dev(synth.activations(1, max(args.rows, 33), 2048))
@@ -756,7 +768,7 @@ def run_ours(args) -> None:
                    "multi_gpu": "replicas only: each rank runs the sweep on its own weight copies, no collective"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm"], "traffic": traffic, "traffic_capture": traffic_note, "peak_kind": peaks["kind"],
-                     "kernel": "dense_gemv_kernel (21 launches a step; bytes and time are the step's, per launch)"},
+                     "kernel": "t3_dense_gemv_<codebook>_n<n>_r8 (21 launches a step; bytes and time are the step's, per launch)"},
         "cpu_baseline": {"value": cpu["value"], "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": "one full pass of the 21-linear sweep, format.project decoding every tile per call",
                          "single_thread": cpu_single_thread()},
@@ -782,9 +794,10 @@ def main() -> None:
     ap.add_argument("--quick", action="store_true", help="headline and e2e only (no per-linear table, no submetrics)")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of replaying CUDA graphs")
     ap.add_argument("--dense-split", type=int, default=0, help="force the dense GEMV's K split (t3_configure; 0 = the library's choice)")
-    ap.add_argument("--case", default=None, choices=["moe_decode", "moe_prefill", "dense_prefill", "resident_prefill"],
+    ap.add_argument("--case", default=None, choices=["moe_decode", "moe_prefill", "dense_prefill", "resident_prefill", "dense_decode"],
                     help="run one case eagerly --steps times and exit (for profilers)")
     ap.add_argument("--rows", type=int, default=1, help="rows of --case")
+    ap.add_argument("--shape", default="16384x7168x4", help="INxOUTxK of --case dense_decode")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
