@@ -119,7 +119,9 @@ int t3_dequant(const void* trellis, int in_dim, int out_dim, int n, t3_decode de
 int t3_codebook_table(t3_decode dec, void* out, void* stream);
 
 /* root.linear (src/root.zig:309-351): y [rows, out] in x's dtype for x [rows, in]. `workspace` may be null when
- * t3_linear_workspace_bytes returns 0 for the call. */
+ * t3_linear_workspace_bytes returns 0 for the call (up to 8 rows). For 9 to 32 rows the workspace (rows x in f16, 256-byte
+ * aligned) is OPTIONAL: with it the rows are rotated once by a launch of their own ahead of the GEMV, without it every CTA
+ * rotates its own copy; the same bytes either way. Past 32 rows it is required. */
 size_t t3_linear_workspace_bytes(size_t rows, int in_dim, int out_dim, int n);
 int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, const void* suh, const void* svh,
               int in_dim, int out_dim, int n, t3_decode dec, void* y, void* workspace, size_t workspace_bytes,
@@ -247,7 +249,8 @@ int t3_linear_unrot(const void* x, int x_dtype, size_t rows, const void* w_std_t
 /* The native kernel seam (src/hip/plan.zig:9-70: "the launches of turboexl3's kernels, from a shape alone: kernel symbol,
  * grid, block, shared bytes and arguments by role"). The decode-row kernels carry extern "C" names after the reference's
  * pattern t3_<group>_<kernel>_<profile>...:
- *   t3_dense_gemv_<mul1|mcg>_n<n>_r<8|16|32>   t3_dec_gate_up_<..>_n<n>_r<..>   t3_dec_down_<..>_n<n>_r<..>   t3_dec_merge
+ *   t3_dense_gemv_<mul1|mcg>_n<n>_r<8|16|32>   t3_dense_prep   t3_dec_gate_up_<..>_n<n>_r<..>   t3_dec_down_<..>_n<n>_r<..>
+ *   t3_dec_merge
  * (n = halfwords a tile for the rates with kernels of their own, 0 for the run-time-rate kernels). t3_plan_linear and
  * t3_plan_moe give, without launching, the launches t3_linear / t3_moe would record for a decode-row call under the
  * current configuration: each kernel takes ONE argument block (DenseArgs / MoeArgs of csrc/t3_internal.h) whose buffers are

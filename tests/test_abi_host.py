@@ -153,7 +153,9 @@ def test_launch_plans_name_kernels_and_shapes():
     assert l["symbol"] == "t3_dense_gemv_mul1_n64_r8" and l["group"] == "dense"
     assert l["grid"][1] == 6144 // 128 and l["grid"][0] == l["cluster"] and l["block"] == 544
     assert 0 < l["shared"] <= 200 * 1024 and l["roles"][:3] == [0, 7, 3]  # x, y, trellis
-    assert t3.plan_linear(17, 2048, 2048, 36, t3.Decode(t3.MCG))[0]["symbol"] == "t3_dense_gemv_mcg_n0_r32"
+    prep, gemv = t3.plan_linear(17, 2048, 2048, 36, t3.Decode(t3.MCG))  # past 8 rows: the rows rotated once, then the GEMV
+    assert prep["symbol"] == "t3_dense_prep" and prep["grid"][0] == (17 * 16 + 3) // 4 and prep["roles"] == [0, 1, 4]
+    assert gemv["symbol"] == "t3_dense_gemv_mcg_n0_r32" and gemv["roles"][0] == 4  # reads xp
     with pytest.raises(t3.Exl3Error, match="Exl3EngineNotImplemented"):
         t3.plan_linear(33, 2048, 2048, 64)
     with pytest.raises(t3.Exl3Error, match="BadExl3Shape"):

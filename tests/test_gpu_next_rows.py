@@ -204,8 +204,9 @@ def test_the_launch_plan_names_the_kernels_that_run():
     for rows, n, cb in ((1, 64, t3.MUL1), (12, 48, t3.MCG), (30, 36, t3.MUL1)):
         trellis, suh, svh = synth.linear(90, 512, 384, n, scaled=True)
         t3.linear(dev(synth.activations(91, rows, 512)), dev(trellis), dev(suh), dev(svh), t3.Decode(cb))
-        (plan,) = t3.plan_linear(rows, 512, 384, n, t3.Decode(cb))
-        assert t3.last_kernel_symbol() == plan["symbol"], (rows, n, plan)
+        plan = t3.plan_linear(rows, 512, 384, n, t3.Decode(cb))
+        assert len(plan) == (1 if rows <= 8 else 2)
+        assert t3.last_kernel_symbol() == plan[-1]["symbol"], (rows, n, plan)
     H, I, E, n = 256, 128, 8, 32
     bank, _ = make_bank(92, E, H, I, n)
     for rows, topk in ((3, 2), (5, 1)):

@@ -448,7 +448,10 @@ void fill_launch(t3_launch* l, const char* symbol, const char* group, dim3 grid,
 
 size_t t3_linear_workspace_bytes(size_t rows, int in_dim, int out_dim, int n) {
     (void)n;
-    if (rows <= T3_DECODE_ROWS_MAX || in_dim <= 0 || out_dim <= 0) return 0;  // the decode-row kernel keeps everything on chip
+    if (in_dim <= 0 || out_dim <= 0) return 0;
+    if (rows <= kFusedRows) return 0;  // the decode-row kernel keeps everything on chip
+    // 9 to 32 rows: the rows rotated once ahead of the GEMV (optional: without it every CTA rotates its own copy)
+    if (rows <= T3_DECODE_ROWS_MAX) return (rows * (size_t)in_dim * 2u + 255u) & ~(size_t)255u;
     return prefill_linear_workspace(rows, (uint32_t)in_dim, (uint32_t)out_dim);
 }
 
@@ -497,6 +500,11 @@ int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, cons
     a.trace = g_trace;
     a.x = x;
     a.y = y;
+    if (rows > kFusedRows && !cfg.probe && workspace && workspace_bytes >= t3_linear_workspace_bytes(rows, in_dim, out_dim, n)) {
+        a.xp_g = workspace;
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        if (int rc = cuda_status(launch_dense_prep(a, static_cast<cudaStream_t>(stream)))) return rc;
+    }
     if (cfg.probe) {  // a timing probe in the served kernel's place: y is not the linear's output
         if (rows > 8) return T3_ENGINE_NOT_IMPLEMENTED;
         return cuda_status(launch_dense_gemv(a, 1 + cfg.probe, static_cast<cudaStream_t>(stream)));
@@ -528,10 +536,21 @@ int t3_plan_linear(size_t rows, int in_dim, int out_dim, int n, t3_decode dec, t
     const uint32_t rm = row_cap_for(a.rows);
     char symbol[64];
     std::snprintf(symbol, sizeof symbol, "t3_dense_gemv_%s_n%u_r%u", dec.codebook == T3_MCG ? "mcg" : "mul1", named_rate(a.n), rm);
-    fill_launch(&out[0], symbol, "dense", dim3(a.split, a.out / 128u, 1), 32u * 17u,
-                gemv_smem_bytes(rm, a.rows, a.slice_max, a.split, a.n, a.ring), a.split,
-                {T3_ROLE_X, T3_ROLE_Y, T3_ROLE_TRELLIS, T3_ROLE_SUH, T3_ROLE_SVH});
-    return 1;
+    int k = 0;
+    if (a.rows > kFusedRows) {  // with the call's workspace: the rows rotated once ahead of the GEMV
+        if (max_launches < 2) return -T3_BAD_EXL3_SHAPE;
+        fill_launch(&out[k++], "t3_dense_prep", "dense", dim3((a.rows * (a.in / 128u) + 3u) / 4u, 1, 1), 128u, 0u, 1u,
+                    {T3_ROLE_X, T3_ROLE_SUH, T3_ROLE_XP});
+    }
+    if (a.rows > kFusedRows)
+        fill_launch(&out[k++], symbol, "dense", dim3(a.split, a.out / 128u, 1), 32u * 17u,
+                    gemv_smem_bytes(rm, a.rows, a.slice_max, a.split, a.n, a.ring), a.split,
+                    {T3_ROLE_XP, T3_ROLE_Y, T3_ROLE_TRELLIS, T3_ROLE_SVH});
+    else
+        fill_launch(&out[k++], symbol, "dense", dim3(a.split, a.out / 128u, 1), 32u * 17u,
+                    gemv_smem_bytes(rm, a.rows, a.slice_max, a.split, a.n, a.ring), a.split,
+                    {T3_ROLE_X, T3_ROLE_Y, T3_ROLE_TRELLIS, T3_ROLE_SUH, T3_ROLE_SVH});
+    return k;
 }
 
 // ---- routed experts -------------------------------------------------------------------------------------------------

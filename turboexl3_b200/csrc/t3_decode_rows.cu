@@ -29,7 +29,7 @@ constexpr uint32_t kMaxSlots = 1024;  // 32 rows x 32 top-k
 // ---------------------------------------------------------------------------------------------- shared pieces
 
 struct CtaSmem {
-    uint64_t *full, *empty;
+    uint64_t *full, *empty, *xp_full;
     __half* xp;
     float *local, *recv;
     uint8_t* ring;
@@ -39,6 +39,7 @@ __device__ __forceinline__ CtaSmem carve(uint8_t* smem, const GemvSmem& L) {
     CtaSmem c;
     c.full = reinterpret_cast<uint64_t*>(smem + L.bars);
     c.empty = c.full + kMaxStages;
+    c.xp_full = c.full + 2u * kMaxStages;
     c.xp = reinterpret_cast<__half*>(smem + L.xp);
     c.local = reinterpret_cast<float*>(smem + L.local);
     c.recv = reinterpret_cast<float*>(smem + L.recv);
@@ -50,6 +51,10 @@ __device__ __forceinline__ void init_barriers(const CtaSmem& c, uint32_t stages)
     if (threadIdx.x < stages) {  // one thread a stage
         mbar_init(&c.full[threadIdx.x], 1u);
         mbar_init(&c.empty[threadIdx.x], kConsumerWarps);
+        mbar_init_fence();
+    }
+    if (threadIdx.x == kMaxStages) {
+        mbar_init(c.xp_full, 1u);
         mbar_init_fence();
     }
 }
@@ -100,18 +105,40 @@ __device__ __forceinline__ void dense_gemv_body(const DenseArgs& a) {
     if (warp == kConsumerWarps) {
         // the weights do not depend on the stream's previous kernel: start them, then let the next kernel do the same
         const uint8_t* src = a.trellis + ((size_t)(b0 * 8u) * out_tiles + blk * 8u) * tile_bytes;
-        produce_slab(c.ring, c.full, c.empty, src, (size_t)out_tiles * tile_bytes, nrows, row_bytes, rc, pos, lane, a.err);
-        pdl_trigger();
+        const size_t stride = (size_t)out_tiles * tile_bytes;
+        if (a.xp_g == nullptr) {
+            produce_slab(c.ring, c.full, c.empty, src, stride, nrows, row_bytes, rc, pos, lane, a.err);
+            pdl_trigger();
+        } else {
+            // as many stages as the ring holds without waiting for a consumer (who waits for the prepared rows), then the
+            // prepared rows of this CTA's K slice (the previous kernel's output), then the rest of the slab
+            const uint32_t head = min(nrows, rc.stages * kStageRows);
+            produce_slab(c.ring, c.full, c.empty, src, stride, head, row_bytes, rc, pos, lane, a.err);
+            pdl_trigger();
+            pdl_wait();
+            const uint32_t slice_bytes = nblk * 256u;
+            if (lane == 0) mbar_arrive_expect_tx(c.xp_full, a.rows * slice_bytes);
+            __syncwarp();
+            if (lane < a.rows)
+                bulk_copy_g2s(c.xp + lane * xstride, static_cast<const __half*>(a.xp_g) + (size_t)lane * a.in + b0 * 128u, slice_bytes,
+                              c.xp_full);
+            produce_slab(c.ring, c.full, c.empty, src + (size_t)head * stride, stride, nrows - head, row_bytes, rc, pos, lane, a.err);
+        }
     } else {
         pdl_trigger();
         load_scales(static_cast<const __half*>(a.svh) + blk * 128u, lane, sv);  // weights-side: ahead of the wait
-        if (warp == 0) prefetch_l2(static_cast<const __half*>(a.suh) + b0 * 128u, nblk * 256u, lane);
-        pdl_wait();  // x may be the previous kernel's output
-        for (uint32_t task = warp; task < a.rows * nblk; task += kConsumerWarps) {
-            const uint32_t row = task / nblk, b = task - row * nblk;
-            const uint32_t k0 = (b0 + b) * 128u;
-            prepare_block(a.x, a.x_dt, (size_t)row * a.in + k0, static_cast<const __half*>(a.suh) + k0,
-                          c.xp + row * xstride + b * 128u, lane);
+        if (a.xp_g == nullptr) {
+            if (warp == 0) prefetch_l2(static_cast<const __half*>(a.suh) + b0 * 128u, nblk * 256u, lane);
+            pdl_wait();  // x may be the previous kernel's output
+            for (uint32_t task = warp; task < a.rows * nblk; task += kConsumerWarps) {
+                const uint32_t row = task / nblk, b = task - row * nblk;
+                const uint32_t k0 = (b0 + b) * 128u;
+                prepare_block(a.x, a.x_dt, (size_t)row * a.in + k0, static_cast<const __half*>(a.suh) + k0,
+                              c.xp + row * xstride + b * 128u, lane);
+            }
+        } else {
+            pdl_wait();
+            mbar_wait_report(smem_addr(c.xp_full), 0u, a.err, kErrFullWait);
         }
         named_sync(1, kConsumerThreads);
         if (traced && tid == 0) {
@@ -499,6 +526,18 @@ T3_ALL_RATES(t3_dec_down, moe_down_body, MoeArgs)
 #endif
 #if T3_CB == 0
 extern "C" __global__ void __launch_bounds__(256) t3_dec_merge(const MoeArgs a) { moe_merge_body(a); }
+
+// grid (ceil(rows in/128 / 4)), 128 threads: a warp one (row, 128-block) of the input rotation into a.xp_g
+extern "C" __global__ void __launch_bounds__(128) t3_dense_prep(const DenseArgs a) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, nb = a.in / 128u;
+    const uint32_t task = blockIdx.x * 4u + warp;
+    pdl_trigger();  // the GEMV that follows starts its weight stream now
+    pdl_wait();     // x may be the previous kernel's output; the prepared rows' last reader has finished
+    if (task >= a.rows * nb) return;
+    const uint32_t row = task / nb, b = task - row * nb;
+    prepare_block(a.x, a.x_dt, (size_t)row * a.in + b * 128u, static_cast<const __half*>(a.suh) + b * 128u,
+                  static_cast<__half*>(const_cast<void*>(a.xp_g)) + (size_t)row * a.in + b * 128u, lane);
+}
 #endif
 
 #if T3_SERVED
@@ -528,6 +567,21 @@ cudaError_t T3_CAT(launch_dense_gemv_cb, T3_CB)(const DenseArgs& a, cudaStream_t
     return launch_cluster(fn, a, dim3(a.split, a.out / 128u, 1), a.split, gemv_smem_bytes(rm, a.rows, a.slice_max, a.split, a.n, a.ring),
                           a.overlap != 0, stream);
 }
+
+#if T3_CB == 0
+cudaError_t launch_dense_prep(const DenseArgs& a, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((a.rows * (a.in / 128u) + 3u) / 4u, 1, 1);
+    cfg.blockDim = dim3(128, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = a.overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, t3_dense_prep, a);
+}
+#endif
 
 #if T3_SERVED
 cudaError_t T3_CAT(launch_moe_gate_up_cb, T3_CB)(const MoeArgs& a, cudaStream_t stream) {

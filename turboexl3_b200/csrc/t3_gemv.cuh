@@ -57,7 +57,7 @@ __host__ __device__ inline GemvSmem gemv_smem(uint32_t rm, uint32_t xrows, uint3
                                               uint32_t stages) {
     GemvSmem s;
     s.bars = 0;
-    s.xp = 2u * kMaxStages * 8u;
+    s.xp = 2u * kMaxStages * 8u + 128u;  // the ring's full and empty barriers, then one for prepared rows copied in
     const uint32_t xp_bytes = xrows * (slice_k + kXpPad) * 2u;
     s.local = s.xp + ((xp_bytes + 127u) & ~127u);
     s.recv = s.local + ((rm * kPartialStride * 4u + 127u) & ~127u);

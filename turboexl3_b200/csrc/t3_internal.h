@@ -14,6 +14,8 @@ struct RingPlan {
 // One dense linear at decode rows (rows <= 32)
 struct DenseArgs {
     const void* x;            // [rows, in], dtype x_dt
+    const void* xp_g;         // or null: the rows already prepared (f16 [rows, in], lane order inside every 16) by t3_dense_prep,
+                              // which the CTAs copy in instead of rotating x themselves (calls of more than 8 rows)
     void* y;                  // [rows, out], dtype x_dt
     const uint8_t* trellis;   // [in/16, out/16, n] u16
     const void* suh;          // f16 [in]
@@ -69,6 +71,9 @@ struct MoeArgs {
 void note_symbol(const void* kernel);
 
 cudaError_t launch_dense_gemv(const DenseArgs& a, int codebook, cudaStream_t stream);
+// the input rotation of every row once, into a.xp_g (ahead of launch_dense_gemv on the same stream)
+cudaError_t launch_dense_prep(const DenseArgs& a, cudaStream_t stream);
+constexpr uint32_t kFusedRows = 8;  // up to this many rows a dense decode-row CTA rotates x itself
 cudaError_t launch_moe_gate_up(const MoeArgs& a, int codebook, cudaStream_t stream);
 cudaError_t launch_moe_down(const MoeArgs& a, int codebook, cudaStream_t stream);
 cudaError_t launch_moe_merge(const MoeArgs& a, cudaStream_t stream);
