@@ -278,3 +278,33 @@ def test_timing_probes_run_in_the_served_kernels_place():
     finally:
         t3.configure()
     assert torch.equal(t3.linear(*args), served)
+
+
+def test_large_linear_global_exchange_matches_the_cluster_kernel_within_bars():
+    """Linears of 24 MB of codes and up, given their workspace, let the K slices' sums meet in global memory (any slice
+    count, CTAs placed one by one); without the workspace the cluster kernel runs. Different K partitions, so not the same
+    bytes, but each within the dense bars of the oracle; the same call twice gives the same bytes."""
+    in_dim, out_dim, n = 16384, 7168, 32  # K2: 29 MB of codes
+    L = t3.lib()
+    assert L.t3_linear_workspace_bytes(1, in_dim, out_dim, n) > 0
+    plan = t3.plan_linear(1, in_dim, out_dim, n)
+    assert plan[-1]["cluster"] == 1 and plan[-1]["grid"][0] not in (1, 2, 4, 8, 16)
+    rng = np.random.default_rng(5)
+    trellis = rng.integers(0, 65536, size=(in_dim // 16, out_dim // 16, n), dtype=np.uint16)
+    _, suh, svh = synth.linear(6, in_dim, 128, 16)
+    svh = np.where(rng.random(out_dim) < 0.5, -1.0, 1.0).astype(np.float16)
+    what = ob.reconstruct_inner(trellis, in_dim, out_dim, n, ob.MUL1)
+    for rows in (1, 7):
+        x = synth.activations(7, rows, in_dim)
+        args = (dev(x), dev(trellis.view(np.int16)), dev(suh), dev(svh))
+        y = t3.linear(*args)  # api.linear brings the workspace
+        assert t3.last_kernel_symbol().startswith("t3_dense_gemv_mul1_n32")
+        assert torch.equal(y, t3.linear(*args))
+        yb = torch.empty_like(y)
+        rc = L.t3_linear(args[0].data_ptr(), 1, rows, args[1].data_ptr(), args[2].data_ptr(), args[3].data_ptr(), in_dim, out_dim, n,
+                         t3.Decode.mul1._c(), yb.data_ptr(), None, 0, torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        ref = ob.linear_rows_what(x.astype(np.float32), what, suh, svh, in_dim, out_dim)
+        for got in (y, yb):
+            check(host_f32(got), ref, "f16", f"large_linear_rows{rows}")
+    assert t3.device_error() == 0

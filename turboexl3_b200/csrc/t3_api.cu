@@ -410,16 +410,66 @@ int t3_codebook_table(t3_decode dec, void* out, void* stream) {
 // ---- dense linear ---------------------------------------------------------------------------------------------------
 
 namespace {
+// Linears of 24 MB of codes and up with their workspace: any slice count s, CTAs placed one by one (no cluster), the slices'
+// sums meeting in global memory. The cost of a count: the CTAs of the fullest multiprocessor times a slice's 128-input blocks
+// (all CTAs resident at once, two a multiprocessor). Returns 0 when no count beats the cluster kernel's by a tenth (the
+// global exchange costs a couple of microseconds a launch).
+uint32_t pick_split_global(uint32_t nb, uint32_t out_blocks, uint32_t cluster_split) {
+    const uint32_t sms = one_wave() / 2u;
+    auto cost_of = [&](uint32_t s) { return ((out_blocks * s + sms - 1u) / sms) * ((nb + s - 1u) / s); };
+    uint32_t best_s = 0, best = cost_of(cluster_split) * 9u / 10u;
+    for (uint32_t s = 2; s <= 16u && s <= nb; ++s) {
+        if (out_blocks * s > 2u * sms) break;
+        const uint32_t cost = cost_of(s);
+        if (cost < best) best = cost, best_s = s;
+    }
+    return best_s;
+}
+
+size_t align256(size_t v) { return (v + 255u) & ~(size_t)255u; }
+
+// The workspace of a dense linear at decode rows, in this order: the rows rotated ahead of the GEMV (more than kFusedRows
+// rows), the slices' partial sums and the blocks' arrival counters (large linears on the global exchange).
+struct DenseWs {
+    size_t xp, part, counters, total;
+};
+DenseWs dense_ws(uint32_t rows, uint32_t in, uint32_t out, uint32_t global_split) {
+    DenseWs w;
+    w.xp = 0;
+    w.part = rows > kFusedRows ? align256((size_t)rows * in * 2u) : 0u;
+    w.counters = w.part + (global_split ? align256((size_t)(out / 128u) * global_split * rows * 512u) : 0u);
+    w.total = w.counters + (global_split ? align256((size_t)(out / 128u) * 4u) : 0u);
+    return w;
+}
+
+bool large_linear(uint32_t in, uint32_t out, uint32_t n) { return (uint64_t)in * out * n >= (uint64_t)24u * 1024u * 1024u * 128u; }
+
 // The launch shape of a dense linear at decode rows: the K split (cluster size) and the code ring. a.rows, in, out, n set.
-int plan_dense(DenseArgs& a, const t3_config& cfg) {
+// global_ok: the call has its workspace, so a large linear may take the global exchange (a.part is set non-null as a mark;
+// the caller points it into the workspace).
+int plan_dense(DenseArgs& a, const t3_config& cfg, bool global_ok) {
     const uint32_t nb = a.in / 128u;
-    const bool large = (uint64_t)a.in * a.out * a.n >= (uint64_t)24u * 1024u * 1024u * 128u;  // 24 MB of codes and up
+    const bool large = large_linear(a.in, a.out, a.n);
     a.split = cfg.dense_split ? (cfg.dense_split < nb ? cfg.dense_split : nb)
                               : (large ? pick_split_large(nb, a.out / 128u) : pick_split(nb, a.out / 128u, 1u, 8u, one_wave() / 2u));
+    a.part = nullptr;
+    if (large && global_ok && !cfg.dense_split && !cfg.probe) {
+        const uint32_t s = pick_split_global(nb, a.out / 128u, a.split);
+        if (s) {
+            a.split = s;
+            a.part = reinterpret_cast<float*>(1);  // a mark: the caller sets the pointer
+        }
+    }
     a.overlap = !cfg.no_overlap;
     a.slice_max = largest_slice(nb, a.split);
     // a slice too long for shared memory (its prepared rows) is cut further, up to the widest cluster
-    while (!plan_ring(row_cap_for(a.rows), a.rows, a.slice_max, a.split, a.n, a.ring)) {
+    while (!plan_ring(row_cap_for(a.rows), a.rows, a.slice_max, a.part ? 1u : a.split, a.n, a.ring)) {
+        if (a.part) {  // back to the cluster kernel
+            a.part = nullptr;
+            a.split = pick_split_large(nb, a.out / 128u);
+            a.slice_max = largest_slice(nb, a.split);
+            continue;
+        }
         if (a.split * 2u > nb || a.split * 2u > 16u) return T3_ENGINE_NOT_IMPLEMENTED;
         a.split *= 2u;
         a.slice_max = largest_slice(nb, a.split);
@@ -447,12 +497,21 @@ void fill_launch(t3_launch* l, const char* symbol, const char* group, dim3 grid,
 
 
 size_t t3_linear_workspace_bytes(size_t rows, int in_dim, int out_dim, int n) {
-    (void)n;
-    if (in_dim <= 0 || out_dim <= 0) return 0;
-    if (rows <= kFusedRows) return 0;  // the decode-row kernel keeps everything on chip
-    // 9 to 32 rows: the rows rotated once ahead of the GEMV (optional: without it every CTA rotates its own copy)
-    if (rows <= T3_DECODE_ROWS_MAX) return (rows * (size_t)in_dim * 2u + 255u) & ~(size_t)255u;
-    return prefill_linear_workspace(rows, (uint32_t)in_dim, (uint32_t)out_dim);
+    if (in_dim <= 0 || out_dim <= 0 || rows < 1) return 0;
+    if (rows > T3_DECODE_ROWS_MAX) return prefill_linear_workspace(rows, (uint32_t)in_dim, (uint32_t)out_dim);
+    if (in_dim % 128 != 0 || out_dim % 128 != 0 || !rate_ok(n)) return 0;
+    // Decode rows. Up to 8 rows of an ordinary linear: nothing (the kernel keeps everything on chip). 9 to 32 rows: the rows
+    // rotated once ahead of the GEMV. Linears of 24 MB of codes and up: the K slices' partial sums, when a slice count that
+    // fills the multiprocessors evenly exists for the shape. All optional: a call without it takes the cluster kernel.
+    t3_config cfg;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        cfg = g_cfg;
+    }
+    DenseArgs a = {};
+    a.in = (uint32_t)in_dim, a.out = (uint32_t)out_dim, a.n = (uint32_t)n, a.rows = (uint32_t)rows;
+    if (plan_dense(a, cfg, true) != T3_OK) return 0;
+    return dense_ws(a.rows, a.in, a.out, a.part ? a.split : 0u).total;
 }
 
 int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, const void* suh, const void* svh,
@@ -495,12 +554,24 @@ int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, cons
     a.x_dt = x_dtype;
     note_engine(1, (uint64_t)in_dim, (uint64_t)out_dim, (uint64_t)n, 0);
     a.rows = (uint32_t)rows;
-    if (int rc = plan_dense(a, cfg)) return rc;
+    if (int rc = plan_dense(a, cfg, workspace != nullptr)) return rc;
+    DenseWs ws = dense_ws(a.rows, a.in, a.out, a.part ? a.split : 0u);
+    bool has_ws = workspace != nullptr && workspace_bytes >= ws.total;
+    if (a.part && !has_ws) {  // too small for the global exchange: the cluster kernel, with the rotated rows if those fit
+        if (int rc = plan_dense(a, cfg, false)) return rc;
+        ws = dense_ws(a.rows, a.in, a.out, 0u);
+        has_ws = workspace != nullptr && workspace_bytes >= ws.total;
+    }
     a.err = dev_error_ptr();
     a.trace = g_trace;
+    if (a.part) {
+        a.part = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + ws.part);
+        a.counters = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(workspace) + ws.counters);
+        if (int rc = cuda_status(cudaMemsetAsync(a.counters, 0, (size_t)(a.out / 128u) * 4u, static_cast<cudaStream_t>(stream)))) return rc;
+    }
     a.x = x;
     a.y = y;
-    if (rows > kFusedRows && !cfg.probe && workspace && workspace_bytes >= t3_linear_workspace_bytes(rows, in_dim, out_dim, n)) {
+    if (rows > kFusedRows && !cfg.probe && has_ws) {
         a.xp_g = workspace;
         g_launches.fetch_add(1, std::memory_order_relaxed);
         if (int rc = cuda_status(launch_dense_prep(a, static_cast<cudaStream_t>(stream)))) return rc;
@@ -532,7 +603,7 @@ int t3_plan_linear(size_t rows, int in_dim, int out_dim, int n, t3_decode dec, t
     }
     DenseArgs a = {};
     a.in = (uint32_t)in_dim, a.out = (uint32_t)out_dim, a.n = (uint32_t)n, a.rows = (uint32_t)rows;
-    if (int rc = plan_dense(a, cfg)) return -rc;
+    if (int rc = plan_dense(a, cfg, true)) return -rc;
     const uint32_t rm = row_cap_for(a.rows);
     char symbol[64];
     std::snprintf(symbol, sizeof symbol, "t3_dense_gemv_%s_n%u_r%u", dec.codebook == T3_MCG ? "mcg" : "mul1", named_rate(a.n), rm);
@@ -544,12 +615,13 @@ int t3_plan_linear(size_t rows, int in_dim, int out_dim, int n, t3_decode dec, t
     }
     if (a.rows > kFusedRows)
         fill_launch(&out[k++], symbol, "dense", dim3(a.split, a.out / 128u, 1), 32u * 17u,
-                    gemv_smem_bytes(rm, a.rows, a.slice_max, a.split, a.n, a.ring), a.split,
+                    gemv_smem_bytes(rm, a.rows, a.slice_max, a.part ? 1u : a.split, a.n, a.ring), a.part ? 1u : a.split,
                     {T3_ROLE_XP, T3_ROLE_Y, T3_ROLE_TRELLIS, T3_ROLE_SVH});
     else
         fill_launch(&out[k++], symbol, "dense", dim3(a.split, a.out / 128u, 1), 32u * 17u,
-                    gemv_smem_bytes(rm, a.rows, a.slice_max, a.split, a.n, a.ring), a.split,
+                    gemv_smem_bytes(rm, a.rows, a.slice_max, a.part ? 1u : a.split, a.n, a.ring), a.part ? 1u : a.split,
                     {T3_ROLE_X, T3_ROLE_Y, T3_ROLE_TRELLIS, T3_ROLE_SUH, T3_ROLE_SVH});
+    if (a.part) out[k - 1].roles[out[k - 1].nroles++] = T3_ROLE_Z;  // the slices' partial sums meet in global memory
     return k;
 }
 
@@ -569,8 +641,6 @@ int validate_bank(const t3_bank* b, int hidden_of_x) {
     if (b->n_gate != b->n_down) return T3_ENGINE_NOT_IMPLEMENTED;  // src/root.zig:841
     return T3_OK;
 }
-
-size_t align256(size_t v) { return (v + 255u) & ~(size_t)255u; }
 
 // The routed chain at decode rows on filled arguments (geometry, rows, top-k, pointers): plans the launches and records
 // them. workspace: t3_moe_workspace_bytes(rows, topk, bank) bytes.

@@ -78,13 +78,15 @@ __device__ __forceinline__ void gemv_and_push(cg::cluster_group& cluster, const 
 
 // ---------------------------------------------------------------------------------------------- dense linear
 
-// grid (split, out / 128), cluster (split, 1, 1)
+// grid (split, out / 128), cluster (split, 1, 1) — or no cluster when the partial sums meet in global memory (a.part)
 template <int N, int RM>
 __device__ __forceinline__ void dense_gemv_body(const DenseArgs& a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* smem = aligned_smem(smem_raw);
+    __shared__ uint32_t s_last;
     cg::cluster_group cluster = cg::this_cluster();
-    const uint32_t rank = cluster.block_rank(), csize = a.split, blk = blockIdx.y;
+    const bool global = a.part != nullptr;
+    const uint32_t rank = global ? blockIdx.x : cluster.block_rank(), csize = global ? 1u : a.split, blk = blockIdx.y;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     uint32_t b0, b1;
     slice_blocks(a.in / 128u, a.split, rank, b0, b1);
@@ -146,9 +148,59 @@ __device__ __forceinline__ void dense_gemv_body(const DenseArgs& a) {
             mbar_wait(&c.full[0], 0u);
             a.trace[3] = clock64();
         }
-        gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, a.rows, pos, a.rows, rank, csize, warp, lane, a.err);
+        if (!global) {
+            gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, a.rows, pos, a.rows, rank, csize, warp, lane, a.err);
+        } else {
+            // the slice's sums to global memory; the block's last arriver adds the slices in slice order and finishes
+            const uint32_t tcol = warp & (kTileWarps - 1u), kg = warp / kTileWarps;
+            float acc[RowCap<RM>::kMB][2][4] = {};
+            consume_slab<N, CB, RM>(c.ring, c.full, c.empty, nrows, a.n, a.mask, rc, c.xp, xstride, a.rows, pos, tcol, kg, lane, acc, a.err);
+            if (kg == 1) store_local<RM>(c.local, acc, tcol, lane);
+            named_sync(1, kConsumerThreads);
+            if (kg == 0) {
+                const uint32_t g = lane >> 2, q = lane & 3u;
+                float* mine = a.part + ((size_t)blk * a.split + rank) * a.rows * 128u;
+#pragma unroll
+                for (int mb = 0; mb < RowCap<RM>::kMB; ++mb)
+#pragma unroll
+                    for (int h = 0; h < (RowCap<RM>::kHalf ? 1 : 2); ++h) {
+                        const uint32_t m = mb * 16 + h * 8 + g;
+                        if (m >= a.rows) continue;
+#pragma unroll
+                        for (int nt = 0; nt < 2; ++nt) {
+                            const uint32_t col = tcol * 16u + nt * 8u + 2u * q;
+                            const float2 o = *reinterpret_cast<const float2*>(c.local + m * kPartialStride + col);
+                            __stcg(reinterpret_cast<float2*>(mine + m * 128u + col),
+                                   make_float2(acc[mb][nt][2 * h] + o.x, acc[mb][nt][2 * h + 1] + o.y));
+                        }
+                    }
+            }
+            __threadfence();
+            named_sync(1, kConsumerThreads);
+            if (tid == 0) s_last = atomicAdd(&a.counters[blk], 1u) == a.split - 1u;
+            named_sync(1, kConsumerThreads);
+            if (!s_last) return;
+            __threadfence();
+            for (uint32_t row = warp; row < a.rows; row += kConsumerWarps) {
+                float v[4];
+                for (uint32_t r = 0; r < a.split; ++r) {
+                    const float* src = a.part + (((size_t)blk * a.split + r) * a.rows + row) * 128u + lane;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float t = __ldcg(src + 32 * j);
+                        v[j] = r == 0u ? t : v[j] + t;
+                    }
+                }
+                finish_block(v, sv, lane);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) store_act(a.y, a.x_dt, (size_t)row * a.out + blk * 128u + lane + 32u * j, v[j]);
+            }
+            if (tid == 0) a.counters[blk] = 0u;  // as the next call on this workspace expects it
+            return;
+        }
         if (traced && tid == 0) a.trace[4] = clock64();
     }
+    if (global) return;  // the copy warp: its copies have landed (the consumers waited for each)
     cluster_arrive();
     if (rank >= a.rows) return;  // owns no row: nothing reads this CTA's shared memory after its arrival
     cluster_wait();
@@ -564,7 +616,8 @@ extern "C" __global__ void __launch_bounds__(128) t3_dense_prep(const DenseArgs 
 cudaError_t T3_CAT(launch_dense_gemv_cb, T3_CB)(const DenseArgs& a, cudaStream_t stream) {
     const uint32_t rm = row_cap_for(a.rows);
     KernelFn<DenseArgs> fn = T3_PICK(t3_dense_gemv, a.n, rm);
-    return launch_cluster(fn, a, dim3(a.split, a.out / 128u, 1), a.split, gemv_smem_bytes(rm, a.rows, a.slice_max, a.split, a.n, a.ring),
+    const uint32_t cluster = a.part ? 1u : a.split;
+    return launch_cluster(fn, a, dim3(a.split, a.out / 128u, 1), cluster, gemv_smem_bytes(rm, a.rows, a.slice_max, cluster, a.n, a.ring),
                           a.overlap != 0, stream);
 }
 

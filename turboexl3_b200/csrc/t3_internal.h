@@ -22,7 +22,11 @@ struct DenseArgs {
     const void* svh;          // f16 [out]
     uint32_t rows, in, out, n, mask;
     int x_dt;
-    uint32_t split;           // cluster size: K slices
+    float* part;              // or null. Set: the K slices' partial sums meet in global memory, [out/128][split][rows][128] f32, not
+                              // in a cluster's shared memory (any slice count, CTAs placed one by one: large linears whose
+                              // CTA count then fills the multiprocessors evenly)
+    uint32_t* counters;       // with part: [out/128] arrivals a block, zero before the launch; the last arriver finishes the block
+    uint32_t split;           // K slices (the cluster size unless `part` is set)
     uint32_t slice_max;       // inputs of the largest K slice
     RingPlan ring;
     int overlap;              // launch with the programmatic-dependent-launch attribute
