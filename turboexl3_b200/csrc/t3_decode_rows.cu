@@ -158,22 +158,18 @@ __device__ __forceinline__ void dense_gemv_body(const DenseArgs& a) {
             if (kg == 1) store_local<RM>(c.local, acc, tcol, lane);
             named_sync(1, kConsumerThreads);
             if (kg == 0) {
-                const uint32_t g = lane >> 2, q = lane & 3u;
                 float* mine = a.part + ((size_t)blk * a.split + rank) * a.rows * 128u;
 #pragma unroll
                 for (int mb = 0; mb < RowCap<RM>::kMB; ++mb)
 #pragma unroll
-                    for (int h = 0; h < (RowCap<RM>::kHalf ? 1 : 2); ++h) {
-                        const uint32_t m = mb * 16 + h * 8 + g;
-                        if (m >= a.rows) continue;
+                    for (int nt = 0; nt < Frags<RM>::kNt; ++nt)
 #pragma unroll
-                        for (int nt = 0; nt < 2; ++nt) {
-                            const uint32_t col = tcol * 16u + nt * 8u + 2u * q;
-                            const float2 o = *reinterpret_cast<const float2*>(c.local + m * kPartialStride + col);
-                            __stcg(reinterpret_cast<float2*>(mine + m * 128u + col),
-                                   make_float2(acc[mb][nt][2 * h] + o.x, acc[mb][nt][2 * h + 1] + o.y));
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t m = fragment_row<RM>(lane, mb, e);
+                            if (m >= a.rows) continue;
+                            const uint32_t col = tcol * 16u + fragment_col<RM>(lane, nt, e);
+                            __stcg(mine + m * 128u + col, acc[mb][nt][e] + c.local[m * kPartialStride + col]);
                         }
-                    }
             }
             __threadfence();
             named_sync(1, kConsumerThreads);

@@ -127,15 +127,24 @@ struct RowOffsets {
     }
 };
 
-// one decoded tile times the prepared rows at inputs [16 tk, 16 tk + 16): xk points at the lane's columns there, row 0
+// one decoded tile times the prepared rows at inputs [16 tk, 16 tk + 16): xk points at the lane's columns there, row 0.
+// Up to 8 rows (RM = 8) the product is taken TRANSPOSED, (W tile)^T (16 outputs x 16 inputs) times x^T (16 inputs x 8 rows):
+// the decoded words, which are the B fragments of the tile's two column halves, are in another order exactly the A fragment
+// of the transposed tile, and the lane's 8-byte load of a prepared row is the whole B fragment. One tensor-core step a tile
+// instead of two, four accumulators instead of eight, and no register is moved or zeroed to build an operand. The
+// accumulators are then acc[0][0][e + 2 half] = (row 2q + e, column g + 8 half) of the tile (see store_local, push_partial).
 template <int RM>
 __device__ __forceinline__ void mma_tile(float (&acc)[RowCap<RM>::kMB][2][4], const __half* xk, const RowOffsets<RM>& ro,
                                          const uint32_t (&b)[4]) {
+    if (RowCap<RM>::kHalf) {
+        const uint2 lo = *reinterpret_cast<const uint2*>(xk + ro.lo[0]);
+        mma16816(acc[0][0], b[0], b[2], b[1], b[3], lo.x, lo.y);
+        return;
+    }
 #pragma unroll
     for (int mb = 0; mb < RowCap<RM>::kMB; ++mb) {
         const uint2 lo = *reinterpret_cast<const uint2*>(xk + ro.lo[mb]);
-        uint2 hi = make_uint2(0u, 0u);
-        if (!RowCap<RM>::kHalf) hi = *reinterpret_cast<const uint2*>(xk + ro.hi[mb]);
+        const uint2 hi = *reinterpret_cast<const uint2*>(xk + ro.hi[mb]);
         mma16816(acc[mb][0], lo.x, hi.x, lo.y, hi.y, b[0], b[1]);
         mma16816(acc[mb][1], lo.x, hi.x, lo.y, hi.y, b[2], b[3]);
     }
@@ -210,21 +219,33 @@ __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full
 
 // ---- the cluster reduce-scatter -----------------------------------------------------------------------------------
 
+// Where a lane's accumulators sit in a [rows][128] tile of partial sums: element e of the fragment that covers tile column
+// half `nt` (and, past 8 rows, 16-row block mb) is row fragment_row, column tcol * 16 + fragment_col
+template <int RM>
+__device__ __forceinline__ uint32_t fragment_row(uint32_t lane, int mb, int e) {
+    return RowCap<RM>::kHalf ? 2u * (lane & 3u) + (uint32_t)(e & 1) : (uint32_t)mb * 16u + (lane >> 2) + ((e & 2) ? 8u : 0u);
+}
+template <int RM>
+__device__ __forceinline__ uint32_t fragment_col(uint32_t lane, int nt, int e) {
+    return RowCap<RM>::kHalf ? (lane >> 2) + ((e & 2) ? 8u : 0u) : (uint32_t)nt * 8u + 2u * (lane & 3u) + (uint32_t)(e & 1);
+}
+// the fragments a lane holds: one (transposed) up to 8 rows, else two column halves a 16-row block
+template <int RM>
+struct Frags {
+    static constexpr int kNt = RowCap<RM>::kHalf ? 1 : 2;
+};
+
 // K group 1's accumulators into the CTA's local tile [RM][kPartialStride]
 template <int RM>
 __device__ __forceinline__ void store_local(float* local, const float (&acc)[RowCap<RM>::kMB][2][4], uint32_t tcol,
                                             uint32_t lane) {
-    const uint32_t g = lane >> 2, q = lane & 3u;
 #pragma unroll
     for (int mb = 0; mb < RowCap<RM>::kMB; ++mb)
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            const uint32_t col = tcol * 16u + nt * 8u + 2u * q;
-            *reinterpret_cast<float2*>(local + (mb * 16 + g) * kPartialStride + col) = make_float2(acc[mb][nt][0], acc[mb][nt][1]);
-            if (!RowCap<RM>::kHalf)
-                *reinterpret_cast<float2*>(local + (mb * 16 + g + 8) * kPartialStride + col) =
-                    make_float2(acc[mb][nt][2], acc[mb][nt][3]);
-        }
+        for (int nt = 0; nt < Frags<RM>::kNt; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                local[fragment_row<RM>(lane, mb, e) * kPartialStride + tcol * 16u + fragment_col<RM>(lane, nt, e)] = acc[mb][nt][e];
 }
 
 // K group 0 adds group 1's tile to its accumulators and pushes each live row m (< count) to the CTA that owns it,
@@ -234,22 +255,19 @@ template <int RM>
 __device__ __forceinline__ void push_partial(cg::cluster_group& cluster, float* recv, const float* local,
                                              const float (&acc)[RowCap<RM>::kMB][2][4], uint32_t count, uint32_t rank,
                                              uint32_t csize, uint32_t tcol, uint32_t lane) {
-    const uint32_t g = lane >> 2, q = lane & 3u;
     const uint32_t owned = rows_owned(RM, csize);
 #pragma unroll
     for (int mb = 0; mb < RowCap<RM>::kMB; ++mb)
 #pragma unroll
-        for (int h = 0; h < (RowCap<RM>::kHalf ? 1 : 2); ++h) {
-            const uint32_t m = mb * 16 + h * 8 + g;
-            if (m >= count) continue;
-            float* dst = cluster.map_shared_rank(recv, m % csize) + (rank * owned + m / csize) * kPartialStride;
+        for (int nt = 0; nt < Frags<RM>::kNt; ++nt)
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                const uint32_t col = tcol * 16u + nt * 8u + 2u * q;
-                const float2 o = *reinterpret_cast<const float2*>(local + m * kPartialStride + col);
-                *reinterpret_cast<float2*>(dst + col) = make_float2(acc[mb][nt][2 * h] + o.x, acc[mb][nt][2 * h + 1] + o.y);
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t m = fragment_row<RM>(lane, mb, e);
+                if (m >= count) continue;
+                const uint32_t col = tcol * 16u + fragment_col<RM>(lane, nt, e);
+                float* dst = cluster.map_shared_rank(recv, m % csize) + (rank * owned + m / csize) * kPartialStride;
+                dst[col] = acc[mb][nt][e] + local[m * kPartialStride + col];
             }
-        }
 }
 
 // Sum over ranks first, first + step, ... (count of them) of owned row `slot`, for the lane's columns lane + 32 j
