@@ -488,6 +488,8 @@ def run_case(args) -> None:
         _, suh, svh = synth.linear(7, i, o, 16)
         suh_d, svh_d = dev(suh), dev(svh)
         x = dev(synth.activations(9, min(max(args.rows, 1), 32), i))
+        if args.probe:
+            t3.configure(probe=args.probe)
         run = lambda: [t3.linear(x, w, suh_d, svh_d) for w in ws]
         per = copies
     else:
@@ -798,6 +800,8 @@ def main() -> None:
                     help="run one case eagerly --steps times and exit (for profilers)")
     ap.add_argument("--rows", type=int, default=1, help="rows of --case")
     ap.add_argument("--shape", default="16384x7168x4", help="INxOUTxK of --case dense_decode")
+    ap.add_argument("--probe", type=int, default=0, choices=[0, 1, 2, 3],
+                    help="--case dense_decode with the kernel's timing probe in the served kernel's place (t3_config.probe)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

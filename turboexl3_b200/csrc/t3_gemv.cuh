@@ -116,35 +116,47 @@ __device__ __forceinline__ void produce_slab(uint8_t* ring, uint64_t* full, uint
 // tensor-core step's A operand, a row past the last live one read from the last live one
 template <int RM>
 struct RowOffsets {
-    uint32_t lo[RowCap<RM>::kMB], hi[RowCap<RM>::kMB];
+    uint32_t lo[RowCap<RM>::kMB], hi[RowCap<RM>::kMB];  // byte offsets
     __device__ __forceinline__ void init(uint32_t lane, uint32_t live, uint32_t xstride) {
         const uint32_t g = lane >> 2, last = live - 1u;
 #pragma unroll
         for (int mb = 0; mb < RowCap<RM>::kMB; ++mb) {
-            lo[mb] = min((uint32_t)mb * 16u + g, last) * xstride;
-            hi[mb] = min((uint32_t)mb * 16u + 8u + g, last) * xstride;
+            lo[mb] = min((uint32_t)mb * 16u + g, last) * xstride * 2u;
+            hi[mb] = min((uint32_t)mb * 16u + 8u + g, last) * xstride * 2u;
         }
     }
 };
 
-// one decoded tile times the prepared rows at inputs [16 tk, 16 tk + 16): xk points at the lane's columns there, row 0.
+// loads from this CTA's shared memory by 32-bit shared address (constant parts of an address fold into the instruction)
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
+// one decoded tile times the prepared rows at inputs [16 tk, 16 tk + 16): xk is the shared address of the lane's columns there, row 0.
 // Up to 8 rows (RM = 8) the product is taken TRANSPOSED, (W tile)^T (16 outputs x 16 inputs) times x^T (16 inputs x 8 rows):
 // the decoded words, which are the B fragments of the tile's two column halves, are in another order exactly the A fragment
 // of the transposed tile, and the lane's 8-byte load of a prepared row is the whole B fragment. One tensor-core step a tile
 // instead of two, four accumulators instead of eight, and no register is moved or zeroed to build an operand. The
 // accumulators are then acc[0][0][e + 2 half] = (row 2q + e, column g + 8 half) of the tile (see store_local, push_partial).
 template <int RM>
-__device__ __forceinline__ void mma_tile(float (&acc)[RowCap<RM>::kMB][2][4], const __half* xk, const RowOffsets<RM>& ro,
+__device__ __forceinline__ void mma_tile(float (&acc)[RowCap<RM>::kMB][2][4], uint32_t xk, const RowOffsets<RM>& ro,
                                          const uint32_t (&b)[4]) {
     if (RowCap<RM>::kHalf) {
-        const uint2 lo = *reinterpret_cast<const uint2*>(xk + ro.lo[0]);
+        const uint2 lo = lds_u64(xk + ro.lo[0]);
         mma16816(acc[0][0], b[0], b[2], b[1], b[3], lo.x, lo.y);
         return;
     }
 #pragma unroll
     for (int mb = 0; mb < RowCap<RM>::kMB; ++mb) {
-        const uint2 lo = *reinterpret_cast<const uint2*>(xk + ro.lo[mb]);
-        const uint2 hi = *reinterpret_cast<const uint2*>(xk + ro.hi[mb]);
+        const uint2 lo = lds_u64(xk + ro.lo[mb]);
+        const uint2 hi = lds_u64(xk + ro.hi[mb]);
         mma16816(acc[mb][0], lo.x, hi.x, lo.y, hi.y, b[0], b[1]);
         mma16816(acc[mb][1], lo.x, hi.x, lo.y, hi.y, b[2], b[3]);
     }
@@ -172,47 +184,52 @@ __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full
     uint32_t woff[kRaw];
 #pragma unroll
     for (uint32_t i = 0; i < kRaw; ++i) woff[i] = tcol * tile_bytes + kg * row_bytes + plan.idx[i] * 4u;
-    const __half* xs = xp + 4u * (lane & 3u) + kg * 16u;
+    uint32_t xs = smem_addr(xp) + (4u * (lane & 3u) + kg * 16u) * 2u;  // shared address of the lane's columns, row 0, this stage
     RowOffsets<RM> ro;
     ro.init(lane, live_rows, xstride);
-    const uint32_t full0 = smem_addr(full), empty0 = smem_addr(empty);
+    const uint32_t full0 = smem_addr(full), empty0 = smem_addr(empty), ring0 = smem_addr(ring);
     uint32_t slot = pos.slot, par = pos.lap & 1u, lap = pos.lap;
+    // the slot's barriers and stage as running addresses
+    uint32_t full_a = full0 + slot * 8u, empty_a = empty0 + slot * 8u, st = ring0 + slot * stage_bytes;
     const bool lane0 = lane == 0;
 #pragma unroll 1
-    for (uint32_t r0 = 0; r0 < nrows; r0 += kStageRows, xs += kStageRows * 16u) {
-        mbar_wait_report(full0 + slot * 8u, par, err, kErrFullWait);
-        const uint8_t* st = ring + slot * stage_bytes;
+    for (uint32_t r0 = 0; r0 < nrows; r0 += kStageRows, xs += kStageRows * 32u) {
+        mbar_wait_report(full_a, par, err, kErrFullWait);
         if (CB == kProbeStream) {
             // timing probe: the stage has landed, nothing reads it
         } else if (N > 0) {
             // the stage's four tiles of this warp, two at a time: words, then decodes, then tensor-core steps, so the
             // dependent chains of two tiles overlap and the registers of four are never needed at once
+            uint32_t wa[kRaw];
+#pragma unroll
+            for (uint32_t w = 0; w < kRaw; ++w) wa[w] = st + woff[w];
 #pragma unroll
             for (uint32_t h = 0; h < kBatch; h += kHalfBatch) {
                 uint32_t raw[kHalfBatch][kRaw];
 #pragma unroll
                 for (uint32_t i = 0; i < kHalfBatch; ++i)
 #pragma unroll
-                    for (uint32_t w = 0; w < kRaw; ++w)
-                        raw[i][w] = *reinterpret_cast<const uint32_t*>(st + woff[w] + (h + i) * kKGroups * row_bytes);
+                    for (uint32_t w = 0; w < kRaw; ++w) raw[i][w] = lds_u32(wa[w] + (h + i) * kKGroups * row_bytes);
                 uint32_t b[kHalfBatch][4];
 #pragma unroll
                 for (uint32_t i = 0; i < kHalfBatch; ++i) decode_raw<NP, CB>(raw[i], plan, mask, b[i]);
 #pragma unroll
-                for (uint32_t i = 0; i < kHalfBatch; ++i) mma_tile<RM>(acc, xs + (h + i) * kKGroups * 16u, ro, b[i]);
+                for (uint32_t i = 0; i < kHalfBatch; ++i) mma_tile<RM>(acc, xs + (h + i) * kKGroups * 32u, ro, b[i]);
             }
         } else {
+            const uint8_t* stp = ring + (st - ring0);
 #pragma unroll 1
             for (uint32_t i = 0; i < kBatch; ++i) {
                 uint32_t b[4];
-                decode_lane_any<CB>(reinterpret_cast<const uint32_t*>(st + tcol * tile_bytes + (kg + i * kKGroups) * row_bytes),
+                decode_lane_any<CB>(reinterpret_cast<const uint32_t*>(stp + tcol * tile_bytes + (kg + i * kKGroups) * row_bytes),
                                     n, lane, mask, b);
-                mma_tile<RM>(acc, xs + i * kKGroups * 16u, ro, b);
+                mma_tile<RM>(acc, xs + i * kKGroups * 32u, ro, b);
             }
         }
         __syncwarp();
-        if (lane0) mbar_arrive_addr(empty0 + slot * 8u);
-        if (++slot == rc.stages) slot = 0, par ^= 1u, ++lap;
+        if (lane0) mbar_arrive_addr(empty_a);
+        full_a += 8u, empty_a += 8u, st += stage_bytes;
+        if (++slot == rc.stages) slot = 0, par ^= 1u, ++lap, full_a = full0, empty_a = empty0, st = ring0;
     }
     pos.slot = slot, pos.lap = lap;
 }
