@@ -124,8 +124,8 @@ uint32_t largest_slice(uint32_t nb, uint32_t split) {
     return mx * 128u;
 }
 
-// The ring of one GEMV CTA: stages of kStageRows tk rows (one 128-input block), as many as the slab needs or the budget
-// holds.
+// The ring of one GEMV CTA: stages of kStageRows tk rows (two 128-input blocks), as many as the slab needs or the budget
+// holds; three where the default budget holds fewer and two CTAs still fit a multiprocessor.
 bool plan_ring(uint32_t row_cap, uint32_t xrows, uint32_t slice_max, uint32_t cluster, uint32_t n, RingPlan& ring) {
     const uint32_t row_bytes = 16u * n, nrows = slice_max / 16u;  // nrows is a multiple of 8 (whole 128-blocks)
     const uint32_t stage_rows = kStageRows;
@@ -134,6 +134,7 @@ bool plan_ring(uint32_t row_cap, uint32_t xrows, uint32_t slice_max, uint32_t cl
     const uint32_t fixed = gemv_smem(row_cap, xrows, slice_max, cluster, stage_bytes, 0).total;
     if (fixed + stage_bytes > kSmemCap) return false;
     uint32_t budget = g_cfg.ring_bytes ? g_cfg.ring_bytes : kDefaultRing;
+    if (!g_cfg.ring_bytes && budget < 3u * stage_bytes && fixed + 3u * stage_bytes <= 108u * 1024u) budget = 3u * stage_bytes;
     if (budget > kSmemCap - fixed) budget = kSmemCap - fixed;
     uint32_t stages = budget / stage_bytes;
     stages = stages < 1u ? 1u : stages;

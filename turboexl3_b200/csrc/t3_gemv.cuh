@@ -30,8 +30,10 @@ constexpr uint32_t kGemvThreads = kConsumerThreads + 32u;
 constexpr uint32_t kMaxStages = 32;
 constexpr uint32_t kPartialStride = 136;  // floats per row of a partial-sum tile (128 + 8: conflict-free float2 stores)
 constexpr uint32_t kXpPad = 16;           // halfs added to an xp row so a quad's 8-byte loads spread over the banks
-constexpr uint32_t kBatch = 4;            // tiles of a stage a warp owns: their code words are loaded together
-constexpr uint32_t kStageRows = kKGroups * kBatch;  // tk rows of a ring stage: one 128-input block, one batch a warp
+constexpr uint32_t kBatch = 8;            // tiles of a full stage a warp owns (taken two at a time)
+constexpr uint32_t kStageRows = kKGroups * kBatch;  // tk rows of a ring stage: two 128-input blocks (a slab's last stage may
+                                                    // hold one: slabs are whole 128-input blocks)
+constexpr uint32_t kBlockRows = 8;        // tk rows of a 128-input block
 
 // How the ring is cut for one launch (host-chosen)
 struct Ring {
@@ -93,17 +95,18 @@ struct RingPos {
     }
 };
 
-// Streams tk rows [0, nrows) of a block's slab into the ring (nrows a multiple of kStageRows): row r is `row_bytes`
+// Streams tk rows [0, nrows) of a block's slab into the ring (nrows a multiple of kBlockRows): row r is `row_bytes`
 // contiguous bytes at src + r * src_row_stride (bytes). `pos` continues across calls so barrier parities stay in step.
 __device__ __forceinline__ void produce_slab(uint8_t* ring, uint64_t* full, uint64_t* empty, const uint8_t* src,
                                              size_t src_row_stride, uint32_t nrows, uint32_t row_bytes, Ring rc,
                                              RingPos& pos, uint32_t lane, uint32_t* err) {
     const uint32_t stage_bytes = kStageRows * row_bytes;
     for (uint32_t r0 = 0; r0 < nrows; r0 += kStageRows) {
+        const uint32_t here = min(kStageRows, nrows - r0);  // a full stage, or the slab's last 128-input block
         if (pos.lap > 0) mbar_wait_report(smem_addr(&empty[pos.slot]), (pos.lap - 1u) & 1u, err, kErrEmptyWait);
-        if (lane == 0) mbar_arrive_expect_tx(&full[pos.slot], stage_bytes);
+        if (lane == 0) mbar_arrive_expect_tx(&full[pos.slot], here * row_bytes);
         __syncwarp();
-        if (lane < kStageRows)
+        if (lane < here)
             bulk_copy_g2s(ring + pos.slot * stage_bytes + lane * row_bytes, src + (size_t)(r0 + lane) * src_row_stride,
                           row_bytes, &full[pos.slot]);
         pos.advance(rc.stages);
@@ -163,10 +166,10 @@ __device__ __forceinline__ void mma_tile(float (&acc)[RowCap<RM>::kMB][2][4], ui
 }
 
 // Consumer warp (tile column `tcol`, K group `kg`) folds tk rows kg, kg + kKGroups, ... of [0, nrows) into acc (nrows a
-// multiple of kStageRows). xp: `live_rows` prepared rows in lane order, row stride `xstride` halfs, k = 0 at the slab's
+// multiple of kBlockRows). xp: `live_rows` prepared rows in lane order, row stride `xstride` halfs, k = 0 at the slab's
 // first input.
 // acc[mb][nt] is the mma C fragment of rows 16 mb .. 16 mb + 15, columns 16 tcol + 8 nt .. + 7.
-// A stage holds kStageRows tk rows, so a warp's share of a stage is exactly one batch of kBatch tiles, and with the rate
+// A full stage holds kStageRows tk rows, a warp's share of it kBatch tiles taken two at a time, and with the rate
 // a template constant every shared-memory offset inside a stage is an immediate.
 template <int N, int CB, int RM>
 __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full, uint64_t* empty, uint32_t nrows,
@@ -175,7 +178,7 @@ __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full
                                              float (&acc)[RowCap<RM>::kMB][2][4], uint32_t* err) {
     constexpr int NP = N > 0 ? N : 16;
     constexpr uint32_t kRaw = raw_words(NP);
-    constexpr uint32_t kHalfBatch = kBatch / 2u;  // tiles whose words and fragments are in registers together
+    constexpr uint32_t kHalfBatch = 2u;  // tiles whose words and fragments are in registers together
     const uint32_t n = N > 0 ? (uint32_t)N : n_rt;
     const uint32_t tile_bytes = 2u * n, row_bytes = 16u * n, stage_bytes = kStageRows * row_bytes;
     LanePlan<NP> plan;
@@ -194,6 +197,7 @@ __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full
     const bool lane0 = lane == 0;
 #pragma unroll 1
     for (uint32_t r0 = 0; r0 < nrows; r0 += kStageRows, xs += kStageRows * 32u) {
+        const uint32_t tiles = min(kStageRows, nrows - r0) / kKGroups;  // this warp's tiles of the stage: 8, or 4 in a last half stage
         mbar_wait_report(full_a, par, err, kErrFullWait);
         if (CB == kProbeStream) {
             // timing probe: the stage has landed, nothing reads it
@@ -205,6 +209,7 @@ __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full
             for (uint32_t w = 0; w < kRaw; ++w) wa[w] = st + woff[w];
 #pragma unroll
             for (uint32_t h = 0; h < kBatch; h += kHalfBatch) {
+                if (h >= tiles) break;
                 uint32_t raw[kHalfBatch][kRaw];
 #pragma unroll
                 for (uint32_t i = 0; i < kHalfBatch; ++i)
@@ -219,7 +224,7 @@ __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full
         } else {
             const uint8_t* stp = ring + (st - ring0);
 #pragma unroll 1
-            for (uint32_t i = 0; i < kBatch; ++i) {
+            for (uint32_t i = 0; i < tiles; ++i) {
                 uint32_t b[4];
                 decode_lane_any<CB>(reinterpret_cast<const uint32_t*>(stp + tcol * tile_bytes + (kg + i * kKGroups) * row_bytes),
                                     n, lane, mask, b);
