@@ -64,13 +64,13 @@ __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.w
 
 // The consumer side of one pass once xp is ready: GEMV over the slab, the two K groups joined, the partial pushed to the
 // rows' owners. `count` live rows.
-template <int N, int RM>
+template <int N, int RM, int HB = 2>
 __device__ __forceinline__ void gemv_and_push(cg::cluster_group& cluster, const CtaSmem& c, uint32_t nrows, uint32_t n,
                                               uint32_t mask, Ring rc, uint32_t xstride, uint32_t xrows, RingPos& pos, uint32_t count,
                                               uint32_t rank, uint32_t csize, uint32_t warp, uint32_t lane, uint32_t* err) {
     const uint32_t tcol = warp & (kTileWarps - 1u), kg = warp / kTileWarps;
     float acc[RowCap<RM>::kMB][2][4] = {};
-    consume_slab<N, CB, RM>(c.ring, c.full, c.empty, nrows, n, mask, rc, c.xp, xstride, xrows, pos, tcol, kg, lane, acc, err);
+    consume_slab<N, CB, RM, HB>(c.ring, c.full, c.empty, nrows, n, mask, rc, c.xp, xstride, xrows, pos, tcol, kg, lane, acc, err);
     if (kg == 1) store_local<RM>(c.local, acc, tcol, lane);
     named_sync(1, kConsumerThreads);
     if (kg == 0) push_partial<RM>(cluster, c.recv, c.local, acc, count, rank, csize, tcol, lane);
@@ -84,6 +84,9 @@ __device__ __forceinline__ void dense_gemv_body(const DenseArgs& a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* smem = aligned_smem(smem_raw);
     __shared__ uint32_t s_last;
+    // up to 8 rows the accumulators are four registers, so four tiles' words and fragments fit beside them: more
+    // independent chains a warp where few warps share a scheduler (the small linears)
+    constexpr int kDenseBatch = RowCap<RM>::kHalf ? 4 : 2;
     cg::cluster_group cluster = cg::this_cluster();
     const bool global = a.part != nullptr;
     const uint32_t rank = global ? blockIdx.x : cluster.block_rank(), csize = global ? 1u : a.split, blk = blockIdx.y;
@@ -149,12 +152,12 @@ __device__ __forceinline__ void dense_gemv_body(const DenseArgs& a) {
             a.trace[3] = clock64();
         }
         if (!global) {
-            gemv_and_push<N, RM>(cluster, c, nrows, a.n, a.mask, rc, xstride, a.rows, pos, a.rows, rank, csize, warp, lane, a.err);
+            gemv_and_push<N, RM, kDenseBatch>(cluster, c, nrows, a.n, a.mask, rc, xstride, a.rows, pos, a.rows, rank, csize, warp, lane, a.err);
         } else {
             // the slice's sums to global memory; the block's last arriver adds the slices in slice order and finishes
             const uint32_t tcol = warp & (kTileWarps - 1u), kg = warp / kTileWarps;
             float acc[RowCap<RM>::kMB][2][4] = {};
-            consume_slab<N, CB, RM>(c.ring, c.full, c.empty, nrows, a.n, a.mask, rc, c.xp, xstride, a.rows, pos, tcol, kg, lane, acc, a.err);
+            consume_slab<N, CB, RM, kDenseBatch>(c.ring, c.full, c.empty, nrows, a.n, a.mask, rc, c.xp, xstride, a.rows, pos, tcol, kg, lane, acc, a.err);
             if (kg == 1) store_local<RM>(c.local, acc, tcol, lane);
             named_sync(1, kConsumerThreads);
             if (kg == 0) {

@@ -171,14 +171,16 @@ __device__ __forceinline__ void mma_tile(float (&acc)[RowCap<RM>::kMB][2][4], ui
 // acc[mb][nt] is the mma C fragment of rows 16 mb .. 16 mb + 15, columns 16 tcol + 8 nt .. + 7.
 // A full stage holds kStageRows tk rows, a warp's share of it kBatch tiles taken two at a time, and with the rate
 // a template constant every shared-memory offset inside a stage is an immediate.
-template <int N, int CB, int RM>
+// HB: tiles whose words and fragments are in registers together (the routed kernels keep two: four spill there).
+template <int N, int CB, int RM, int HB = 2>
 __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full, uint64_t* empty, uint32_t nrows,
                                              uint32_t n_rt, uint32_t mask, Ring rc, const __half* xp, uint32_t xstride,
                                              uint32_t live_rows, RingPos& pos, uint32_t tcol, uint32_t kg, uint32_t lane,
                                              float (&acc)[RowCap<RM>::kMB][2][4], uint32_t* err) {
     constexpr int NP = N > 0 ? N : 16;
     constexpr uint32_t kRaw = raw_words(NP);
-    constexpr uint32_t kHalfBatch = 2u;  // tiles whose words and fragments are in registers together
+    constexpr uint32_t kHalfBatch = (uint32_t)HB;
+    static_assert(kBatch % HB == 0 && (kBlockRows / kKGroups) % HB == 0, "a stage, and a last half stage, are whole batches");
     const uint32_t n = N > 0 ? (uint32_t)N : n_rt;
     const uint32_t tile_bytes = 2u * n, row_bytes = 16u * n, stage_bytes = kStageRows * row_bytes;
     LanePlan<NP> plan;
