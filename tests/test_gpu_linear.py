@@ -308,3 +308,24 @@ def test_large_linear_global_exchange_matches_the_cluster_kernel_within_bars():
         for got in (y, yb):
             check(host_f32(got), ref, "f16", f"large_linear_rows{rows}")
     assert t3.device_error() == 0
+
+
+@pytest.mark.parametrize("rows", [9, 16, 17, 32])
+def test_rows_past_8_with_and_without_the_workspace_give_the_same_bytes(rows):
+    """Past 8 rows the workspace is optional: with it the rows are rotated once by a launch of their own and the CTAs pull
+    them by bulk copy, without it every CTA rotates its own copy. The same arithmetic on the same K slices: the same bytes."""
+    in_dim, out_dim, n = 1024, 768, 48
+    trellis, suh, svh = synth.linear(21, in_dim, out_dim, n, scaled=True)
+    x = dev(synth.activations(22, rows, in_dim))
+    args = (x, dev(trellis), dev(suh), dev(svh))
+    L = t3.lib()
+    assert L.t3_linear_workspace_bytes(rows, in_dim, out_dim, n) >= rows * in_dim * 2
+    with_ws = t3.linear(*args)
+    assert t3.launch_count() > 0
+    without = torch.empty_like(with_ws)
+    before = t3.launch_count()
+    rc = L.t3_linear(x.data_ptr(), 1, rows, args[1].data_ptr(), args[2].data_ptr(), args[3].data_ptr(), in_dim, out_dim, n,
+                     t3.Decode.mul1._c(), without.data_ptr(), None, 0, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0 and t3.launch_count() - before == 1  # one launch: no prepare of its own
+    assert torch.equal(with_ws, without)
+    assert t3.device_error() == 0

@@ -168,9 +168,9 @@ __device__ __forceinline__ void dense_gemv_body(const DenseArgs& a) {
                     for (int nt = 0; nt < Frags<RM>::kNt; ++nt)
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const uint32_t m = fragment_row<RM>(lane, mb, e);
+                            const uint32_t m = fragment_row<RM>(lane, mb, nt, e);
                             if (m >= a.rows) continue;
-                            const uint32_t col = tcol * 16u + fragment_col<RM>(lane, nt, e);
+                            const uint32_t col = tcol * 16u + fragment_col<RM>(lane, e);
                             __stcg(mine + m * 128u + col, acc[mb][nt][e] + c.local[m * kPartialStride + col]);
                         }
             }

@@ -143,11 +143,12 @@ __device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
 }
 
 // one decoded tile times the prepared rows at inputs [16 tk, 16 tk + 16): xk is the shared address of the lane's columns there, row 0.
-// Up to 8 rows (RM = 8) the product is taken TRANSPOSED, (W tile)^T (16 outputs x 16 inputs) times x^T (16 inputs x 8 rows):
+// The product is taken TRANSPOSED, (W tile)^T (16 outputs x 16 inputs) times x^T (16 inputs x 8 rows) a block of 8 rows:
 // the decoded words, which are the B fragments of the tile's two column halves, are in another order exactly the A fragment
 // of the transposed tile, and the lane's 8-byte load of a prepared row is the whole B fragment. One tensor-core step a tile
-// instead of two, four accumulators instead of eight, and no register is moved or zeroed to build an operand. The
-// accumulators are then acc[0][0][e + 2 half] = (row 2q + e, column g + 8 half) of the tile (see store_local, push_partial).
+// and 8 rows, four accumulators an 8-row block, and no register is moved or zeroed to build an operand. Row block rb = 2 mb
+// + nt of the pass is acc[mb][nt], whose element e is (row 8 rb + 2q + (e & 1), column g + 8 (e >> 1)) of the tile (see
+// fragment_row, fragment_col). Up to 8 rows only acc[0][0] exists.
 template <int RM>
 __device__ __forceinline__ void mma_tile(float (&acc)[RowCap<RM>::kMB][2][4], uint32_t xk, const RowOffsets<RM>& ro,
                                          const uint32_t (&b)[4]) {
@@ -160,15 +161,15 @@ __device__ __forceinline__ void mma_tile(float (&acc)[RowCap<RM>::kMB][2][4], ui
     for (int mb = 0; mb < RowCap<RM>::kMB; ++mb) {
         const uint2 lo = lds_u64(xk + ro.lo[mb]);
         const uint2 hi = lds_u64(xk + ro.hi[mb]);
-        mma16816(acc[mb][0], lo.x, hi.x, lo.y, hi.y, b[0], b[1]);
-        mma16816(acc[mb][1], lo.x, hi.x, lo.y, hi.y, b[2], b[3]);
+        mma16816(acc[mb][0], b[0], b[2], b[1], b[3], lo.x, lo.y);
+        mma16816(acc[mb][1], b[0], b[2], b[1], b[3], hi.x, hi.y);
     }
 }
 
 // Consumer warp (tile column `tcol`, K group `kg`) folds tk rows kg, kg + kKGroups, ... of [0, nrows) into acc (nrows a
 // multiple of kBlockRows). xp: `live_rows` prepared rows in lane order, row stride `xstride` halfs, k = 0 at the slab's
 // first input.
-// acc[mb][nt] is the mma C fragment of rows 16 mb .. 16 mb + 15, columns 16 tcol + 8 nt .. + 7.
+// acc[mb][nt] is the (transposed) mma C fragment of rows 8 (2 mb + nt) .. + 7, columns 16 tcol .. + 15.
 // A full stage holds kStageRows tk rows, a warp's share of it kBatch tiles taken two at a time, and with the rate
 // a template constant every shared-memory offset inside a stage is an immediate.
 // HB: tiles whose words and fragments are in registers together (the routed kernels keep two: four spill there).
@@ -243,17 +244,17 @@ __device__ __forceinline__ void consume_slab(const uint8_t* ring, uint64_t* full
 
 // ---- the cluster reduce-scatter -----------------------------------------------------------------------------------
 
-// Where a lane's accumulators sit in a [rows][128] tile of partial sums: element e of the fragment that covers tile column
-// half `nt` (and, past 8 rows, 16-row block mb) is row fragment_row, column tcol * 16 + fragment_col
+// Where a lane's accumulators sit in a [rows][128] tile of partial sums: element e of acc[mb][nt] is row fragment_row,
+// column tcol * 16 + fragment_col
 template <int RM>
-__device__ __forceinline__ uint32_t fragment_row(uint32_t lane, int mb, int e) {
-    return RowCap<RM>::kHalf ? 2u * (lane & 3u) + (uint32_t)(e & 1) : (uint32_t)mb * 16u + (lane >> 2) + ((e & 2) ? 8u : 0u);
+__device__ __forceinline__ uint32_t fragment_row(uint32_t lane, int mb, int nt, int e) {
+    return 8u * (uint32_t)(2 * mb + nt) + 2u * (lane & 3u) + (uint32_t)(e & 1);
 }
 template <int RM>
-__device__ __forceinline__ uint32_t fragment_col(uint32_t lane, int nt, int e) {
-    return RowCap<RM>::kHalf ? (lane >> 2) + ((e & 2) ? 8u : 0u) : (uint32_t)nt * 8u + 2u * (lane & 3u) + (uint32_t)(e & 1);
+__device__ __forceinline__ uint32_t fragment_col(uint32_t lane, int e) {
+    return (lane >> 2) + ((e & 2) ? 8u : 0u);
 }
-// the fragments a lane holds: one (transposed) up to 8 rows, else two column halves a 16-row block
+// the 8-row blocks a lane holds a 16-row block of the pass: one up to 8 rows, else two
 template <int RM>
 struct Frags {
     static constexpr int kNt = RowCap<RM>::kHalf ? 1 : 2;
@@ -269,7 +270,7 @@ __device__ __forceinline__ void store_local(float* local, const float (&acc)[Row
         for (int nt = 0; nt < Frags<RM>::kNt; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-                local[fragment_row<RM>(lane, mb, e) * kPartialStride + tcol * 16u + fragment_col<RM>(lane, nt, e)] = acc[mb][nt][e];
+                local[fragment_row<RM>(lane, mb, nt, e) * kPartialStride + tcol * 16u + fragment_col<RM>(lane, e)] = acc[mb][nt][e];
 }
 
 // K group 0 adds group 1's tile to its accumulators and pushes each live row m (< count) to the CTA that owns it,
@@ -286,9 +287,9 @@ __device__ __forceinline__ void push_partial(cg::cluster_group& cluster, float* 
         for (int nt = 0; nt < Frags<RM>::kNt; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const uint32_t m = fragment_row<RM>(lane, mb, e);
+                const uint32_t m = fragment_row<RM>(lane, mb, nt, e);
                 if (m >= count) continue;
-                const uint32_t col = tcol * 16u + fragment_col<RM>(lane, nt, e);
+                const uint32_t col = tcol * 16u + fragment_col<RM>(lane, e);
                 float* dst = cluster.map_shared_rank(recv, m % csize) + (rank * owned + m / csize) * kPartialStride;
                 dst[col] = acc[mb][nt][e] + local[m * kPartialStride + col];
             }
