@@ -434,10 +434,15 @@ size_t align256(size_t v) { return (v + 255u) & ~(size_t)255u; }
 struct DenseWs {
     size_t xp, part, counters, total;
 };
-DenseWs dense_ws(uint32_t rows, uint32_t in, uint32_t out, uint32_t global_split) {
+// Whether a call's rows are rotated once by a launch of their own instead of inside every CTA: past kFusedRows rows always;
+// up to kFusedRows when a CTA's share of the work would be more than two rotations a warp (many rows on long K slices: each
+// CTA repeats the rotation of its whole slice for every row before its first tensor-core step).
+bool prep_ahead(uint32_t rows, uint32_t slice_max) { return rows > kFusedRows || rows * (slice_max / 128u) > 2u * kConsumerWarps; }
+
+DenseWs dense_ws(uint32_t rows, uint32_t in, uint32_t out, uint32_t global_split, uint32_t slice_max) {
     DenseWs w;
     w.xp = 0;
-    w.part = rows > kFusedRows ? align256((size_t)rows * in * 2u) : 0u;
+    w.part = prep_ahead(rows, slice_max) ? align256((size_t)rows * in * 2u) : 0u;
     w.counters = w.part + (global_split ? align256((size_t)(out / 128u) * global_split * rows * 512u) : 0u);
     w.total = w.counters + (global_split ? align256((size_t)(out / 128u) * 4u) : 0u);
     return w;
@@ -512,7 +517,7 @@ size_t t3_linear_workspace_bytes(size_t rows, int in_dim, int out_dim, int n) {
     DenseArgs a = {};
     a.in = (uint32_t)in_dim, a.out = (uint32_t)out_dim, a.n = (uint32_t)n, a.rows = (uint32_t)rows;
     if (plan_dense(a, cfg, true) != T3_OK) return 0;
-    return dense_ws(a.rows, a.in, a.out, a.part ? a.split : 0u).total;
+    return dense_ws(a.rows, a.in, a.out, a.part ? a.split : 0u, a.slice_max).total;
 }
 
 int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, const void* suh, const void* svh,
@@ -556,11 +561,11 @@ int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, cons
     note_engine(1, (uint64_t)in_dim, (uint64_t)out_dim, (uint64_t)n, 0);
     a.rows = (uint32_t)rows;
     if (int rc = plan_dense(a, cfg, workspace != nullptr)) return rc;
-    DenseWs ws = dense_ws(a.rows, a.in, a.out, a.part ? a.split : 0u);
+    DenseWs ws = dense_ws(a.rows, a.in, a.out, a.part ? a.split : 0u, a.slice_max);
     bool has_ws = workspace != nullptr && workspace_bytes >= ws.total;
     if (a.part && !has_ws) {  // too small for the global exchange: the cluster kernel, with the rotated rows if those fit
         if (int rc = plan_dense(a, cfg, false)) return rc;
-        ws = dense_ws(a.rows, a.in, a.out, 0u);
+        ws = dense_ws(a.rows, a.in, a.out, 0u, a.slice_max);
         has_ws = workspace != nullptr && workspace_bytes >= ws.total;
     }
     a.err = dev_error_ptr();
@@ -572,7 +577,7 @@ int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, cons
     }
     a.x = x;
     a.y = y;
-    if (rows > kFusedRows && !cfg.probe && has_ws) {
+    if (prep_ahead(a.rows, a.slice_max) && !cfg.probe && has_ws) {
         a.xp_g = workspace;
         g_launches.fetch_add(1, std::memory_order_relaxed);
         if (int rc = cuda_status(launch_dense_prep(a, static_cast<cudaStream_t>(stream)))) return rc;
@@ -609,12 +614,13 @@ int t3_plan_linear(size_t rows, int in_dim, int out_dim, int n, t3_decode dec, t
     char symbol[64];
     std::snprintf(symbol, sizeof symbol, "t3_dense_gemv_%s_n%u_r%u", dec.codebook == T3_MCG ? "mcg" : "mul1", named_rate(a.n), rm);
     int k = 0;
-    if (a.rows > kFusedRows) {  // with the call's workspace: the rows rotated once ahead of the GEMV
+    const bool ahead = prep_ahead(a.rows, a.slice_max);
+    if (ahead) {  // with the call's workspace: the rows rotated once ahead of the GEMV
         if (max_launches < 2) return -T3_BAD_EXL3_SHAPE;
         fill_launch(&out[k++], "t3_dense_prep", "dense", dim3((a.rows * (a.in / 128u) + 3u) / 4u, 1, 1), 128u, 0u, 1u,
                     {T3_ROLE_X, T3_ROLE_SUH, T3_ROLE_XP});
     }
-    if (a.rows > kFusedRows)
+    if (ahead)
         fill_launch(&out[k++], symbol, "dense", dim3(a.split, a.out / 128u, 1), 32u * 17u,
                     gemv_smem_bytes(rm, a.rows, a.slice_max, a.part ? 1u : a.split, a.n, a.ring), a.part ? 1u : a.split,
                     {T3_ROLE_XP, T3_ROLE_Y, T3_ROLE_TRELLIS, T3_ROLE_SVH});
