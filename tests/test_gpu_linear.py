@@ -294,7 +294,7 @@ def test_large_linear_global_exchange_matches_the_cluster_kernel_within_bars():
     _, suh, svh = synth.linear(6, in_dim, 128, 16)
     svh = np.where(rng.random(out_dim) < 0.5, -1.0, 1.0).astype(np.float16)
     what = ob.reconstruct_inner(trellis, in_dim, out_dim, n, ob.MUL1)
-    for rows in (1, 7):
+    for rows in (1, 7, 12, 32):  # 7: the rows rotated ahead as well; 12, 32: whichever exchange their prepared rows leave room for
         x = synth.activations(7, rows, in_dim)
         args = (dev(x), dev(trellis.view(np.int16)), dev(suh), dev(svh))
         y = t3.linear(*args)  # api.linear brings the workspace
