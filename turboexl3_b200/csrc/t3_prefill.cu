@@ -26,7 +26,13 @@ namespace {
 
 constexpr uint32_t kBN = 128, kBK = 64;
 constexpr uint32_t kBBytes = kBN * kBK * 2u;  // 16 KB
-constexpr uint32_t kDecodeWarps = 16;
+// Decode warps a CTA: a warp takes one of the CTA's 8 tile columns and kTilesPerWarp of a stage's four tile rows. A warp's
+// waits, fence, arrivals and ring arithmetic are paid a stage whatever its tiles, so fewer warps with more tiles each issue
+// fewer instructions a tile.
+constexpr uint32_t kDecodeWarps = 8;
+constexpr uint32_t kTilesPerWarp = 32u / kDecodeWarps;           // 4 (8 warps) or 2 (16)
+constexpr uint32_t kEpilogueCols = 128u / (kDecodeWarps / 4u);  // accumulator columns a warp moves: 64 or 32
+static_assert(kDecodeWarps == 8 || kDecodeWarps == 16, "decode warps");
 constexpr uint32_t kGemmThreads = 32u * (2u + kDecodeWarps);
 constexpr uint32_t kMaxStages = 4;      // operand stages (A by TMA, B by the decode warps)
 constexpr uint32_t kMaxCodeStages = 8;  // stages of the code ring that feeds the decode warps
@@ -288,24 +294,25 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
         }
     } else {
         // decode warp dw: output tile column dw % 8 of the CTA's 128, input tile rows 2 (dw / 8) and 2 (dw / 8) + 1 of a stage
-        const uint32_t dw = warp - 2u, tcol = dw & 7u, tk0 = (dw >> 3) * 2u;
+        const uint32_t dw = warp - 2u, tcol = dw & 7u, tk0 = (dw >> 3) * kTilesPerWarp;
         constexpr int NP = NN > 0 ? NN : 16;
         constexpr uint32_t kRaw = raw_words(NP);
+        constexpr uint32_t T = kTilesPerWarp;
         LanePlan<NP> plan;
         plan.init(lane);
-        // byte offsets of the lane's words of its two tiles inside a code stage
-        uint32_t woff[2][kRaw];
+        // byte offsets of the lane's words of its tiles inside a code stage
+        uint32_t woff[T][kRaw];
 #pragma unroll
-        for (uint32_t i = 0; i < 2u; ++i)
+        for (uint32_t i = 0; i < T; ++i)
 #pragma unroll
             for (uint32_t w = 0; w < kRaw; ++w) woff[i][w] = ((tk0 + i) * 8u + tcol) * tile_bytes + plan.idx[w] * 4u;
         const uint32_t g = lane >> 2, q = lane & 3u;
-        // where the lane's eight half2 words of its two tiles go in a B stage:
+        // where the lane's eight half2 words of its tiles go in a B stage:
         // B[n][k] at n * 128 + ((k / 8) ^ (n % 8)) * 16 + (k % 8) * 2; k = 16 tk + 2 q (+8), n = 16 tcol + g (+8)
         const uint32_t row0 = (tcol * 16u + g) * 128u + 4u * q;
-        uint32_t boff[2][2];
+        uint32_t boff[T][2];
 #pragma unroll
-        for (uint32_t i = 0; i < 2u; ++i) {
+        for (uint32_t i = 0; i < T; ++i) {
             boff[i][0] = row0 + ((2u * (tk0 + i)) ^ g) * 16u;
             boff[i][1] = row0 + ((2u * (tk0 + i) + 1u) ^ g) * 16u;
         }
@@ -313,18 +320,18 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
             const uint32_t s = ks % kStages, u = ks / kStages, cs = ks % kCodeStages, uc = ks / kCodeStages;
             if (!mbar_wait(&full_c[cs], uc & 1u)) report(a.err, kErrFullWait);
             const uint8_t* cst = codes + cs * code_stage_bytes;
-            uint32_t b[2][4];
+            uint32_t b[T][4];
             if (NN > 0) {
-                uint32_t raw[2][kRaw];
+                uint32_t raw[T][kRaw];
 #pragma unroll
-                for (uint32_t i = 0; i < 2u; ++i)
+                for (uint32_t i = 0; i < T; ++i)
 #pragma unroll
                     for (uint32_t w = 0; w < kRaw; ++w) raw[i][w] = *reinterpret_cast<const uint32_t*>(cst + woff[i][w]);
 #pragma unroll
-                for (uint32_t i = 0; i < 2u; ++i) decode_raw<NP, CB>(raw[i], plan, a.mask, b[i]);
+                for (uint32_t i = 0; i < T; ++i) decode_raw<NP, CB>(raw[i], plan, a.mask, b[i]);
             } else {
 #pragma unroll
-                for (uint32_t i = 0; i < 2u; ++i)
+                for (uint32_t i = 0; i < T; ++i)
                     decode_lane_any<CB>(reinterpret_cast<const uint32_t*>(cst + ((tk0 + i) * 8u + tcol) * tile_bytes), a.n, lane,
                                         a.mask, b[i]);
             }
@@ -333,7 +340,7 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
             if (u > 0 && !mbar_wait(&empty[s], (u - 1u) & 1u)) report(a.err, kErrEmptyWait);
             uint8_t* bst = smem + s * kStageBytes + kABytes;
 #pragma unroll
-            for (uint32_t i = 0; i < 2u; ++i) {
+            for (uint32_t i = 0; i < T; ++i) {
                 *reinterpret_cast<uint32_t*>(bst + boff[i][0]) = b[i][0];
                 *reinterpret_cast<uint32_t*>(bst + boff[i][1]) = b[i][1];
                 *reinterpret_cast<uint32_t*>(bst + boff[i][0] + 8u * 128u) = b[i][2];
@@ -347,9 +354,10 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
         // accumulator halves (BM = 256) and the columns between them
         if (!mbar_wait(acc_full, 0u)) report(a.err, kErrMmaWait);
         tc_fence_after();
-        // every accumulator's lane quarter `quarter`, columns 32 grp .. + 31 of its 128
-        const uint32_t quarter = warp & 3u, grp = dw >> 2;  // grp 0..3
-        const uint32_t col0 = grp * 32u;
+        // every accumulator's lane quarter `quarter`, columns kEpilogueCols grp .. of its 128, sixteen at a time
+        const uint32_t quarter = warp & 3u, grp = dw >> 2;
+        const uint32_t col0 = grp * kEpilogueCols;
+        constexpr uint32_t kChunks = kEpilogueCols / 16u;
         if (a.svh[0] != nullptr) {
             // Fused finish (format.finishOutput): the accumulators go to shared memory as f16 (the operand stages are
             // free: every MMA and every copy has completed), then a warp takes eight rows at a time through the
@@ -357,8 +365,8 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
             constexpr uint32_t kZStride = 128u + 8u;  // halfs a row: 16-byte aligned rows, staggered over the banks
             __half* ztile = reinterpret_cast<__half*>(smem);
 #pragma unroll 1
-            for (uint32_t hc = 0; hc < (BM / 128u) * 2u; ++hc) {
-                const uint32_t half = hc >> 1, c = (hc & 1u) * 16u;
+            for (uint32_t hc = 0; hc < (BM / 128u) * kChunks; ++hc) {
+                const uint32_t half = hc / kChunks, c = (hc % kChunks) * 16u;
                 const uint32_t r = half * 128u + quarter * 32u + lane;
                 uint32_t v[16];
                 tmem_ld16(tmem + ((quarter * 32u) << 16) + half * 128u + col0 + c, v);
@@ -392,8 +400,8 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
             }
         } else
 #pragma unroll 1
-        for (uint32_t hc = 0; hc < (BM / 128u) * 2u; ++hc) {
-            const uint32_t half = hc >> 1, c = (hc & 1u) * 16u;
+        for (uint32_t hc = 0; hc < (BM / 128u) * kChunks; ++hc) {
+            const uint32_t half = hc / kChunks, c = (hc % kChunks) * 16u;
             const int r = (int)(half * 128u + quarter * 32u + lane);
             // the inner products as they are: to y in its 16-bit dtype when it is given (one rounding: the un-rotated
             // trunk), else to z as f16
