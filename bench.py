@@ -338,6 +338,15 @@ def prefill_submetric(t3, synth, torch) -> dict:
             us = st["median"]
             out[f"resident_{i}x{o}_rows{rows}"] = {"us": round(us, 1), "us_min": round(st["min"], 1),
                                                    "TFLOPS": round(2.0 * rows * i * o / us / 1e6, 1), "reps": st["reps"]}
+    # few prefill rows (33..256): K cut into slices a CTA each; eight calls a graph replay (a call is shorter than its launch)
+    for (i, o, k, rows) in [(6144, 2048, 4, 128), (2048, 6144, 4, 128)]:
+        w = tuple(dev(a) for a in synth.linear(5, i, o, 16 * k))
+        x = dev(synth.activations(1, rows, i))
+        g = graph_of(lambda: [t3.linear(x, *w) for _ in range(8)])
+        st = time_stats(g.replay, 20)
+        us = st["median"] / 8
+        out[f"dense_{i}x{o}_K{k}_rows{rows}"] = {"us": round(us, 1), "us_min": round(st["min"] / 8, 1),
+                                                 "TFLOPS": round(2.0 * rows * i * o / us / 1e6, 1), "reps": st["reps"]}
     H, I, E, topk, n = 2048, 512, 512, 10, 48
     arrs = synth.bank(3, E, H, I, n)
     bank = t3.Bank(t3.Proj(dev(arrs["gate_t"]), dev(arrs["gate_suh"]), dev(arrs["gate_svh"])),

@@ -90,6 +90,10 @@ def test_workspace_sizes():
     b = _bank(hidden=2048, inter=512)
     assert L.t3_moe_workspace_bytes(4, 10, C.byref(b)) >= 40 * (512 + 2048) * 2
     assert L.t3_linear_workspace_bytes(1, 2048, 2048, 64) == 0
+    # prefill rows: the prepared rows; up to 256 rows of a linear with few 128-column CTAs, the K slices' slab as well
+    assert L.t3_linear_workspace_bytes(257, 6144, 2048, 64) == 257 * 6144 * 2
+    assert L.t3_linear_workspace_bytes(256, 6144, 2048, 64) > 256 * 6144 * 2 + 2 * 16 * 2 * 128 * 128 * 4
+    assert L.t3_linear_workspace_bytes(256, 2048, 32768, 64) == 256 * 2048 * 2  # 256 CTAs a row tile: nothing to cut
 
 
 def test_expert_quant_json():  # src/core/spec.zig:92-160

@@ -166,11 +166,19 @@ struct GemmArgs {
     void* y;                    // [rows][N], one op
     int y_dt;
     uint32_t ab_bf16;           // both operands are bf16 (the un-rotated trunk on bf16 activations); else f16
+    // K slices (dense linears of few CTAs; grid z): slice z runs K stages [ksteps z / ksplit, ksteps (z + 1) / ksplit) and
+    // leaves its f32 accumulators in part[tile][z][BM][128]; the tile's last arriver (counters[tile], zero before the launch)
+    // adds the slices in slice order and finishes. 0 or 1: one CTA runs all of K. With the fused finish only.
+    uint32_t ksplit;
+    float* part;
+    uint32_t* counters;
     uint32_t* err;
 };
 
 // RES: the B operand is a kept W_hat (transposed, [N, K] f16) loaded by TMA like A; nothing is decoded.
-template <int NN, int CB, int BM, bool RES = false, bool PAIR = false>
+// SLICED: the K-slice exchange (GemmArgs::ksplit > 1) is compiled in: 128-row tiles of dense linears only, so the routed
+// experts' kernels do not carry its registers.
+template <int NN, int CB, int BM, bool RES = false, bool PAIR = false, bool SLICED = false>
 __global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
     gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs a) {
     using T = Tile<BM, PAIR>;
@@ -202,7 +210,12 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t per_op = a.N / kBN, op = blockIdx.x / per_op, nt = blockIdx.x - op * per_op;
-    const uint32_t ksteps = a.K / kBK;
+    uint32_t ks_lo = 0, ksteps = a.K / kBK;
+    if (SLICED) {
+        const uint32_t all = ksteps;
+        ks_lo = all * blockIdx.z / a.ksplit;
+        ksteps = all * (blockIdx.z + 1u) / a.ksplit - ks_lo;
+    }
     const uint32_t tile_bytes = 2u * a.n, out_tiles = a.N / 16u;
 
     if (tid == 0) {
@@ -245,8 +258,8 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
                         mbar_arrive_expect_tx(&full_c[cs], 4u * row_bytes);
 #pragma unroll
                         for (uint32_t i = 0; i < 4u; ++i)
-                            bulk_copy_g2s(codes + cs * code_stage_bytes + i * row_bytes, src + (size_t)(kc * 4u + i) * tk_stride,
-                                          row_bytes, &full_c[cs]);
+                            bulk_copy_g2s(codes + cs * code_stage_bytes + i * row_bytes,
+                                          src + (size_t)((ks_lo + kc) * 4u + i) * tk_stride, row_bytes, &full_c[cs]);
                         ++kc;
                         moved = true;
                     }
@@ -255,10 +268,11 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
                     const uint32_t s = ka % kStages, u = ka / kStages;
                     if (u == 0 || mbar_try(smem_addr(&empty[s]), (u - 1u) & 1u)) {
                         mbar_arrive_expect_tx(&full_a[s], RES ? kStageBytes : kABytes);
-                        if (RES) tma_load_2d(smem + s * kStageBytes + kABytes, &tmap_b, (int)(ka * kBK), (int)(nt * kBN), &full_a[s]);
+                        const int kx = (int)((ks_lo + ka) * kBK);
+                        if (RES) tma_load_2d(smem + s * kStageBytes + kABytes, &tmap_b, kx, (int)(nt * kBN), &full_a[s]);
 #pragma unroll
                         for (uint32_t h = 0; h < BM; h += T::kBoxRows)  // a TMA box holds at most 256 rows
-                            tma_load_2d(smem + s * kStageBytes + h * kBK * 2u, &tmap_a, (int)(ka * kBK),
+                            tma_load_2d(smem + s * kStageBytes + h * kBK * 2u, &tmap_a, kx,
                                         (int)(op * a.a_op_rows) + first + (int)h, &full_a[s]);
                         ++ka;
                         moved = true;
@@ -364,6 +378,69 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
             // tensor-core Hadamard, scales by svh, rounds and stores y.
             constexpr uint32_t kZStride = 128u + 8u;  // halfs a row: 16-byte aligned rows, staggered over the banks
             __half* ztile = reinterpret_cast<__half*>(smem);
+            constexpr bool sliced = SLICED;
+            const uint32_t tile = blockIdx.y * gridDim.x + blockIdx.x;
+            float* slab = sliced ? a.part + (size_t)tile * a.ksplit * (BM * 128u) : nullptr;
+            if (sliced) {
+                // this slice's accumulators to its place in the tile's slab
+#pragma unroll 1
+                for (uint32_t hc = 0; hc < (BM / 128u) * kChunks; ++hc) {
+                    const uint32_t half = hc / kChunks, c = (hc % kChunks) * 16u;
+                    const uint32_t r = half * 128u + quarter * 32u + lane;
+                    uint32_t v[16];
+                    tmem_ld16(tmem + ((quarter * 32u) << 16) + half * 128u + col0 + c, v);
+                    if ((int)r < rows) {
+                        float4* dst = reinterpret_cast<float4*>(slab + ((size_t)blockIdx.z * BM + r) * 128u + col0 + c);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            __stcg(dst + j, make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                        __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
+                    }
+                }
+                tc_fence_before();
+                __threadfence();
+                named_sync(2, kDecodeWarps * 32u);
+                volatile uint32_t* last_slot = tmem_slot + 2;
+                if (dw == 0u && lane == 0u) *last_slot = atomicAdd(&a.counters[tile], 1u) == a.ksplit - 1u ? 1u : 0u;
+                named_sync(2, kDecodeWarps * 32u);
+                if (*last_slot != 0u) {
+                    __threadfence();
+                    if (dw == 0u && lane == 0u) a.counters[tile] = 0u;  // as the next call on this workspace expects it
+                }
+            }
+            const bool finisher = !sliced || *(volatile uint32_t*)(tmem_slot + 2) != 0u;
+            if (finisher) {
+            if (sliced) {
+                // The slices' sums in slice order, by all the decode warps together: a thread takes float4 positions of the
+                // tile's live rows 256 apart (a warp reads whole 512-byte rows), two positions' loads of every slice in
+                // flight at once. (Rows past the tile's last are never stored.)
+                const uint32_t tid_d = dw * 32u + lane, live = (uint32_t)rows * 32u;
+                const uint32_t nz = a.ksplit;
+#pragma unroll 1
+                for (uint32_t p0 = tid_d; p0 < live; p0 += 2u * kDecodeWarps * 32u) {
+                    float4 t[2][8];
+#pragma unroll
+                    for (uint32_t b = 0; b < 2u; ++b) {
+                        const uint32_t p = p0 + b * kDecodeWarps * 32u;
+                        const float4* src = reinterpret_cast<const float4*>(slab) + (size_t)(p >> 5) * 32u + (p & 31u);
+#pragma unroll
+                        for (uint32_t z = 0; z < 8u; ++z)
+                            if (z < nz && p < live) t[b][z] = __ldcg(src + (size_t)z * (BM * 32u));
+                    }
+#pragma unroll
+                    for (uint32_t b = 0; b < 2u; ++b) {
+                        const uint32_t p = p0 + b * kDecodeWarps * 32u;
+                        if (p >= live) continue;
+                        float4 acc = t[b][0];
+#pragma unroll
+                        for (uint32_t z = 1; z < 8u; ++z)
+                            if (z < nz) acc.x += t[b][z].x, acc.y += t[b][z].y, acc.z += t[b][z].z, acc.w += t[b][z].w;
+                        const __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
+                        *reinterpret_cast<uint2*>(ztile + (p >> 5) * kZStride + (p & 31u) * 4u) =
+                            make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+                    }
+                }
+            } else {
 #pragma unroll 1
             for (uint32_t hc = 0; hc < (BM / 128u) * kChunks; ++hc) {
                 const uint32_t half = hc / kChunks, c = (hc % kChunks) * 16u;
@@ -379,6 +456,7 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
                 uint4* dst = reinterpret_cast<uint4*>(ztile + r * kZStride + col0 + c);
                 dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                 dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            }
             }
             tc_fence_before();
             named_sync(2, kDecodeWarps * 32u);
@@ -398,6 +476,7 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
                     for (int i = 0; i < 8; ++i) store_act4(dst, dst_dt, o + 16u * i, out[i]);
                 }
             }
+            }  // finisher
         } else
 #pragma unroll 1
         for (uint32_t hc = 0; hc < (BM / 128u) * kChunks; ++hc) {
@@ -754,29 +833,30 @@ template <int BM>
 cudaError_t launch_gemm_resident(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& g, uint32_t max_tiles,
                                  cudaStream_t stream) {
     void (*fn)(const CUtensorMap, const CUtensorMap, const GemmArgs) = gemm_decode_kernel<0, 0, BM, true>;
+    if (BM == 128 && g.ksplit > 1u) fn = gemm_decode_kernel<0, 0, 128, true, false, true>;
     const uint32_t smem_bytes = Tile<BM>::smem(0);
     cudaError_t rc = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)smem_bytes);
     if (rc != cudaSuccess) return rc;
-    fn<<<dim3(g.N / kBN, max_tiles, 1), kGemmThreads, smem_bytes, stream>>>(map_a, map_b, g);
+    fn<<<dim3(g.N / kBN, max_tiles, g.ksplit > 1u ? g.ksplit : 1u), kGemmThreads, smem_bytes, stream>>>(map_a, map_b, g);
     return cudaGetLastError();
 }
 
-template <int CB, int BM, bool PAIR = false>
+template <int CB, int BM, bool PAIR = false, bool kSliced = false>
 cudaError_t launch_gemm_cb(const CUtensorMap& map, const GemmArgs& g, uint32_t max_tiles, cudaStream_t stream) {
     void (*fn)(const CUtensorMap, const CUtensorMap, const GemmArgs) = nullptr;
     switch (g.n) {
 #define T3_CASE(NN) \
-    case NN: fn = gemm_decode_kernel<NN, CB, BM, false, PAIR>; break;
+    case NN: fn = gemm_decode_kernel<NN, CB, BM, false, PAIR, kSliced>; break;
         T3_CASE(16) T3_CASE(32) T3_CASE(48) T3_CASE(64) T3_CASE(80) T3_CASE(96) T3_CASE(112) T3_CASE(128)
 #undef T3_CASE
-        default: fn = gemm_decode_kernel<0, CB, BM, false, PAIR>; break;
+        default: fn = gemm_decode_kernel<0, CB, BM, false, PAIR, kSliced>; break;
     }
     const uint32_t smem_bytes = Tile<BM, PAIR>::smem(g.n);
     cudaError_t rc = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)Tile<BM, PAIR>::smem(128u));
     if (rc != cudaSuccess) return rc;
-    fn<<<dim3(g.ops * g.N / kBN, max_tiles, 1), kGemmThreads, smem_bytes, stream>>>(map, map, g);
+    fn<<<dim3(g.ops * g.N / kBN, max_tiles, g.ksplit > 1u ? g.ksplit : 1u), kGemmThreads, smem_bytes, stream>>>(map, map, g);
     return cudaGetLastError();
 }
 
@@ -792,6 +872,9 @@ cudaError_t launch_gemm(const CUtensorMap& map, const GemmArgs& g, uint32_t max_
     if (bm == 256u)
         return codebook == kMcg ? launch_gemm_cb<kMcg, 256>(map, g, max_tiles, stream)
                                 : launch_gemm_cb<kMul1, 256>(map, g, max_tiles, stream);
+    if (g.ksplit > 1u)  // the K-slice exchange compiled in (dense linears of few rows)
+        return codebook == kMcg ? launch_gemm_cb<kMcg, 128, false, true>(map, g, max_tiles, stream)
+                                : launch_gemm_cb<kMul1, 128, false, true>(map, g, max_tiles, stream);
     return codebook == kMcg ? launch_gemm_cb<kMcg, 128>(map, g, max_tiles, stream)
                             : launch_gemm_cb<kMul1, 128>(map, g, max_tiles, stream);
 }
@@ -813,10 +896,31 @@ uint32_t one_wave_ctas() {
 
 // ---- dense linear, more than 32 rows ---------------------------------------------------------------------------------
 
-// the prepared rows only: the GEMM's epilogue finishes into y, so the inner products never reach memory
+// K slices of a dense linear of few rows: up to kSlicedRowsMax rows a call is one or two M tiles of 128 rows, out / 128 CTAs
+// each, every one decoding all of its 128 columns' weights (a 6144 -> 2048 linear at 40 rows ran on 16 CTAs). Such calls cut K
+// into slices, a CTA a slice, that meet in global memory (see GemmArgs::ksplit). The count follows the geometry alone (the
+// CTAs of TWO M tiles against two CTAs a multiprocessor, four K stages a slice at least, eight slices at most: the tile's
+// last arriver reads them all), so a row's bytes do not depend on the call's row count within the arm.
+constexpr uint32_t kSlicedRowsMax = 256;
+uint32_t prefill_ksplit(size_t rows, uint32_t in, uint32_t out) {
+    if (rows > kSlicedRowsMax) return 1u;
+    const uint32_t ncol = out / kBN, ksteps = in / kBK;
+    uint32_t s = one_wave_ctas() / ncol;
+    s = s < 8u ? s : 8u;
+    s = s < ksteps / 4u ? s : ksteps / 4u;
+    return s < 2u ? 1u : s;
+}
+
+// the prepared rows (the GEMM's epilogue finishes into y, so the inner products of an unsliced call never reach memory);
+// for a sliced call the slices' partial sums and the tiles' arrival counters as well
 size_t prefill_linear_workspace(size_t rows, uint32_t in, uint32_t out) {
-    (void)out;
-    return up256(rows * in * 2u);
+    size_t bytes = up256(rows * in * 2u);
+    const uint32_t s = prefill_ksplit(rows, in, out);
+    if (s > 1u) {
+        const size_t mtiles = (rows + 127u) / 128u, ncol = out / kBN;
+        bytes += up256(mtiles * ncol * s * 128u * 128u * 4u) + up256(mtiles * ncol * 4u);
+    }
+    return bytes;
 }
 
 cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cudaStream_t stream, int* launches) {
@@ -845,9 +949,21 @@ cudaError_t launch_prefill_linear(const PrefillLinearArgs& p, int codebook, cuda
                                            : ((ctas + sms - 1u) / sms) * (cand + 128u);
         if (cost < best) best = cost, bm = cand;
     }
+    GemmArgs g = {};
+    const uint32_t ksplit = prefill_ksplit(p.rows, p.in, p.out);
+    if (ksplit > 1u) {
+        // K slices on 128-row tiles: the slab of partial sums and the counters follow the prepared rows in the workspace
+        bm = 128u;
+        const size_t mtiles = (p.rows + 127u) / 128u;
+        uint8_t* at = ws + up256((size_t)p.rows * p.in * 2u);
+        g.ksplit = ksplit;
+        g.part = reinterpret_cast<float*>(at);
+        g.counters = reinterpret_cast<uint32_t*>(at + up256(mtiles * ncol * ksplit * 128u * 128u * 4u));
+        const cudaError_t mrc = cudaMemsetAsync(g.counters, 0, mtiles * ncol * 4u, stream);
+        if (mrc != cudaSuccess) return mrc;
+    }
     CUtensorMap map;
     if (!make_a_map(&map, xp, p.rows, p.in, bm == 128u ? 128u : 256u)) return cudaErrorNotSupported;
-    GemmArgs g = {};
     g.trellis[0] = g.trellis[1] = p.trellis;
     g.K = p.in;
     g.N = p.out;
