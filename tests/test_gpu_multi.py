@@ -56,7 +56,8 @@ def _worker(rank: int, world: int, port: int, fail):
             t_sh, svh_sh = par.shard_columns(dev(trellis), dev(svh), rank, world)
             y = par.column_sharded_linear(x, t_sh, dev(suh), svh_sh, out_dim, t3.Decode.mul1)
             whole = t3.linear(x, dev(trellis), dev(suh), dev(svh))
-            # a rank computes whole output columns with the unsharded K split: the same bytes as the single-GPU call
+            # a rank computes whole output columns; at this geometry shard and whole take the same K split (1024 inputs
+            # cap it): the same bytes as the single-GPU call
             assert torch.equal(y.view(torch.int16), whole.view(torch.int16)), f"rank {rank} rows {rows}: column shards differ"
             # left sharded (no collective) and gathered as stacked shards: the same columns
             b0, b1 = par.column_blocks(out_dim, rank, world)
