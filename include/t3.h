@@ -122,8 +122,9 @@ int t3_codebook_table(t3_decode dec, void* out, void* stream);
  * t3_linear_workspace_bytes returns 0 for the call (up to 8 rows). For 9 to 32 rows the workspace (rows x in f16, 256-byte
  * aligned) is OPTIONAL: with it the rows are rotated once by a launch of their own ahead of the GEMV, without it every CTA
  * rotates its own copy; the same bytes either way. Past 32 rows it is required (256-byte aligned): the prepared rows, and
- * for calls of up to 256 rows on a linear with few 128-column blocks the partial sums of the K slices such a call is cut
- * into (the slices meet there; a row's bytes do not depend on the row count within 33..256, nor within 257 and up). */
+ * for calls of up to 512 rows on a linear with few 128-column blocks the partial sums of the K slices such a call is cut
+ * into (the slices meet there; the slice counts of the two arms, 33..256 and 257..512 rows, follow in and out alone, so a
+ * row's bytes do not depend on the row count within an arm, nor past 512 rows). */
 size_t t3_linear_workspace_bytes(size_t rows, int in_dim, int out_dim, int n);
 int t3_linear(const void* x, int x_dtype, size_t rows, const void* trellis, const void* suh, const void* svh,
               int in_dim, int out_dim, int n, t3_decode dec, void* y, void* workspace, size_t workspace_bytes,

@@ -90,9 +90,13 @@ def test_workspace_sizes():
     b = _bank(hidden=2048, inter=512)
     assert L.t3_moe_workspace_bytes(4, 10, C.byref(b)) >= 40 * (512 + 2048) * 2
     assert L.t3_linear_workspace_bytes(1, 2048, 2048, 64) == 0
-    # prefill rows: the prepared rows; up to 256 rows of a linear with few 128-column CTAs, the K slices' slab as well
-    assert L.t3_linear_workspace_bytes(257, 6144, 2048, 64) == 257 * 6144 * 2
-    assert L.t3_linear_workspace_bytes(256, 6144, 2048, 64) > 256 * 6144 * 2 + 2 * 16 * 2 * 128 * 128 * 4
+    # prefill rows: the prepared rows; for few rows of a linear with few 128-column CTAs, the K slices' slab as well (two arms,
+    # 33..256 and 257..512 rows; the second only where K is long)
+    assert L.t3_linear_workspace_bytes(513, 6144, 2048, 64) == 513 * 6144 * 2
+    assert L.t3_linear_workspace_bytes(512, 6144, 2048, 64) > 512 * 6144 * 2 + 4 * 16 * 2 * 128 * 128 * 4
+    assert L.t3_linear_workspace_bytes(257, 2048, 2048, 64) == 257 * 2048 * 2
+    assert L.t3_linear_workspace_bytes(256, 2048, 2048, 64) > 256 * 2048 * 2 + 2 * 16 * 2 * 128 * 128 * 4
+    assert L.t3_linear_workspace_bytes(256, 2048, 6144, 64) == 256 * 2048 * 2  # short K, CTAs past one a multiprocessor
     assert L.t3_linear_workspace_bytes(256, 2048, 32768, 64) == 256 * 2048 * 2  # 256 CTAs a row tile: nothing to cut
 
 

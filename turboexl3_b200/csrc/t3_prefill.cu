@@ -896,19 +896,28 @@ uint32_t one_wave_ctas() {
 
 // ---- dense linear, more than 32 rows ---------------------------------------------------------------------------------
 
-// K slices of a dense linear of few rows: up to kSlicedRowsMax rows a call is one or two M tiles of 128 rows, out / 128 CTAs
-// each, every one decoding all of its 128 columns' weights (a 6144 -> 2048 linear at 40 rows ran on 16 CTAs). Such calls cut K
-// into slices, a CTA a slice, that meet in global memory (see GemmArgs::ksplit). The count follows the geometry alone (the
-// CTAs of TWO M tiles against two CTAs a multiprocessor, four K stages a slice at least, eight slices at most: the tile's
-// last arriver reads them all), so a row's bytes do not depend on the call's row count within the arm.
-constexpr uint32_t kSlicedRowsMax = 256;
+// K slices of a dense linear of few rows: a call of up to 512 rows is one to four M tiles of 128 rows, out / 128 CTAs each,
+// every one decoding all of its 128 columns' weights (a 6144 -> 2048 linear ran on 16 to 64 CTAs for 66 us whatever its
+// rows). Such calls cut K into slices, a CTA a slice, that meet in global memory (see GemmArgs::ksplit). Two arms, 33..256
+// rows (two M tiles at most) and 257..512 (four), each with a slice count that follows the geometry alone, so a row's bytes
+// do not depend on the call's row count within an arm. The count: what fills two CTAs a multiprocessor at the arm's most
+// tiles, eight at most (the tile's last arriver reads every slice), four K stages a slice at least — eight where K is short
+// (under 64 stages), and there only while every CTA has a multiprocessor to itself and only in the first arm: with short K
+// the slab's traffic and two CTAs sharing a multiprocessor cost what the slices save (measured: 2048 -> 6144 at 256 rows
+// 35 us in three slices against 29, 2048 -> 2048 at 512 rows 32 us in four against 28).
 uint32_t prefill_ksplit(size_t rows, uint32_t in, uint32_t out) {
-    if (rows > kSlicedRowsMax) return 1u;
-    const uint32_t ncol = out / kBN, ksteps = in / kBK;
-    uint32_t s = one_wave_ctas() / ncol;
+    if (rows > 512u) return 1u;
+    const uint32_t ncol = out / kBN, ksteps = in / kBK, sms = one_wave_ctas();
+    const bool long_k = ksteps >= 64u;
+    const uint32_t mtiles = rows <= 256u ? 2u : 4u;
+    if (mtiles == 4u && !long_k) return 1u;
+    uint32_t s = (2u * sms) / (mtiles * ncol);
     s = s < 8u ? s : 8u;
-    s = s < ksteps / 4u ? s : ksteps / 4u;
-    return s < 2u ? 1u : s;
+    const uint32_t by_k = long_k ? ksteps / 4u : ksteps / 8u;
+    s = s < by_k ? s : by_k;
+    if (s < 2u) return 1u;
+    if (!long_k && mtiles * ncol * s > sms) return 1u;
+    return s;
 }
 
 // the prepared rows (the GEMM's epilogue finishes into y, so the inner products of an unsliced call never reach memory);
