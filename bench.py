@@ -489,7 +489,7 @@ def run_case(args) -> None:
         per = len(calls)
     elif args.case == "dense_decode":
         # one linear at decode rows over enough weight copies (random codes) to stream from HBM: --shape INxOUTxK
-        i, o, k = (int(v) for v in args.shape.lower().split("x"))
+        i, o, k = (int(v) for v in (args.shape or "16384x7168x4").lower().split("x"))
         halfs = (i // 16) * (o // 16) * 16 * k
         copies = max(2, min(8, int(400e6 // (2 * halfs))))
         pool = torch.randint(0, 2 ** 31 - 1, (copies * halfs // 2,), dtype=torch.int32, device="cuda").view(torch.int16)
@@ -502,8 +502,9 @@ def run_case(args) -> None:
         run = lambda: [t3.linear(x, w, suh_d, svh_d) for w in ws]
         per = copies
     else:
-        w = tuple(dev(a) for a in synth.linear(5, 2048, 6144, 64))
-        x = dev(synth.activations(1, max(args.rows, 33), 2048))
+        i, o, k = (int(v) for v in (args.shape or "2048x6144x4").lower().split("x"))
+        w = tuple(dev(a) for a in synth.linear(5, i, o, 16 * k))
+        x = dev(synth.activations(1, max(args.rows, 33), i))
         if args.case == "resident_prefill":
             w_t = t3.resident_build(w[0])
             run = lambda: t3.linear_resident(x, w_t, w[1], w[2])
@@ -808,7 +809,7 @@ def main() -> None:
     ap.add_argument("--case", default=None, choices=["moe_decode", "moe_prefill", "dense_prefill", "resident_prefill", "dense_decode"],
                     help="run one case eagerly --steps times and exit (for profilers)")
     ap.add_argument("--rows", type=int, default=1, help="rows of --case")
-    ap.add_argument("--shape", default="16384x7168x4", help="INxOUTxK of --case dense_decode")
+    ap.add_argument("--shape", default=None, help="INxOUTxK of --case dense_decode (default 16384x7168x4) and dense_prefill / resident_prefill (default 2048x6144x4)")
     ap.add_argument("--probe", type=int, default=0, choices=[0, 1, 2, 3],
                     help="--case dense_decode with the kernel's timing probe in the served kernel's place (t3_config.probe)")
     args = ap.parse_args()
