@@ -307,7 +307,8 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
             umma_commit(acc_full);
         }
     } else {
-        // decode warp dw: output tile column dw % 8 of the CTA's 128, input tile rows 2 (dw / 8) and 2 (dw / 8) + 1 of a stage
+        // decode warp dw: output tile column dw % 8 of the CTA's 128, input tile rows kTilesPerWarp (dw / 8) .. of a stage (all
+        // four with eight warps)
         const uint32_t dw = warp - 2u, tcol = dw & 7u, tk0 = (dw >> 3) * kTilesPerWarp;
         constexpr int NP = NN > 0 ? NN : 16;
         constexpr uint32_t kRaw = raw_words(NP);
@@ -378,11 +379,11 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
             // tensor-core Hadamard, scales by svh, rounds and stores y.
             constexpr uint32_t kZStride = 128u + 8u;  // halfs a row: 16-byte aligned rows, staggered over the banks
             __half* ztile = reinterpret_cast<__half*>(smem);
-            constexpr bool sliced = SLICED;
-            const uint32_t tile = blockIdx.y * gridDim.x + blockIdx.x;
-            float* slab = sliced ? a.part + (size_t)tile * a.ksplit * (BM * 128u) : nullptr;
-            if (sliced) {
+            bool finisher = true;  // this CTA runs the finish (with K in slices: the tile's last arriver only)
+            if (SLICED) {
                 // this slice's accumulators to its place in the tile's slab
+                const uint32_t tile = blockIdx.y * gridDim.x + blockIdx.x;
+                float* slab = a.part + (size_t)tile * a.ksplit * (BM * 128u);
 #pragma unroll 1
                 for (uint32_t hc = 0; hc < (BM / 128u) * kChunks; ++hc) {
                     const uint32_t half = hc / kChunks, c = (hc % kChunks) * 16u;
@@ -403,80 +404,78 @@ __global__ void __launch_bounds__(kGemmThreads, Tile<BM, PAIR>::kMinBlocks)
                 volatile uint32_t* last_slot = tmem_slot + 2;
                 if (dw == 0u && lane == 0u) *last_slot = atomicAdd(&a.counters[tile], 1u) == a.ksplit - 1u ? 1u : 0u;
                 named_sync(2, kDecodeWarps * 32u);
-                if (*last_slot != 0u) {
+                finisher = *last_slot != 0u;
+                if (finisher) {
                     __threadfence();
                     if (dw == 0u && lane == 0u) a.counters[tile] = 0u;  // as the next call on this workspace expects it
-                }
-            }
-            const bool finisher = !sliced || *(volatile uint32_t*)(tmem_slot + 2) != 0u;
-            if (finisher) {
-            if (sliced) {
-                // The slices' sums in slice order, by all the decode warps together: a thread takes float4 positions of the
-                // tile's live rows 256 apart (a warp reads whole 512-byte rows), two positions' loads of every slice in
-                // flight at once. (Rows past the tile's last are never stored.)
-                const uint32_t tid_d = dw * 32u + lane, live = (uint32_t)rows * 32u;
-                const uint32_t nz = a.ksplit;
+                    // The slices' sums in slice order, by all the decode warps together: a thread takes float4 positions of
+                    // the tile's live rows 256 apart (a warp reads whole 512-byte rows), two positions' loads of every slice
+                    // in flight at once. (Rows past the tile's last are never stored.)
+                    const uint32_t tid_d = dw * 32u + lane, live = (uint32_t)rows * 32u;
+                    const uint32_t nz = a.ksplit;
 #pragma unroll 1
-                for (uint32_t p0 = tid_d; p0 < live; p0 += 2u * kDecodeWarps * 32u) {
-                    float4 t[2][8];
+                    for (uint32_t p0 = tid_d; p0 < live; p0 += 2u * kDecodeWarps * 32u) {
+                        float4 t[2][8];
 #pragma unroll
-                    for (uint32_t b = 0; b < 2u; ++b) {
-                        const uint32_t p = p0 + b * kDecodeWarps * 32u;
-                        const float4* src = reinterpret_cast<const float4*>(slab) + (size_t)(p >> 5) * 32u + (p & 31u);
+                        for (uint32_t b = 0; b < 2u; ++b) {
+                            const uint32_t p = p0 + b * kDecodeWarps * 32u;
+                            const float4* src = reinterpret_cast<const float4*>(slab) + p;
 #pragma unroll
-                        for (uint32_t z = 0; z < 8u; ++z)
-                            if (z < nz && p < live) t[b][z] = __ldcg(src + (size_t)z * (BM * 32u));
-                    }
+                            for (uint32_t z = 0; z < 8u; ++z)
+                                if (z < nz && p < live) t[b][z] = __ldcg(src + (size_t)z * (BM * 32u));
+                        }
 #pragma unroll
-                    for (uint32_t b = 0; b < 2u; ++b) {
-                        const uint32_t p = p0 + b * kDecodeWarps * 32u;
-                        if (p >= live) continue;
-                        float4 acc = t[b][0];
+                        for (uint32_t b = 0; b < 2u; ++b) {
+                            const uint32_t p = p0 + b * kDecodeWarps * 32u;
+                            if (p >= live) continue;
+                            float4 acc = t[b][0];
 #pragma unroll
-                        for (uint32_t z = 1; z < 8u; ++z)
-                            if (z < nz) acc.x += t[b][z].x, acc.y += t[b][z].y, acc.z += t[b][z].z, acc.w += t[b][z].w;
-                        const __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
-                        *reinterpret_cast<uint2*>(ztile + (p >> 5) * kZStride + (p & 31u) * 4u) =
-                            make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+                            for (uint32_t z = 1; z < 8u; ++z)
+                                if (z < nz) acc.x += t[b][z].x, acc.y += t[b][z].y, acc.z += t[b][z].z, acc.w += t[b][z].w;
+                            const __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
+                            *reinterpret_cast<uint2*>(ztile + (p >> 5) * kZStride + (p & 31u) * 4u) =
+                                make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+                        }
                     }
                 }
             } else {
 #pragma unroll 1
-            for (uint32_t hc = 0; hc < (BM / 128u) * kChunks; ++hc) {
-                const uint32_t half = hc / kChunks, c = (hc % kChunks) * 16u;
-                const uint32_t r = half * 128u + quarter * 32u + lane;
-                uint32_t v[16];
-                tmem_ld16(tmem + ((quarter * 32u) << 16) + half * 128u + col0 + c, v);
-                uint32_t packed[8];
+                for (uint32_t hc = 0; hc < (BM / 128u) * kChunks; ++hc) {
+                    const uint32_t half = hc / kChunks, c = (hc % kChunks) * 16u;
+                    const uint32_t r = half * 128u + quarter * 32u + lane;
+                    uint32_t v[16];
+                    tmem_ld16(tmem + ((quarter * 32u) << 16) + half * 128u + col0 + c, v);
+                    uint32_t packed[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const __half2 h = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
-                    packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+                    for (int j = 0; j < 8; ++j) {
+                        const __half2 h = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                        packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(ztile + r * kZStride + col0 + c);
+                    dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
                 }
-                uint4* dst = reinterpret_cast<uint4*>(ztile + r * kZStride + col0 + c);
-                dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
             }
-            }
-            tc_fence_before();
-            named_sync(2, kDecodeWarps * 32u);
-            const HadB hb = had_b(lane);
-            const uint32_t pg = lane >> 2, pq = lane & 3u;
-            const __half* sv = svh_s + 4u * pq;
-            void* const dst = a.y ? a.y : static_cast<void*>(a.z);
-            const int dst_dt = a.y ? a.y_dt : (int)kF16;
+            if (finisher) {
+                tc_fence_before();
+                named_sync(2, kDecodeWarps * 32u);
+                const HadB hb = had_b(lane);
+                const uint32_t pg = lane >> 2, pq = lane & 3u;
+                const __half* sv = svh_s + 4u * pq;
+                void* const dst = a.y ? a.y : static_cast<void*>(a.z);
+                const int dst_dt = a.y ? a.y_dt : (int)kF16;
 #pragma unroll 1
-            for (uint32_t g8 = dw; g8 < BM / 8u; g8 += kDecodeWarps) {
-                const uint32_t r = g8 * 8u + pg;
-                float out[8][4];
-                finish_block_mma(ztile + r * kZStride + 4u * pq, sv, hb, out);
-                if ((int)r < rows) {
-                    const size_t o = op * a.z_op_stride + (size_t)(first + (int)r) * a.N + nt * kBN + 4u * pq;
+                for (uint32_t g8 = dw; g8 < BM / 8u; g8 += kDecodeWarps) {
+                    const uint32_t r = g8 * 8u + pg;
+                    float out[8][4];
+                    finish_block_mma(ztile + r * kZStride + 4u * pq, sv, hb, out);
+                    if ((int)r < rows) {
+                        const size_t o = op * a.z_op_stride + (size_t)(first + (int)r) * a.N + nt * kBN + 4u * pq;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) store_act4(dst, dst_dt, o + 16u * i, out[i]);
+                        for (int i = 0; i < 8; ++i) store_act4(dst, dst_dt, o + 16u * i, out[i]);
+                    }
                 }
             }
-            }  // finisher
         } else
 #pragma unroll 1
         for (uint32_t hc = 0; hc < (BM / 128u) * kChunks; ++hc) {
