@@ -90,3 +90,37 @@ def test_plan_refusals_are_the_calls():
         t3.plan_moe(4, 2, 10, 500, 2048, 48)  # hidden is not whole 128-blocks
     with pytest.raises(t3.Exl3Error, match="Exl3EngineNotImplemented"):
         t3.plan_moe(33, 2, 10, 512, 2048, 48)  # prefill rows: the plan covers the decode-row kernels
+
+
+def test_prefill_workspace_holds_the_prepared_rows_and_a_bounded_slab():
+    """Past 32 rows the workspace is the prepared rows (f16) plus, for calls of up to 512 rows that are cut into K slices, a slab
+    of partial sums: a whole number of 64 KB tiles (128 x 128 f32 a slice a row tile), never more than two CTAs a
+    multiprocessor's worth; nothing past 512 rows; and the same answer for every rate (the slab follows in and out alone)."""
+    L = lib()
+    up256 = lambda v: (v + 255) & ~255
+    for i, o in itertools.product(DIMS, DIMS):
+        for rows in (33, 128, 129, 256, 257, 512, 513, 4096):
+            ws = L.t3_linear_workspace_bytes(rows, i, o, 64)
+            xp = up256(rows * i * 2)
+            assert ws >= xp, (i, o, rows)
+            assert ws == L.t3_linear_workspace_bytes(rows, i, o, 36)
+            if rows > 512:
+                assert ws == xp, (i, o, rows)
+                continue
+            extra = ws - xp
+            if extra:
+                mtiles, ncol = (rows + 127) // 128, o // 128
+                counters = up256(mtiles * ncol * 4)
+                slab = extra - counters
+                assert slab > 0 and slab % (mtiles * ncol * 65536) == 0, (i, o, rows, extra)
+                slices = slab // (mtiles * ncol * 65536)
+                assert 2 <= slices <= 8 and slices * 4 <= i // 64, (i, o, rows, slices)
+                assert mtiles * ncol * slices <= 2 * 148, (i, o, rows, slices)  # two CTAs a multiprocessor at most (148 of them)
+        # within an arm the slice count does not depend on the rows
+        for lo, hi in ((33, 256), (257, 512)):
+            per_tile = set()
+            for rows in (lo, (lo + hi) // 2, hi):
+                extra = L.t3_linear_workspace_bytes(rows, i, o, 64) - up256(rows * i * 2)
+                mtiles, ncol = (rows + 127) // 128, o // 128
+                per_tile.add((extra - up256(mtiles * ncol * 4)) // (mtiles * ncol * 65536) if extra else 1)
+            assert len(per_tile) == 1, (i, o, lo, hi, per_tile)
